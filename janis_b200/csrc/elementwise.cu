@@ -1,0 +1,256 @@
+// Row-wise kernels of the residual stream: embedding gather, RMS norms (alone,
+// and fused with the residual sum and the next norm), the gated activation,
+// and the rotary encoding fused with the write of keys and values into the
+// paged cache.  Sums of squares, reciprocal roots, angles and the residual sum
+// are float; storage types only decide what is read and written.
+#include "common.cuh"
+
+namespace janis {
+
+// ---------------------------------------------------------------------------
+// embedding: out[t, :] = float(table[tokens[t], :]) * scale        (float rows)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                             float* __restrict__ out, int H, int V, float scale) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= V) tok = 0;   // the host has checked the ids; padding rows carry 0
+    const T* row = table + (size_t)tok * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]) * scale;
+}
+
+// ---------------------------------------------------------------------------
+// y[r, :] = x[src(r), :] * rsqrt(mean(x^2) + eps) * w      (w already holds offset + weight)
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void rmsnorm_kernel(const TI* __restrict__ x, const float* __restrict__ w,
+                               const int* __restrict__ rows, TO* __restrict__ y, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const TI* xr = x + (size_t)src * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_float(xr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* yr = y + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_float<TO>(to_float(xr[i]) * inv * w[i]);
+}
+
+// ---------------------------------------------------------------------------
+// h[r, :] += norm(res[r, :]; w_post)           (the residual sum, float, in place;
+//                                               res itself when there is no w_post)
+// y[r, :]  = norm(h[r, :]; w_next)             (only when w_next is given)
+// `res` may be the sum of `n_part` partial results laid out [n_part, rows, H].
+// ---------------------------------------------------------------------------
+template <typename TR, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_part,
+                                   size_t part_stride, const float* __restrict__ w_post, float eps_post,
+                                   const float* __restrict__ w_next, float eps_next,
+                                   TO* __restrict__ y, int H) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const TR* rr = res + (size_t)r * H;
+    float* hr = h + (size_t)r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = to_float(rr[i]);
+        for (int p = 1; p < n_part; ++p) v += to_float(rr[p * part_stride + i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    // without a post norm (w_post == nullptr) the result is added as it is
+    const float inv = w_post ? 1.0f / sqrtf(ss / (float)H + eps_post) : 1.0f;
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = to_float(rr[i]);
+        for (int p = 1; p < n_part; ++p) v += to_float(rr[p * part_stride + i]);
+        const float hv = hr[i] + (w_post ? v * inv * w_post[i] : v);
+        hr[i] = hv;                         // read back below by this same thread only
+        ss2 = fmaf(hv, hv, ss2);
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)H + eps_next);
+    TO* yr = y + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_float<TO>(hr[i] * inv2 * w_next[i]);
+}
+
+// ---------------------------------------------------------------------------
+// gated activation over a fused [rows, 2*I] product whose columns alternate in
+// groups of `group`: group g of gate columns, then group g of up columns.
+// act: 0 = gelu (tanh form), 1 = silu
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int rows, int I, int group,
+                                 int act) {
+    const size_t n = (size_t)rows * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(idx / I), j = (int)(idx % I);
+        const size_t base = (size_t)r * 2 * I + (size_t)(j / group) * 2 * group + (j % group);
+        const float g = to_float(gu[base]), u = to_float(gu[base + group]);
+        const float a = act == 0 ? gelu_tanh(g) : g / (1.0f + expf(-g));
+        out[idx] = from_float<T>(a * u);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// rotary encoding of q and k in place, and the write of k (rotated) and v into
+// the paged cache.  qkv: [T, row_heads, hd], heads q, then k, then v (a layer that
+// only reads another's keys has rows of q alone).  Pair (i, i + rot/2), i < rot/2;
+// features from `rot` on pass through.  theta = float(pos) * inv_freq[i].
+// A token of a sequence with slot < 0 (padding) is rotated but not stored.  With
+// a ring (ring_len > 0) position p lives at p % ring_len and only positions
+// >= seq_end - ring_len are stored, so that no two tokens of a step share a place.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ tok_pos,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                  const int* __restrict__ seq_end, const float* __restrict__ inv_freq,
+                                  int rot, int nq, int nkv, int hd, int row_heads, T* __restrict__ kpool,
+                                  T* __restrict__ vpool, const int* __restrict__ page_table,
+                                  int table_stride, int ring_len, int store_q_only) {
+    extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = rot >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float theta = (float)pos * inv_freq[i];
+        float s, c;
+        sincosf(theta, &s, &c);
+        cs[i] = c;
+        cs[half + i] = s;
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)t * row_heads * hd;
+    const int n_rot_heads = store_q_only ? nq : nq + nkv;
+    for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
+        const int head = idx / half, i = idx % half;
+        T* p = row + (size_t)head * hd;
+        const float a = to_float(p[i]), b = to_float(p[i + half]);
+        const float c = cs[i], s = cs[half + i];
+        p[i] = from_float<T>(a * c - b * s);
+        p[i + half] = from_float<T>(a * s + b * c);
+    }
+    if (store_q_only || kpool == nullptr) return;
+    const int seq = tok_seq[t];
+    const int slot = seq_slot[seq];
+    if (slot < 0) return;
+    int idx = pos;
+    if (ring_len > 0) {
+        if (pos < seq_end[seq] - ring_len) return;
+        idx = pos % ring_len;
+    }
+    const int page = page_table[(size_t)slot * table_stride + idx / JANIS_PAGE];
+    const int off = idx % JANIS_PAGE;
+    __syncthreads();                        // the rotated k of this row is complete
+    const T* ksrc = row + (size_t)nq * hd;
+    const T* vsrc = row + (size_t)(nq + nkv) * hd;
+    for (int e = threadIdx.x; e < nkv * hd; e += blockDim.x) {
+        const int kvh = e / hd, d = e % hd;
+        const size_t dst = (((size_t)page * nkv + kvh) * JANIS_PAGE + off) * hd + d;
+        kpool[dst] = ksrc[e];
+        vpool[dst] = vsrc[e];
+    }
+}
+
+}  // namespace janis
+
+using namespace janis;
+
+static inline int row_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
+
+JANIS_EXPORT int janis_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H,
+                             int V, float scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (table_dtype == JANIS_F32)
+        embed_kernel<float><<<T, row_threads(H), 0, stream>>>(tokens, (const float*)table, out, H, V, scale);
+    else if (table_dtype == JANIS_BF16)
+        embed_kernel<bf16><<<T, row_threads(H), 0, stream>>>(tokens, (const bf16*)table, out, H, V, scale);
+    else
+        return fail("embed: unknown table dtype %d", table_dtype);
+    return launched("embed");
+}
+
+JANIS_EXPORT int janis_rmsnorm(const void* x, int x_dtype, const float* w, const int* rows, void* y, int y_dtype,
+                               int R, int H, float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    const int nt = row_threads(H);
+#define JANIS_CASE(TI, TO) rmsnorm_kernel<TI, TO><<<R, nt, 0, stream>>>((const TI*)x, w, rows, (TO*)y, H, eps)
+    if (x_dtype == JANIS_F32 && y_dtype == JANIS_F32) JANIS_CASE(float, float);
+    else if (x_dtype == JANIS_F32 && y_dtype == JANIS_BF16) JANIS_CASE(float, bf16);
+    else if (x_dtype == JANIS_BF16 && y_dtype == JANIS_F32) JANIS_CASE(bf16, float);
+    else if (x_dtype == JANIS_BF16 && y_dtype == JANIS_BF16) JANIS_CASE(bf16, bf16);
+    else return fail("rmsnorm: unknown dtypes %d -> %d", x_dtype, y_dtype);
+#undef JANIS_CASE
+    return launched("rmsnorm");
+}
+
+JANIS_EXPORT int janis_add_rmsnorm(float* h, const void* res, int res_dtype, int n_part, long long part_stride,
+                                   const float* w_post, float eps_post, const float* w_next, float eps_next,
+                                   void* y, int y_dtype, int R, int H, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (n_part < 1) return fail("add_rmsnorm: n_part must be >= 1");
+    if (w_next != nullptr && y == nullptr) return fail("add_rmsnorm: a next norm needs an output");
+    const int nt = row_threads(H);
+#define JANIS_CASE(TR, TO)                                                                                     \
+    add_rmsnorm_kernel<TR, TO><<<R, nt, 0, stream>>>(h, (const TR*)res, n_part, (size_t)part_stride, w_post,    \
+                                                     eps_post, w_next, eps_next, (TO*)y, H)
+    if (res_dtype == JANIS_F32 && y_dtype == JANIS_F32) JANIS_CASE(float, float);
+    else if (res_dtype == JANIS_F32 && y_dtype == JANIS_BF16) JANIS_CASE(float, bf16);
+    else if (res_dtype == JANIS_BF16 && y_dtype == JANIS_F32) JANIS_CASE(bf16, float);
+    else if (res_dtype == JANIS_BF16 && y_dtype == JANIS_BF16) JANIS_CASE(bf16, bf16);
+    else return fail("add_rmsnorm: unknown dtypes %d -> %d", res_dtype, y_dtype);
+#undef JANIS_CASE
+    return launched("add_rmsnorm");
+}
+
+JANIS_EXPORT int janis_gated_act(const void* gu, void* out, int dtype, int rows, int I, int group, int act,
+                                 cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (group <= 0 || I % group) return fail("gated_act: width %d is not a multiple of the group %d", I, group);
+    const size_t n = (size_t)rows * I;
+    const int nt = 256;
+    const int nb = (int)((n + nt - 1) / nt < 148 * 16 ? (n + nt - 1) / nt : 148 * 16);
+    if (dtype == JANIS_F32)
+        gated_act_kernel<float><<<nb, nt, 0, stream>>>((const float*)gu, (float*)out, rows, I, group, act);
+    else if (dtype == JANIS_BF16)
+        gated_act_kernel<bf16><<<nb, nt, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I, group, act);
+    else
+        return fail("gated_act: unknown dtype %d", dtype);
+    return launched("gated_act");
+}
+
+JANIS_EXPORT int janis_rope_store(void* qkv, int dtype, const int* tok_pos, const int* tok_seq,
+                                  const int* seq_slot, const int* seq_end, const float* inv_freq, int rot,
+                                  int T, int nq, int nkv, int hd, int row_heads, void* kpool, void* vpool,
+                                  const int* page_table, int table_stride, int ring_len, int store_q_only,
+                                  cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rot < 0 || rot > hd || (rot & 1)) return fail("rope_store: rotary width %d does not fit head size %d", rot, hd);
+    if (row_heads < (store_q_only ? nq : nq + 2 * nkv)) return fail("rope_store: rows of %d heads are too short", row_heads);
+    if (ring_len % JANIS_PAGE) return fail("rope_store: ring length %d is not a multiple of the page", ring_len);
+    const size_t smem = (size_t)rot * sizeof(float);
+    if (smem > 48 * 1024) return fail("rope_store: rotary width %d too large", rot);
+    const int nt = 256;
+    if (dtype == JANIS_F32)
+        rope_store_kernel<float><<<T, nt, smem, stream>>>((float*)qkv, tok_pos, tok_seq, seq_slot, seq_end,
+                                                          inv_freq, rot, nq, nkv, hd, row_heads, (float*)kpool,
+                                                          (float*)vpool, page_table, table_stride, ring_len,
+                                                          store_q_only);
+    else if (dtype == JANIS_BF16)
+        rope_store_kernel<bf16><<<T, nt, smem, stream>>>((bf16*)qkv, tok_pos, tok_seq, seq_slot, seq_end,
+                                                         inv_freq, rot, nq, nkv, hd, row_heads, (bf16*)kpool, (bf16*)vpool,
+                                                         page_table, table_stride, ring_len, store_q_only);
+    else
+        return fail("rope_store: unknown dtype %d", dtype);
+    return launched("rope_store");
+}
+
+JANIS_EXPORT const char* janis_last_error() { return error_buffer(); }

@@ -1,0 +1,272 @@
+// Choosing the next token from float logits [R, V] on the device: greedy (the
+// lowest id among equal maxima), temperature with an optional nucleus (top-p)
+// cut, the repetition penalty, and masking of given ids.  One CTA per row; all
+// sums run in a fixed order, so a row's choice depends on the row alone.
+//
+// The random number of a draw is Philox4x32-10 keyed by the seed and counted by
+// (request id, index of the token in its reply): it does not depend on which
+// other requests share the batch.
+#include "common.cuh"
+
+namespace janis {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+    const uint32_t hi0 = __umulhi(M0, c[0]), lo0 = M0 * c[0];
+    const uint32_t hi1 = __umulhi(M1, c[2]), lo1 = M1 * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+}
+
+__device__ __forceinline__ float philox_uniform(unsigned long long seed, uint32_t request, uint32_t index) {
+    uint32_t c[4] = {request, index, 0u, 0u};
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        philox_round(c, k0, k1);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return (float)(c[0] >> 8) * (1.0f / 16777216.0f);   // [0, 1), 24 bits
+}
+
+// max of a row with the lowest index that attains it; every thread gets both
+__device__ void block_argmax(float v, int i, float* sv, int* si, float& out_v, int& out_i) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+    __syncthreads();
+    if (lane == 0) { sv[warp] = v; si[warp] = i; }
+    __syncthreads();
+    float bv = sv[0];
+    int bi = si[0];
+    for (int w = 1; w < nwarp; ++w)
+        if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    out_v = bv;
+    out_i = bi;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    float v = -INFINITY;
+    int i = 0x7fffffff;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) {
+        const float x = row[j];
+        if (x > v || (x == v && j < i)) { v = x; i = j; }   // NaN never wins
+    }
+    float bv;
+    int bi;
+    block_argmax(v, i, sv, si, bv, bi);
+    if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+}
+
+// Exclusive scan of one value per thread, in thread order, by thread 0.
+__device__ float block_exclusive_scan(float v, float* buf, float& total) {
+    __syncthreads();
+    buf[threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float run = 0.f;
+        for (int i = 0; i < (int)blockDim.x; ++i) {
+            const float x = buf[i];
+            buf[i] = run;
+            run += x;
+        }
+        buf[blockDim.x] = run;
+    }
+    __syncthreads();
+    total = buf[blockDim.x];
+    return buf[threadIdx.x];
+}
+
+// Temperature sampling of one row.  w_j = exp((l_j - max) / temp).  With top_p < 1
+// the kept set is the shortest prefix, in descending w with ties to the lower id,
+// whose mass reaches top_p of the total; the draw is the inverse CDF over the kept
+// ids in id order at r = u * kept mass.  Thread i owns the contiguous ids
+// [i * per, (i + 1) * per), so thread order is id order.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int* __restrict__ out, float* __restrict__ u_out, int V,
+              float temp, float top_p, unsigned long long seed, const int* __restrict__ request_ids,
+              const int* __restrict__ token_index) {
+    __shared__ float buf[SAMPLE_THREADS + 1];
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ int chosen;
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * V;
+    const int per = (V + blockDim.x - 1) / blockDim.x;
+    const int lo = min((int)threadIdx.x * per, V), hi = min(lo + per, V);
+
+    float v = -INFINITY;
+    int vi = 0x7fffffff;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) {
+        const float x = row[j];
+        if (x > v || (x == v && j < vi)) { v = x; vi = j; }
+    }
+    float mx;
+    int mi;
+    block_argmax(v, vi, sv, si, mx, mi);
+    const float inv_t = 1.0f / temp;
+
+    float total;
+    float mine = 0.f;
+    for (int j = lo; j < hi; ++j) mine += expf((row[j] - mx) * inv_t);
+    block_exclusive_scan(mine, buf, total);
+
+    // nucleus: the largest threshold tau with mass(w >= tau) >= top_p * total
+    float tau = 0.f;
+    int ties_kept = 0x7fffffff;
+    const bool cut = top_p > 0.f && top_p < 1.f;
+    if (cut) {
+        const float need = top_p * total;
+        uint32_t blo = 0u, bhi = __float_as_uint(1.0f);   // w lies in [0, 1]; mass(w >= 0) = total >= need
+        while (blo < bhi) {                               // invariant: mass(w >= blo) >= need
+            const uint32_t mid = blo + (bhi - blo + 1) / 2;
+            const float th = __uint_as_float(mid);
+            float m = 0.f;
+            for (int j = lo; j < hi; ++j) {
+                const float w = expf((row[j] - mx) * inv_t);
+                if (w >= th) m += w;
+            }
+            float mass;
+            block_exclusive_scan(m, buf, mass);
+            if (mass >= need) blo = mid; else bhi = mid - 1;
+        }
+        tau = __uint_as_float(blo);
+        float above = 0.f;
+        for (int j = lo; j < hi; ++j) {
+            const float w = expf((row[j] - mx) * inv_t);
+            if (w > tau) above += w;
+        }
+        float mass_above;
+        block_exclusive_scan(above, buf, mass_above);
+        // the fewest ties, lowest ids first, that lift the mass to `need`
+        ties_kept = tau > 0.f ? (int)ceilf((need - mass_above) / tau) : 0x7fffffff;
+        if (ties_kept < 1) ties_kept = 1;
+    }
+
+    // kept mass per thread, with the rank of each tie in id order
+    float tie_count = 0.f;
+    if (cut)
+        for (int j = lo; j < hi; ++j) tie_count += (expf((row[j] - mx) * inv_t) == tau) ? 1.f : 0.f;
+    float tie_total;
+    const float tie_before = cut ? block_exclusive_scan(tie_count, buf, tie_total) : 0.f;
+    float kept = 0.f;
+    {
+        int rank = (int)tie_before;
+        for (int j = lo; j < hi; ++j) {
+            const float w = expf((row[j] - mx) * inv_t);
+            bool keep = true;
+            if (cut) {
+                if (w == tau) { keep = rank < ties_kept; ++rank; }
+                else keep = w > tau;
+            }
+            if (keep) kept += w;
+        }
+    }
+    float kept_total;
+    const float before = block_exclusive_scan(kept, buf, kept_total);
+
+    const float u = philox_uniform(seed, (uint32_t)request_ids[r], (uint32_t)token_index[r]);
+    const float target = u * kept_total;
+    if (threadIdx.x == 0) {
+        chosen = 0x7fffffff;
+        if (u_out) u_out[r] = u;
+    }
+    __syncthreads();
+    // the owner of the target walks its ids; `before <= target` holds for thread 0 always
+    if (kept > 0.f && before <= target && target <= before + kept) {
+        int rank = (int)tie_before;
+        float acc = before;
+        int pick = -1, last = -1;
+        for (int j = lo; j < hi; ++j) {
+            const float w = expf((row[j] - mx) * inv_t);
+            bool keep = true;
+            if (cut) {
+                if (w == tau) { keep = rank < ties_kept; ++rank; }
+                else keep = w > tau;
+            }
+            if (!keep) continue;
+            acc += w;
+            last = j;
+            if (target <= acc) { pick = j; break; }
+        }
+        if (pick < 0) pick = last;
+        if (pick >= 0) atomicMin(&chosen, pick);   // see below
+    }
+    __syncthreads();
+    // Two neighbouring threads can both claim a target that sits on their border;
+    // the lower id is the inverse CDF's answer, so take the minimum of the claims.
+    if (threadIdx.x == 0) out[r] = chosen != 0x7fffffff ? chosen : mi;
+}
+
+__global__ void repeat_penalty_kernel(float* __restrict__ logits, const int* __restrict__ recent, int n_recent,
+                                      int V, float penalty) {
+    // recent: [R, n_recent], -1 where empty.  A token that occurs twice is changed once.
+    const int r = blockIdx.x;
+    const int* rec = recent + (size_t)r * n_recent;
+    for (int i = threadIdx.x; i < n_recent; i += blockDim.x) {
+        const int tok = rec[i];
+        if (tok < 0 || tok >= V) continue;
+        bool first = true;
+        for (int j = 0; j < i; ++j)
+            if (rec[j] == tok) { first = false; break; }
+        if (!first) continue;
+        float* p = logits + (size_t)r * V + tok;
+        const float v = *p;
+        *p = v > 0.f ? v / penalty : v * penalty;
+    }
+}
+
+__global__ void mask_tokens_kernel(float* __restrict__ logits, const int* __restrict__ ids, int n_ids, int R,
+                                   int V) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= R * n_ids) return;
+    const int r = idx / n_ids, tok = ids[idx % n_ids];
+    if (tok >= 0 && tok < V) logits[(size_t)r * V + tok] = -INFINITY;
+}
+
+}  // namespace janis
+
+using namespace janis;
+
+JANIS_EXPORT int janis_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0) return fail("argmax: empty vocabulary");
+    argmax_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, out, V);
+    return launched("argmax");
+}
+
+JANIS_EXPORT int janis_sample(const float* logits, int* out, float* u_out, int R, int V, float temp, float top_p,
+                              unsigned long long seed, const int* request_ids, const int* token_index,
+                              cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0) return fail("sample: empty vocabulary");
+    if (!(temp > 0.f)) return fail("sample: temperature must be positive (greedy is argmax), found %g", temp);
+    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, out, u_out, V, temp, top_p, seed, request_ids,
+                                                     token_index);
+    return launched("sample");
+}
+
+JANIS_EXPORT int janis_repeat_penalty(float* logits, const int* recent, int n_recent, int R, int V, float penalty,
+                                      cudaStream_t stream) {
+    if (R <= 0 || n_recent <= 0 || !(penalty > 1.f)) return 0;
+    repeat_penalty_kernel<<<R, 64, 0, stream>>>(logits, recent, n_recent, V, penalty);
+    return launched("repeat_penalty");
+}
+
+JANIS_EXPORT int janis_mask_tokens(float* logits, const int* ids, int n_ids, int R, int V, cudaStream_t stream) {
+    if (R <= 0 || n_ids <= 0) return 0;
+    const int n = R * n_ids;
+    mask_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, ids, n_ids, R, V);
+    return launched("mask_tokens");
+}

@@ -1,0 +1,234 @@
+"""The step function: a batch of sequences, the tokens it is given, logits back.
+
+A step is either a *prompt step* (every sequence of the batch is new and brings
+its whole prompt; lengths may differ) or a *decode step* (every sequence brings
+exactly one token).  The step runs only the tokens it is given, packed without
+padding, against what earlier steps left in the cache, and returns float32
+logits at the places asked for, in the order of the entries and of their `want`.
+
+Prompt steps with many tokens are cut at sequence borders into pieces of at
+most `max_step_tokens`; the pieces are independent, so nothing changes but the
+size of the scratch buffers.  Decode steps are replayed from CUDA graphs, one
+per (padded batch size, bound on the lengths); padding rows carry slot -1, touch
+no cache and change no other row.
+
+The reference's forward takes one sequence, one offset, and returns the last
+position's logits (`qwen/model.go:346-349`, `gemma/gemma.go:196-213`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.cache import CacheError, ModelCache
+from ..parts.base import Runtime, StepContext, Workspace
+from .model import DecoderModel
+
+
+class StepError(ValueError):
+    """A step that the engine refuses before anything is launched."""
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()        # places among `tokens` whose logits are asked for
+
+
+def _bucket_batch(n: int) -> int:
+    return n if n <= 8 else (n + 7) // 8 * 8
+
+
+def _bucket_len(n: int) -> int:
+    b = 256
+    while b < n:
+        b *= 2
+    return b
+
+
+class Stepper:
+    MAX_GRAPH_BATCH = 256
+
+    def __init__(self, model: DecoderModel, cache: ModelCache, rt: Runtime, max_step_tokens: int = 16384,
+                 use_graphs: bool = True):
+        self.model, self.cache, self.rt = model, cache, rt
+        self.ws = Workspace(rt.device)
+        self.max_step_tokens = max(1, int(max_step_tokens))
+        self.use_graphs = bool(use_graphs) and torch.device(rt.device).type == "cuda"
+        self._graphs: dict[tuple[int, int], tuple] = {}
+        self._decode_meta = None
+        self._decode_logits = None
+        self.launch_counter = 0     # kernels launched by the last step (decode steps: per replay)
+
+    # ------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry], copy: bool = True) -> torch.Tensor | None:
+        """Run one step.  Returns float32 [wanted, vocab] on the device, or None when nothing is wanted.
+        With copy=False a decode step returns a view of a buffer that the next step overwrites."""
+        entries = list(entries)
+        mode = self._validate(entries)
+        if mode == "prefill":
+            return self._prefill(entries)
+        return self._decode(entries, copy)
+
+    def _validate(self, entries) -> str:
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        seen = set()
+        V = self.model.vocab
+        fresh = decode = 0
+        for e in entries:
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if not self.cache.is_live(e.slot):
+                raise StepError(f"slot {e.slot} is not in use")
+            n = len(e.tokens)
+            if n < 1:
+                raise StepError(f"slot {e.slot}: a sequence must bring at least one token")
+            have = self.cache.length(e.slot)
+            if have + n > self.cache.max_ctx:
+                raise StepError(f"slot {e.slot}: {have} + {n} tokens exceed the context of {self.cache.max_ctx}")
+            for t in e.tokens:
+                if not 0 <= int(t) < V:
+                    raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary of {V}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside its {n} tokens")
+            if have == 0:
+                fresh += 1
+            elif n == 1:
+                decode += 1
+            else:
+                raise StepError(f"slot {e.slot}: {n} tokens onto a sequence of {have}: a sequence that has "
+                                "started goes on one token at a time")
+        if fresh and decode:
+            raise StepError("the sequences of a step either all start or all go on by one token")
+        return "prefill" if fresh else "decode"
+
+    # ------------------------------------------------------------------
+    def _prefill(self, entries) -> torch.Tensor | None:
+        n_want = sum(len(e.want) for e in entries)
+        out = torch.empty((n_want, self.model.vocab), dtype=torch.float32, device=self.rt.device) if n_want else None
+        pieces, cur, cur_tok = [], [], 0
+        for e in entries:
+            if cur and cur_tok + len(e.tokens) > self.max_step_tokens:
+                pieces.append(cur)
+                cur, cur_tok = [], 0
+            cur.append(e)
+            cur_tok += len(e.tokens)
+        pieces.append(cur)
+        row0 = 0
+        for piece in pieces:
+            r = sum(len(e.want) for e in piece)
+            self._prefill_piece(piece, out[row0:row0 + r] if r else None)
+            row0 += r
+        return out
+
+    def _prefill_piece(self, entries, out) -> None:
+        n_seq = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        T = sum(lens)
+        first = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        tok_pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+        tok_seq = np.repeat(np.arange(n_seq, dtype=np.int32), lens)
+        slots = np.asarray([e.slot for e in entries], dtype=np.int32)
+        rows = np.concatenate([first[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries)]
+                              ).astype(np.int32) if out is not None else np.zeros(0, dtype=np.int32)
+        for e, n in zip(entries, lens):
+            self.cache.reserve(e.slot, n)
+        self.cache.sync()
+        host = np.concatenate([tokens, tok_pos, tok_seq, slots, np.zeros(n_seq, np.int32),
+                               np.asarray(lens, np.int32), first, rows])
+        dev = torch.from_numpy(host).to(self.rt.device)
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = dev[o:o + n]
+            o += n
+            return v
+
+        ctx = StepContext(rt=self.rt, ws=self.ws, mode="prefill", n_tok=T, n_seq=n_seq, tokens=take(T),
+                          tok_pos=take(T), tok_seq=take(T), seq_slot=take(n_seq), seq_start=take(n_seq),
+                          seq_end=take(n_seq), seq_first_row=take(n_seq), len_bound=max(lens))
+        rows_dev = take(len(rows))
+        h = self.model.forward(ctx, self.cache)
+        if out is not None:
+            self.model.logits(ctx, h, rows_dev, len(rows), out)
+        for e, n in zip(entries, lens):
+            self.cache.advance(e.slot, n)
+
+    # ------------------------------------------------------------------
+    def _decode(self, entries, copy: bool) -> torch.Tensor | None:
+        n_seq = len(entries)
+        B = _bucket_batch(n_seq)
+        pos = [self.cache.length(e.slot) for e in entries]
+        for e, p in zip(entries, pos):
+            self.cache.reserve(e.slot, p + 1)
+        self.cache.sync()
+        bound = _bucket_len(max(pos) + 1)
+        graphs = self.use_graphs and B <= self.MAX_GRAPH_BATCH
+        if self._decode_meta is None:
+            self._decode_meta = torch.zeros((7, self.MAX_GRAPH_BATCH), dtype=torch.int32, device=self.rt.device)
+        if self._decode_logits is None or self._decode_logits.shape[0] < B:
+            self._graphs.clear()        # graphs hold the address of the old buffer
+            rows = max(B, 8)
+            self._decode_logits = torch.empty((rows, self.model.vocab), dtype=torch.float32, device=self.rt.device)
+        host = np.zeros((7, self.MAX_GRAPH_BATCH if graphs else max(B, 1)), dtype=np.int32)
+        host[0, :n_seq] = [int(e.tokens[0]) for e in entries]
+        host[1, :n_seq] = pos
+        host[2, :B] = np.arange(B)
+        host[3, :] = -1
+        host[3, :n_seq] = [e.slot for e in entries]
+        host[4, :n_seq] = pos
+        host[5, :B] = 1
+        host[5, :n_seq] = np.asarray(pos) + 1
+        host[6, :B] = np.arange(B)
+        if graphs:
+            meta = self._decode_meta
+            meta.copy_(torch.from_numpy(host))
+        else:
+            meta = torch.from_numpy(host).to(self.rt.device)
+        ctx = StepContext(rt=self.rt, ws=self.ws, mode="decode", n_tok=B, n_seq=B, tokens=meta[0, :B],
+                          tok_pos=meta[1, :B], tok_seq=meta[2, :B], seq_slot=meta[3, :B], seq_start=meta[4, :B],
+                          seq_end=meta[5, :B], seq_first_row=meta[6, :B], len_bound=bound)
+        logits = self._decode_logits[:B]
+        key = (B, bound)
+        if graphs and key in self._graphs:
+            self._graphs[key].replay()
+        else:
+            self._decode_body(ctx, logits)
+            if graphs:
+                self._graphs[key] = self._capture(ctx, logits)
+        for e, p in zip(entries, pos):
+            self.cache.advance(e.slot, p + 1)
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if not wanted:
+            return None
+        if len(wanted) == n_seq:
+            res = logits[:n_seq]
+        else:
+            res = logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.rt.device))
+            copy = False
+        return res.clone() if copy else res
+
+    def _decode_body(self, ctx: StepContext, logits: torch.Tensor) -> None:
+        h = self.model.forward(ctx, self.cache)
+        self.model.logits(ctx, h, None, ctx.n_tok, logits)
+
+    def _capture(self, ctx: StepContext, logits: torch.Tensor):
+        """Record the decode step that has just run once (all its buffers exist) into a graph."""
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        self.ws.begin_capture()
+        try:
+            with torch.cuda.graph(g):
+                self._decode_body(ctx, logits)
+        finally:
+            self.ws.end_capture()
+        return g

@@ -1,0 +1,339 @@
+"""The hand-written sm_100a kernels as Python functions over torch tensors.
+
+Each function checks on the host what the kernel relies on (device, dtype,
+contiguity, shapes, alignment), then passes raw pointers and the current CUDA
+stream to the C entry point.  There is no other implementation behind these
+names: without a CUDA device, nvcc or the compiled library they raise.
+
+`linear_bf16` is the one place where a library matrix product stands (cuBLAS
+through torch, for more than 64 rows), as the reference's engine uses a library
+for its products (`engine/backend.go:265-267`, `mlxc/mlxc.go:655`).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from ..csrc import build
+
+PAGE = 64                      # tokens per cache page (JANIS_PAGE in the CUDA sources)
+GEMV_MAX_ROWS = 64
+EPI_NONE, EPI_GATED_GELU, EPI_SOFTCAP, EPI_GATED_SILU = 0, 1, 2, 3
+GATE_GROUP = 8                 # fused gate/up rows alternate in groups of 8
+ACT_GELU_TANH, ACT_SILU = 0, 1
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or failed to launch."""
+
+
+def _need_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("janis_b200 runs on a CUDA device only: torch.cuda.is_available() is False "
+                          "and there is no CPU implementation")
+
+
+_core = None
+_attn: dict[int, ctypes.CDLL] = {}
+
+
+def core():
+    global _core
+    if _core is None:
+        _need_cuda()
+        lib = build.core_library()
+        P, I, F = c_void_p, c_int, c_float
+        lib.janis_embed.argtypes = [P, P, I, P, I, I, I, F, P]
+        lib.janis_rmsnorm.argtypes = [P, I, P, P, P, I, I, I, F, P]
+        lib.janis_add_rmsnorm.argtypes = [P, P, I, I, c_longlong, P, F, P, F, P, I, I, I, P]
+        lib.janis_gated_act.argtypes = [P, P, I, I, I, I, I, P]
+        lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
+        lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
+        lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, P]
+        lib.janis_argmax.argtypes = [P, P, I, I, P]
+        lib.janis_sample.argtypes = [P, P, P, I, I, F, F, c_ulonglong, P, P, P]
+        lib.janis_repeat_penalty.argtypes = [P, P, I, I, I, F, P]
+        lib.janis_mask_tokens.argtypes = [P, P, I, I, I, P]
+        _core = lib
+    return _core
+
+
+def attention_lib(head_dim: int):
+    lib = _attn.get(head_dim)
+    if lib is None:
+        _need_cuda()
+        lib = build.attention_library(head_dim)
+        P, I, F = c_void_p, c_int, c_float
+        lib.janis_attn_head_dim.restype = I
+        lib.janis_attn_decode_scratch.argtypes = [I, I, I]
+        lib.janis_attn_decode_scratch.restype = c_longlong
+        lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P]
+        lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
+        if lib.janis_attn_head_dim() != head_dim:
+            raise KernelError(f"attention library for head size {head_dim} reports {lib.janis_attn_head_dim()}")
+        _attn[head_dim] = lib
+    return lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(lib, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib.janis_last_error().decode("utf-8", "replace"))
+
+
+def _t(x: torch.Tensor, name: str, dtype=None, shape=None) -> int:
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor")
+    if not x.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous")
+    if dtype is not None:
+        ok = x.dtype in dtype if isinstance(dtype, (tuple, list)) else x.dtype == dtype
+        if not ok:
+            raise KernelError(f"{name}: dtype {x.dtype} not accepted here (wanted {dtype})")
+    if shape is not None:
+        if x.dim() != len(shape) or any(s is not None and s != d for s, d in zip(shape, x.shape)):
+            raise KernelError(f"{name}: shape {tuple(x.shape)} does not match {tuple(shape)}")
+    return x.data_ptr()
+
+
+_FLOATS = (torch.float32, torch.bfloat16)
+
+# ---------------------------------------------------------------------------
+# rows of the residual stream
+# ---------------------------------------------------------------------------
+
+def embed(tokens, table, scale: float, out):
+    """out[t] = float(table[tokens[t]]) * scale;  tokens int32 [T], table [V, H], out float32 [T, H]."""
+    T = tokens.numel()
+    V, H = table.shape
+    lib = core()
+    _check(lib, lib.janis_embed(_t(tokens, "tokens", torch.int32), _t(table, "table", _FLOATS), _DT[table.dtype],
+                                _t(out, "out", torch.float32, (T, H)), T, H, V, float(scale), _stream()))
+    return out
+
+
+def rmsnorm(x, weight, eps: float, out, rows=None):
+    """out[r] = x[rows[r] or r] / sqrt(mean(x^2) + eps) * weight;  weight float32 holds offset + w."""
+    H = x.shape[-1]
+    R = out.shape[0]
+    if rows is None and x.shape[0] != R:
+        raise KernelError(f"rmsnorm: {x.shape[0]} input rows for {R} output rows")
+    lib = core()
+    _check(lib, lib.janis_rmsnorm(_t(x, "x", _FLOATS, (None, H)), _DT[x.dtype], _t(weight, "weight", torch.float32, (H,)),
+                                  _t(rows, "rows", torch.int32, (R,)) if rows is not None else None,
+                                  _t(out, "out", _FLOATS, (R, H)), _DT[out.dtype], R, H, float(eps), _stream()))
+    return out
+
+
+def add_rmsnorm(h, res, w_post, eps_post, w_next=None, eps_next=0.0, out=None, n_part=1):
+    """h += norm(res; w_post) in place (float32 residual sum; h += res when w_post is None);
+    out = norm(h; w_next) when w_next is given.
+    `res` is [R, H], or [n_part, R, H] partial results that are added first."""
+    R, H = h.shape
+    if n_part == 1:
+        _t(res, "res", _FLOATS, (R, H))
+        stride = 0
+    else:
+        _t(res, "res", _FLOATS, (n_part, R, H))
+        stride = R * H
+    lib = core()
+    _check(lib, lib.janis_add_rmsnorm(
+        _t(h, "h", torch.float32, (R, H)), res.data_ptr(), _DT[res.dtype], n_part, stride,
+        _t(w_post, "w_post", torch.float32, (H,)) if w_post is not None else None, float(eps_post),
+        _t(w_next, "w_next", torch.float32, (H,)) if w_next is not None else None, float(eps_next),
+        _t(out, "out", _FLOATS, (R, H)) if out is not None else None,
+        _DT[out.dtype] if out is not None else 0, R, H, _stream()))
+    return out
+
+
+def gated_act(gu, out, act: int = ACT_GELU_TANH, group: int = GATE_GROUP):
+    """out[r, j] = act(gate) * up over a fused [R, 2I] product whose columns alternate
+    `group` gate columns and `group` up columns."""
+    R, I2 = gu.shape
+    I = I2 // 2
+    lib = core()
+    _check(lib, lib.janis_gated_act(_t(gu, "gu", _FLOATS, (R, 2 * I)), _t(out, "out", gu.dtype, (R, I)),
+                                    _DT[gu.dtype], R, I, group, act, _stream()))
+    return out
+
+
+def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot: int, nq: int, nkv: int, hd: int,
+               kpool=None, vpool=None, page_table=None, ring_len: int = 0, store: bool = True):
+    """Rotate q and k of qkv [T, heads, hd] (heads = q, then k, then v) in place and write k and v into
+    the paged cache.
+
+    kpool/vpool: [pages, nkv, PAGE, hd] of one cache line; page_table int32 [slots, pages per sequence].
+    With store=False the rows hold q alone and only q is rotated (a layer that reads another layer's
+    keys)."""
+    T = qkv.shape[0]
+    row_heads = nq + 2 * nkv if store else nq
+    _t(qkv, "qkv", _FLOATS, (T, row_heads, hd))
+    _t(tok_pos, "tok_pos", torch.int32)
+    _t(tok_seq, "tok_seq", torch.int32)
+    if tok_pos.numel() < T or tok_seq.numel() < T:
+        raise KernelError("rope_store: position tables shorter than the step")
+    _t(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    stride = 0
+    if store:
+        n_pages = kpool.shape[0]
+        _t(kpool, "kpool", qkv.dtype, (n_pages, nkv, PAGE, hd))
+        _t(vpool, "vpool", qkv.dtype, (n_pages, nkv, PAGE, hd))
+        _t(page_table, "page_table", torch.int32, (None, None))
+        _t(seq_slot, "seq_slot", torch.int32)
+        _t(seq_end, "seq_end", torch.int32)
+        stride = page_table.shape[1]
+    lib = core()
+    _check(lib, lib.janis_rope_store(
+        qkv.data_ptr(), _DT[qkv.dtype], tok_pos.data_ptr(), tok_seq.data_ptr(),
+        seq_slot.data_ptr() if store else None, seq_end.data_ptr() if store else None,
+        inv_freq.data_ptr(), rot, T, nq, nkv, hd, row_heads,
+        kpool.data_ptr() if store else None, vpool.data_ptr() if store else None,
+        page_table.data_ptr() if store else None, stride, ring_len, 0 if store else 1, _stream()))
+    return qkv
+
+
+# ---------------------------------------------------------------------------
+# products
+# ---------------------------------------------------------------------------
+
+def gemm_f32(x, w, out, cap: float = 0.0):
+    """out[M, N] = x[M, K] w[N, K]^T in true float32 (CUDA cores); optional cap * tanh(v / cap)."""
+    M, K = x.shape
+    N = w.shape[0]
+    lib = core()
+    _check(lib, lib.janis_gemm_f32(_t(x, "x", torch.float32, (M, K)), _t(w, "w", torch.float32, (N, K)),
+                                   _t(out, "out", torch.float32, (M, N)), M, N, K, float(cap), _stream()))
+    return out
+
+
+def gemv_bf16(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0):
+    """out = x[M<=64, K] w[N, K]^T, bfloat16 operands, float accumulation; out bfloat16 or float32
+    [M, N], or [M, N/2] with a gated epilogue (rows of w alternate 8 gate rows and 8 up rows)."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if epilogue in (EPI_GATED_GELU, EPI_GATED_SILU) else N
+    lib = core()
+    _check(lib, lib.janis_gemv_bf16(_t(x, "x", torch.bfloat16, (M, K)), _t(w, "w", torch.bfloat16, (N, K)),
+                                    _t(out, "out", _FLOATS, (M, n_out)), _DT[out.dtype], M, N, K, epilogue,
+                                    float(cap), _stream()))
+    return out
+
+
+def linear_bf16(x, w, out):
+    """out[M, N] = x w^T in bfloat16 with float accumulation: the skinny kernel up to 64 rows,
+    the library product (cuBLAS) above."""
+    M = x.shape[0]
+    if M <= GEMV_MAX_ROWS:
+        return gemv_bf16(x, w, out)
+    _t(x, "x", torch.bfloat16)
+    _t(w, "w", torch.bfloat16)
+    _t(out, "out", torch.bfloat16, (M, w.shape[0]))
+    torch.mm(x, w.t(), out=out)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------
+
+def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, hd: int, scale: float, cap: float,
+                 window: int, kv_src=None, kv_row_heads=None, kv_k_head0=None):
+    """Causal (and windowed when window > 0) attention over packed sequences that start at position 0.
+    qkv: [T, nq + 2 nkv, hd], or [T, nq, hd] when keys and values come from `kv_src`, another layer's
+    [T, kv_row_heads, hd] rows whose key heads start at head kv_k_head0 (values nkv heads later)."""
+    T = qkv.shape[0]
+    if kv_src is None:
+        _t(qkv, "qkv", _FLOATS, (T, nq + 2 * nkv, hd))
+        kv_src, kv_row_heads, kv_k_head0 = qkv, nq + 2 * nkv, nq
+    else:
+        _t(qkv, "qkv", _FLOATS, (T, None, hd))
+        if qkv.shape[1] < nq:
+            raise KernelError("attn_prefill: query rows hold fewer heads than nq")
+    q_row_heads = qkv.shape[1]
+    _t(kv_src, "kv_src", qkv.dtype, (T, kv_row_heads, hd))
+    if kv_k_head0 + 2 * nkv > kv_row_heads:
+        raise KernelError("attn_prefill: key/value heads lie outside the rows of kv_src")
+    _t(out, "out", qkv.dtype, (T, nq * hd))
+    lib = attention_lib(hd)
+    _check(lib, lib.janis_attn_prefill(qkv.data_ptr(), kv_src.data_ptr(), _DT[qkv.dtype],
+                                       _t(tok_pos, "tok_pos", torch.int32), _t(tok_seq, "tok_seq", torch.int32),
+                                       _t(seq_first_row, "seq_first_row", torch.int32), out.data_ptr(), T, nq, nkv,
+                                       q_row_heads, kv_row_heads, kv_k_head0, float(scale), float(cap),
+                                       int(window), _stream()))
+    return out
+
+
+def attn_decode_scratch_floats(n_seq: int, nq: int, hd: int, max_chunks: int) -> int:
+    return n_seq * nq * max_chunks * (hd + 2)
+
+
+def attn_decode(qkv, kpool, vpool, page_table, seq_slot, seq_len, scratch, out, nq: int, nkv: int, hd: int,
+                scale: float, cap: float, window: int, ring_len: int, chunk: int, max_chunks: int):
+    """One query per sequence over the paged cache.  qkv: [n_seq, heads >= nq, hd] with q first;
+    seq_len counts the new token; scratch is float32."""
+    n_seq = qkv.shape[0]
+    _t(qkv, "qkv", _FLOATS, (n_seq, None, hd))
+    if qkv.shape[1] < nq:
+        raise KernelError("attn_decode: query rows hold fewer heads than nq")
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", qkv.dtype, (n_pages, nkv, PAGE, hd))
+    _t(vpool, "vpool", qkv.dtype, (n_pages, nkv, PAGE, hd))
+    _t(page_table, "page_table", torch.int32, (None, None))
+    _t(scratch, "scratch", torch.float32)
+    _t(out, "out", qkv.dtype, (n_seq, nq * hd))
+    if seq_slot.numel() < n_seq or seq_len.numel() < n_seq:
+        raise KernelError("attn_decode: sequence tables shorter than the batch")
+    lib = attention_lib(hd)
+    _check(lib, lib.janis_attn_decode(qkv.data_ptr(), kpool.data_ptr(), vpool.data_ptr(), _DT[qkv.dtype],
+                                      page_table.data_ptr(), page_table.shape[1],
+                                      _t(seq_slot, "seq_slot", torch.int32), _t(seq_len, "seq_len", torch.int32),
+                                      scratch.data_ptr(), scratch.numel(), out.data_ptr(), n_seq, nq, nkv,
+                                      qkv.shape[1], float(scale), float(cap), int(window), int(ring_len),
+                                      int(chunk), int(max_chunks), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------
+
+def argmax(logits, out):
+    R, V = logits.shape
+    lib = core()
+    _check(lib, lib.janis_argmax(_t(logits, "logits", torch.float32), _t(out, "out", torch.int32, (R,)), R, V,
+                                 _stream()))
+    return out
+
+
+def sample(logits, out, temp: float, top_p: float, seed: int, request_ids, token_index, u_out=None):
+    R, V = logits.shape
+    lib = core()
+    _check(lib, lib.janis_sample(_t(logits, "logits", torch.float32), _t(out, "out", torch.int32, (R,)),
+                                 _t(u_out, "u_out", torch.float32, (R,)) if u_out is not None else None, R, V,
+                                 float(temp), float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF,
+                                 _t(request_ids, "request_ids", torch.int32, (R,)),
+                                 _t(token_index, "token_index", torch.int32, (R,)), _stream()))
+    return out
+
+
+def repeat_penalty(logits, recent, penalty: float):
+    R, V = logits.shape
+    lib = core()
+    _check(lib, lib.janis_repeat_penalty(_t(logits, "logits", torch.float32), _t(recent, "recent", torch.int32, (R, None)),
+                                         recent.shape[1], R, V, float(penalty), _stream()))
+    return logits
+
+
+def mask_tokens(logits, ids):
+    R, V = logits.shape
+    lib = core()
+    _check(lib, lib.janis_mask_tokens(_t(logits, "logits", torch.float32), _t(ids, "ids", torch.int32), ids.numel(),
+                                      R, V, _stream()))
+    return logits

@@ -1,0 +1,113 @@
+"""Softmax attention with grouped key/value heads, as a mixer.
+
+Order of operations, from the reference (`gemma/gemma.go:66-95`): project q, k,
+v without biases; encode positions on q and k; cache k (encoded) and v; scale
+the scores by `scale`; cap * tanh(s / cap) when a cap is set; mask; softmax;
+weighted sum of values; merge heads; output projection.  Query head h uses
+key/value head h // (heads / kv heads) (`gemma/gemma.go:79-81`,
+`cpu/cpu_attn.go:72`).  The mask is on absolute positions: key j is seen by
+query i iff j <= i and, with a window, j > i - window (the reference's mask is
+causal only and ignores the cache offset, `gemma/gemma.go:232-240`).
+
+The three projections are one product over the rows q | k | v concatenated at
+load; the names on disk stay as they are.  A prompt step reads keys and values
+from the step's own buffer (a windowed layer may see a prompt longer than its
+ring holds); a decode step reads the paged cache.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.cache import KVNeed
+from ..weights.loader import TensorSpec
+from .base import Mixer, PositionEncoding, Runtime, StepContext
+
+
+class SoftmaxAttention(Mixer):
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                 position: PositionEncoding, names: dict[str, str], softcap: float = 0.0,
+                 window: int | None = None, init_std: float = 0.02):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads do not divide over {n_kv_heads} key/value heads")
+        if head_dim % 16 or not 16 <= head_dim <= 512:
+            raise ValueError(f"the attention kernels take head sizes in steps of 16 from 16 to 512, found {head_dim}")
+        for k in ("q", "k", "v", "o"):
+            if k not in names:
+                raise ValueError(f"attention needs the checkpoint name of its {k!r} projection")
+        self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
+        self.scale = float(scale)
+        self.softcap = float(softcap or 0.0)
+        self.window = int(window) if window else 0
+        self.position = position
+        self.names = dict(names)
+        self.init_std = init_std
+        self.w_qkv = None
+        self.w_q = None
+        self.w_o = None
+
+    # -- what it loads and keeps -------------------------------------------
+    def tensor_specs(self):
+        nq, nkv, hd, H, s = self.n_heads, self.n_kv_heads, self.head_dim, self.hidden, self.init_std
+        return {self.names["q"]: TensorSpec((nq * hd, H), init_std=s),
+                self.names["k"]: TensorSpec((nkv * hd, H), init_std=s),
+                self.names["v"]: TensorSpec((nkv * hd, H), init_std=s),
+                self.names["o"]: TensorSpec((H, nq * hd), init_std=s)}
+
+    def sub_parts(self):
+        return [self.position]
+
+    def cache_needs(self):
+        return {"kv": KVNeed(self.n_kv_heads, self.head_dim, self.window or None)}
+
+    def load(self, store, rt: Runtime):
+        if rt.dtype == torch.bfloat16 and (self.hidden % 8 or (self.n_heads * self.head_dim) % 8):
+            raise ValueError("the bfloat16 products need widths that are multiples of 8 "
+                             f"(hidden {self.hidden}, heads x head size {self.n_heads * self.head_dim})")
+        q, k, v = (store.get(self.names[n], rt.dtype) for n in ("q", "k", "v"))
+        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+        self.w_q = self.w_qkv[: self.n_heads * self.head_dim]      # a layer that only reads keys projects q alone
+        self.w_o = store.get(self.names["o"], rt.dtype).contiguous()
+        self.position.load(store, rt)
+
+    # -- a step ------------------------------------------------------------
+    def _decode_geometry(self, ctx: StepContext, sm_count: int):
+        bound = max(ctx.len_bound, 1)
+        span = min(bound, self.window) if self.window else bound
+        chunk = 64
+        while chunk < 1024 and ctx.n_seq * self.n_kv_heads * ((span + 2 * chunk - 1) // (2 * chunk)) >= 2 * sm_count:
+            chunk *= 2
+        max_chunks = (bound + chunk - 1) // chunk
+        if self.window:
+            max_chunks = min(max_chunks, (self.window + chunk - 1) // chunk + 1)
+        return chunk, max_chunks
+
+    def forward(self, x, ctx: StepContext, line):
+        rt, ws, ops = ctx.rt, ctx.ws, ctx.rt.ops
+        T, nq, nkv, hd = ctx.n_tok, self.n_heads, self.n_kv_heads, self.head_dim
+        kv = line["kv"]
+        own = kv.write
+        heads = nq + 2 * nkv if own else nq
+        # a written line that later layers read keeps its step buffer until the step ends
+        name = f"attn.qkv.line{line.index}" if (own and line.has_readers and ctx.mode == "prefill") else "attn.qkv"
+        qkv = ws.buf(name, (T, heads, hd), rt.dtype)
+        rt.linear(x, self.w_qkv if own else self.w_q, qkv.view(T, heads * hd))
+        self.position.encode_and_store(qkv, ctx, nq, nkv, hd, kv)
+        att = ws.buf("attn.ctx", (T, nq * hd), rt.dtype)
+        if ctx.mode == "prefill":
+            if own:
+                if line.has_readers:
+                    ctx.shared[("kv", line.index)] = (qkv, heads, nq)
+                ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
+                                 self.softcap, self.window)
+            else:
+                src, src_heads, k0 = ctx.shared[("kv", line.index)]
+                ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
+                                 self.softcap, self.window, kv_src=src, kv_row_heads=src_heads, kv_k_head0=k0)
+        else:
+            chunk, max_chunks = self._decode_geometry(ctx, rt.sm_count)
+            scratch = ws.buf("attn.partial", (ops.attn_decode_scratch_floats(ctx.n_seq, nq, hd, max_chunks),),
+                             torch.float32)
+            ops.attn_decode(qkv, kv.k, kv.v, kv.table, ctx.seq_slot, ctx.seq_end, scratch, att, nq, nkv, hd,
+                            self.scale, self.softcap, self.window, kv.ring_len, chunk, max_chunks)
+        out = ws.buf("mixer.out", (T, self.hidden), rt.dtype)
+        return rt.linear(att, self.w_o, out)

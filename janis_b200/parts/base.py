@@ -1,0 +1,188 @@
+"""What every part of a layer is, and what a step hands to it.
+
+A model is put together from parts: an embedding, blocks (each an arrangement
+of a mixer, a feed-forward and norms), a final norm and an output head.  A part
+gets its sizes and constants as constructor arguments and the checkpoint names
+of its tensors as a mapping; it never asks which model it is in.
+
+Interfaces (all tensors are on the device; T = tokens of this step, packed
+sequence after sequence without padding):
+
+* `Part.tensor_specs()` -> {checkpoint name: TensorSpec}: what it loads.
+* `Part.load(store, rt)`: take its tensors from the store (`store.get(name,
+  dtype)`), fuse or widen them as its kernels want.
+* `Norm.forward(x, ctx, out, rows=None)`; `Norm.residual_add(h, r, ctx,
+  next_norm=None, out=None)`: h += norm(r) on the float32 residual stream, and
+  out = next_norm(h) when asked.
+* `PositionEncoding.encode_and_store(qkv, ctx, nq, nkv, hd, kv_line)`: encode
+  queries and keys in place and write keys and values into the cache line.
+* `Mixer.cache_needs()` -> {name: KVNeed | StateNeed}; `Mixer.forward(x, ctx,
+  line)` -> [T, hidden] in the activation dtype.  `line[name]` is the cache part
+  it asked for; `line.write` is False when the schedule lets it only read.
+* `FeedForward.forward(x, ctx)` -> [T, hidden].
+* `Block.forward(h, ctx, line, y_in=None, next_norm=None)` -> (h, y_next): h is the
+  float32 residual stream, updated in place; y_in is this block's first norm
+  already applied (by the block before), y_next is `next_norm` applied to the
+  result, so that a norm can be fused across the border of two blocks.
+
+The reference writes each model against its tensor-op interface
+(`engine/backend.go:142-287`) with a struct per layer kind holding its constants
+(`gemma/gemma.go:31-35`, `:98-100`, `:127-131`); the split into exchangeable
+parts chosen layer by layer is this library's.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Mapping
+
+import torch
+
+from ..weights.loader import TensorSpec
+
+
+class Runtime:
+    """The compute dtype, the device and the kernels a model runs with."""
+
+    def __init__(self, dtype: torch.dtype, device, ops):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, found {dtype}")
+        self.dtype = dtype
+        self.device = device
+        self.ops = ops
+        dev = torch.device(device)
+        self.sm_count = (torch.cuda.get_device_properties(dev).multi_processor_count
+                         if dev.type == "cuda" else 1)
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out = x w^T in the compute dtype, accumulated in float32."""
+        if self.dtype == torch.float32:
+            return self.ops.gemm_f32(x, w, out)
+        return self.ops.linear_bf16(x, w, out)
+
+
+class Workspace:
+    """Named device buffers that live across steps (nothing is allocated in a
+    steady state, which stream capture needs).  `buf` returns a view of the
+    first rows; a buffer grows when a larger one is asked for."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: dict[str, torch.Tensor] = {}
+        self.frozen = False
+        self._in_graph: set[str] = set()          # names whose current buffer a CUDA graph has recorded
+        self._retired: list[torch.Tensor] = []    # outgrown buffers that a graph still writes to
+
+    def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        cur = self._bufs.get(name)
+        if cur is None or cur.dtype != dtype or cur.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow during stream capture")
+            if cur is not None and name in self._in_graph:
+                self._retired.append(cur)         # keep its memory valid for the graphs that recorded it
+                self._in_graph.discard(name)
+            cur = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = cur
+        if self.frozen:
+            self._in_graph.add(name)
+        return cur[:n].view(*shape)
+
+    def begin_capture(self) -> None:
+        self.frozen = True
+
+    def end_capture(self) -> None:
+        self.frozen = False
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+@dataclass
+class StepContext:
+    """One step's batch as the parts see it."""
+    rt: Runtime
+    ws: Workspace
+    mode: str                       # "prefill": sequences start at 0; "decode": one token each
+    n_tok: int
+    n_seq: int
+    tokens: torch.Tensor            # int32 [T]
+    tok_pos: torch.Tensor           # int32 [T] absolute position of each token
+    tok_seq: torch.Tensor           # int32 [T] index of its sequence in this step
+    seq_slot: torch.Tensor          # int32 [n_seq] cache slot, < 0 for padding
+    seq_start: torch.Tensor         # int32 [n_seq] tokens cached before the step
+    seq_end: torch.Tensor           # int32 [n_seq] tokens cached after the step
+    seq_first_row: torch.Tensor     # int32 [n_seq] row of the sequence's position 0 in the packed step
+    len_bound: int = 0              # host-side bound on max(seq_end); sizes the decode grids
+    shared: dict = field(default_factory=dict)   # scratch that parts of one step hand to each other
+
+
+class Part:
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {}
+
+    def load(self, store, rt: Runtime) -> None:
+        pass
+
+    def sub_parts(self) -> list["Part"]:
+        return []
+
+
+class Norm(Part):
+    def forward(self, x, ctx: StepContext, out, rows=None):
+        raise NotImplementedError
+
+    def residual_add(self, h, r, ctx: StepContext, next_norm: "Norm | None" = None, out=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def encode_and_store(self, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, kv_line):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_needs(self) -> Mapping[str, Any]:
+        return {}
+
+    def forward(self, x, ctx: StepContext, line):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx: StepContext):
+        raise NotImplementedError
+
+
+class Block(Part):
+    first_norm: Norm | None = None
+    mixer: Mixer
+
+    def forward(self, h, ctx: StepContext, line, y_in=None, next_norm: Norm | None = None):
+        raise NotImplementedError
+
+
+class WeightStore:
+    """Loaded tensors by checkpoint name, with conversions cached so that parts
+    that share a tensor (a tied head) share its converted copy too."""
+
+    def __init__(self, tensors: Mapping[str, torch.Tensor]):
+        self._raw = dict(tensors)
+        self._conv: dict[tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def get(self, name: str, dtype: torch.dtype | None = None) -> torch.Tensor:
+        t = self._raw[name]
+        if dtype is None or t.dtype == dtype:
+            return t
+        key = (name, dtype)
+        if key not in self._conv:
+            self._conv[key] = t.to(dtype)
+        return self._conv[key]
+
+    def drop(self, name: str) -> None:
+        """Forget the stored form of a tensor whose user keeps a fused or converted copy."""
+        self._raw.pop(name, None)
+
+    def names(self):
+        return list(self._raw)

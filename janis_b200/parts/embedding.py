@@ -1,0 +1,62 @@
+"""Token embedding into the float32 residual stream, and the output head.
+
+Gemma2 scales the embedding by sqrt(hidden), a float32 constant
+(`gemma/gemma.go:193`, `:197`), ties the head to the embedding table
+(`gemma/gemma.go:210`, `qwen/embed.go:87-89`) and caps the logits with
+fc * tanh(logits / fc) (`gemma/gemma.go:211-212`).  Logits are float32.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .base import Part, Runtime, StepContext
+
+
+class Embedding(Part):
+    def __init__(self, vocab: int, hidden: int, table_name: str, scale: float = 1.0, init_std: float = 0.02):
+        self.vocab, self.hidden = vocab, hidden
+        self.table_name = table_name
+        self.scale = float(scale)
+        self.init_std = init_std
+        self.table = None
+
+    def tensor_specs(self):
+        return {self.table_name: TensorSpec((self.vocab, self.hidden), init_std=self.init_std)}
+
+    def load(self, store, rt: Runtime):
+        self.table = store.get(self.table_name, rt.dtype).contiguous()
+
+    def forward(self, tokens, ctx: StepContext, out):
+        return ctx.rt.ops.embed(tokens, self.table, self.scale, out)
+
+
+class LMHead(Part):
+    """logits = y W^T, then the cap.  `table_name` may be the embedding's (a tied head)."""
+
+    def __init__(self, vocab: int, hidden: int, table_name: str, softcap: float = 0.0, init_std: float = 0.02):
+        self.vocab, self.hidden = vocab, hidden
+        self.table_name = table_name
+        self.softcap = float(softcap or 0.0)
+        self.init_std = init_std
+        self.table = None
+
+    def tensor_specs(self):
+        return {self.table_name: TensorSpec((self.vocab, self.hidden), init_std=self.init_std)}
+
+    def load(self, store, rt: Runtime):
+        if rt.dtype == torch.bfloat16 and self.hidden % 8:
+            raise ValueError(f"the bfloat16 products need a hidden width that is a multiple of 8, found {self.hidden}")
+        self.table = store.get(self.table_name, rt.dtype).contiguous()
+
+    def forward(self, y, ctx: StepContext, out):
+        """y [R, hidden] in the compute dtype -> out float32 [R, vocab]."""
+        ops = ctx.rt.ops
+        R = y.shape[0]
+        if ctx.rt.dtype == torch.float32:
+            return ops.gemm_f32(y, self.table, out, self.softcap)
+        step = ops.GEMV_MAX_ROWS
+        for r0 in range(0, R, step):
+            r1 = min(R, r0 + step)
+            ops.gemv_bf16(y[r0:r1], self.table, out[r0:r1], ops.EPI_SOFTCAP, self.softcap)
+        return out
