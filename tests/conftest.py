@@ -1,8 +1,12 @@
 """Shared fixtures: the two tiny Gemma2 configurations and model folders of random weights.
 
 The configurations differ in every size and option (heads and groups, widths that
-are no power of two, layers, vocabulary, eps, window, caps, rotary base).  Model
-folders are written into pytest's temporary directory.
+are no power of two, layers, vocabulary, eps, window, caps, rotary base).  Each
+comes with plain random weights (matrices N(0, 0.02), norms N(0, 0.1)) and as a
+"hot" variant whose query/key projections and embedding are scaled up, so that
+attention scores reach the score cap and logits reach the final cap: with the
+plain weights both caps are far away and a fault in them would not show.
+Model folders are written into pytest's temporary directory.
 """
 from __future__ import annotations
 
@@ -30,6 +34,12 @@ TINY_B = dict(
 
 TINY = {"A": TINY_A, "B": TINY_B}
 
+HOT_QK, HOT_EMBED = 20.0, 40.0
+
+# whole-model tolerances, as fractions of the largest reference logit of the comparison
+F32_MODEL_TOL = 1e-4
+BF16_MODEL_TOL = 2e-2
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
@@ -44,20 +54,58 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+def write_tiny(model_dir: str, raw_config: dict, seed: int, hot: bool = False, norms_f32: bool = False) -> None:
+    """A model folder of seeded random weights; `hot` scales q/k projections and the embedding."""
+    from janis_b200 import build_model
+    from janis_b200.weights.loader import random_tensors, write_model_folder
+    _, cfg, model = build_model(raw_config)
+    tensors = random_tensors(model.tensor_specs(), seed, "cpu")
+    for name in list(tensors):
+        t = tensors[name]
+        if hot and (name.endswith("q_proj.weight") or name.endswith("k_proj.weight")):
+            tensors[name] = (t.float() * HOT_QK).to(torch.bfloat16)
+        elif hot and name == "model.embed_tokens.weight":
+            tensors[name] = (t.float() * HOT_EMBED).to(torch.bfloat16)
+        elif norms_f32 and name.endswith("norm.weight"):
+            tensors[name] = t.float()
+    write_model_folder(model_dir, cfg.to_dict(), tensors, {"seed": str(seed)})
+
+
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
-    """{'A': folder, 'B': folder} with config.json and model.safetensors (bfloat16, seeds 11 and 12)."""
-    import janis_b200
+    """{'A', 'B', 'A_hot', 'B_hot'} -> folder with config.json and model.safetensors."""
     out = {}
-    for i, (name, cfg) in enumerate(TINY.items()):
-        d = tmp_path_factory.mktemp(f"tiny_{name}")
-        janis_b200.write_random_model(str(d), cfg, seed=11 + i)
-        out[name] = str(d)
+    seed = 11
+    for name, cfg in TINY.items():
+        for hot in (False, True):
+            key = name + ("_hot" if hot else "")
+            d = tmp_path_factory.mktemp(f"tiny_{key}")
+            write_tiny(str(d), cfg, seed, hot=hot, norms_f32=(name == "B"))
+            out[key] = str(d)
+            seed += 1
     return out
 
 
 @pytest.fixture(scope="session")
 def plain_models(model_dirs):
-    """{'A': (config dict, weights), ...} as the plain implementation reads them."""
+    """Each folder as the plain implementation reads it: key -> (config dict, weights)."""
     from tests.plain import gemma2_plain as P
     return {k: P.load_folder(d) for k, d in model_dirs.items()}
+
+
+_plain_cache: dict = {}
+
+
+def plain_logits(plain_models, key: str, tokens) -> torch.Tensor:
+    """float64 logits [len, vocab] of the plain implementation, remembered per (model, tokens)."""
+    from tests.plain import gemma2_plain as P
+    k = (key, tuple(tokens))
+    if k not in _plain_cache:
+        cfg, w = plain_models[key]
+        _plain_cache[k] = P.forward_logits(cfg, w, list(tokens))
+    return _plain_cache[k]
+
+
+def random_tokens(vocab: int, n: int, seed: int) -> list[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()

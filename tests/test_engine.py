@@ -1,0 +1,138 @@
+"""The engine against the plain implementation: whole prompts, the last 32 tokens one
+by one, unequal batches whose shorter requests end earlier with slots used again,
+long decoding, the first tokens of a sequence.
+
+Every case runs on the GPU (`-m gpu`: the CUDA kernels, float32 and bfloat16) and,
+as a check of the host side alone, on the CPU over the plain kernel statements
+(`on="refs"`, float32, the smaller model).
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from tests.conftest import TINY, plain_logits, random_tokens
+from tests.helpers import assert_logits, make_engine, run_requests
+
+GPU = pytest.mark.gpu
+CASES = [pytest.param("cuda", "float32", marks=GPU), pytest.param("cuda", "bfloat16", marks=GPU),
+         pytest.param("refs", "float32")]
+MODELS = ["A", "B", "A_hot", "B_hot"]
+
+
+def vocab_of(key):
+    return TINY[key[0]]["vocab_size"]
+
+
+def models_for(on):
+    return MODELS if on == "cuda" else ["A_hot", "B"]
+
+
+@pytest.fixture(scope="module")
+def engines(model_dirs):
+    """Engines are expensive to open: one per (model, dtype, backend), reused; every test leaves
+    the cache empty (audited)."""
+    made = {}
+
+    def get(key, dtype, on, **kw):
+        k = (key, dtype, on, tuple(sorted(kw.items())))
+        if k not in made:
+            made[k] = make_engine(model_dirs[key], dtype, on, **kw)
+        return made[k]
+
+    yield get
+    for e in made.values():
+        e.close()
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_each_request_alone_and_whole(on, dtype, engines, plain_models):
+    for key in models_for(on):
+        eng = engines(key, dtype, on, max_tokens=1024)
+        for n, seed in ((1, 1), (5, 2), (17, 3), (64, 4), (65, 5), (140, 6)):
+            req = random_tokens(vocab_of(key), n, seed)
+            got = run_requests(eng, [req], [n])[0]
+            assert_logits(got, plain_logits(plain_models, key, req), dtype, f"{key} whole n={n}")
+        assert eng.cache.live_slots() == []
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_last_32_tokens_one_by_one(on, dtype, engines, plain_models):
+    for key in models_for(on):
+        eng = engines(key, dtype, on, max_tokens=1024)
+        for n, seed in ((33, 7), (40, 8), (96, 9), (150, 10)):
+            req = random_tokens(vocab_of(key), n, seed)
+            got = run_requests(eng, [req], [n - 32])[0]
+            assert_logits(got, plain_logits(plain_models, key, req), dtype, f"{key} last-32 n={n}")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_unequal_batches_one_after_another(on, dtype, engines, plain_models):
+    """Batches of 3 and 4 requests of unequal lengths; the shorter ones end earlier; a cache that
+    holds one batch at a time, so every slot and page is used again by a later batch."""
+    lens = [5, 11, 17, 1, 9, 23, 40, 70, 3, 131, 64, 2]
+    prompts = [3, 11, 9, 1, 2, 20, 40, 38, 1, 100, 63, 1]
+    for key in models_for(on):
+        reqs = [random_tokens(vocab_of(key), n, 20 + i) for i, n in enumerate(lens)]
+        for max_live in (3, 4):
+            eng = engines(key, dtype, on, max_tokens=5 * 64, max_batch=4)
+            got = run_requests(eng, reqs, prompts, max_live=max_live)
+            for i, (g, r) in enumerate(zip(got, reqs)):
+                assert_logits(g, plain_logits(plain_models, key, r), dtype,
+                              f"{key} batch of {max_live}, request {i} (len {lens[i]}, prompt {prompts[i]})")
+            assert eng.cache.live_slots() == []
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_long_decoding_from_a_short_prompt(on, dtype, engines, plain_models):
+    """3 prompt tokens, then 200 single-token steps: page borders, ring wrap-around (windows of 8
+    and 16 live in rings of 64), and a second request beside it that starts longer and ends sooner."""
+    for key in models_for(on):
+        reqs = [random_tokens(vocab_of(key), 203, 40), random_tokens(vocab_of(key), 90, 41)]
+        eng = engines(key, dtype, on, max_tokens=1024)
+        got = run_requests(eng, reqs, [3, 70])
+        for i, (g, r) in enumerate(zip(got, reqs)):
+            assert_logits(g, plain_logits(plain_models, key, r), dtype, f"{key} long decode, request {i}")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_first_tokens_of_a_sequence(on, dtype, engines, plain_models):
+    """A prompt of one token, then tokens 2..12 one by one, beside a request that starts with two."""
+    for key in models_for(on):
+        reqs = [random_tokens(vocab_of(key), 12, 50), random_tokens(vocab_of(key), 12, 51)]
+        eng = engines(key, dtype, on, max_tokens=256)
+        got = run_requests(eng, reqs, [1, 2])
+        for i, (g, r) in enumerate(zip(got, reqs)):
+            assert_logits(g, plain_logits(plain_models, key, r), dtype, f"{key} first tokens, request {i}")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_padding_and_company_change_nothing(on, dtype, engines, plain_models):
+    """The same request alone, in a batch of 2, and in a batch of 9 (padded to 16 rows on the GPU):
+    the same logits beyond rounding; in float32 the decode rows are bit-equal."""
+    key = "B_hot" if on == "cuda" else "B"
+    eng = engines(key, dtype, on, max_tokens=2048)
+    req = random_tokens(vocab_of(key), 40, 60)
+    others = [random_tokens(vocab_of(key), 10 + 3 * i, 61 + i) for i in range(8)]
+    alone = run_requests(eng, [req], [20])[0]
+    pair = run_requests(eng, [req, others[0]], [20, 5])[0]
+    nine = run_requests(eng, [req] + others, [20] + [4] * 8)[0]
+    ref = plain_logits(plain_models, key, req)
+    for name, g in (("alone", alone), ("pair", pair), ("nine", nine)):
+        assert_logits(g, ref, dtype, f"{key} {name}")
+    if dtype == "float32":
+        assert torch.equal(alone[20:], pair[20:]) and torch.equal(alone[20:], nine[20:])
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graphs_and_plain_launches_agree(dtype, model_dirs, plain_models):
+    key = "A_hot"
+    reqs = [random_tokens(vocab_of(key), n, 70 + n) for n in (30, 75, 12)]
+    outs = []
+    for graphs in (True, False):
+        eng = make_engine(model_dirs[key], dtype, "cuda", max_tokens=1024, use_graphs=graphs)
+        outs.append(run_requests(eng, reqs, [10, 70, 1]))
+        eng.close()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)

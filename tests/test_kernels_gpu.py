@@ -1,0 +1,402 @@
+"""Each CUDA kernel alone against its plain statement in tests/kernel_refs.py,
+at sizes other than the engine's tests use: widths and vocabularies that are no
+power of two, head sizes in steps of 16, odd numbers of rows, both dtypes.
+
+Tolerances: float32 paths 2e-5 of the largest reference value (accumulation
+order differs from the float64 reference); bfloat16 outputs one rounding step,
+2^-8 of the largest value, plus the same accumulation allowance.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests import kernel_refs as R
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 2e-5
+BF16_TOL = 2.0 ** -8 + 1e-4
+
+
+def ops():
+    from janis_b200.kernels import ops as o
+    return o
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def close(got, want, tol, what=""):
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    scale = max(want.abs().max().item(), 1e-30)
+    err = (got - want).abs().max().item()
+    assert err <= tol * scale, f"{what}: max err {err:.3e} > {tol:.1e} x scale {scale:.3e}"
+
+
+def tol_of(dtype):
+    return F32_TOL if dtype == torch.float32 else BF16_TOL
+
+
+def rnd(shape, dtype, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype).to(dev())
+
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,V", [(1, 64, 50), (7, 100, 333), (33, 2304, 1000)])
+def test_embed(dtype, T, H, V):
+    table = rnd((V, H), dtype, 1)
+    tokens = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2)).int().to(dev())
+    out = torch.empty((T, H), dtype=torch.float32, device=dev())
+    ops().embed(tokens, table, math.sqrt(H), out)
+    want = torch.empty((T, H), dtype=torch.float32)
+    R.embed(tokens.cpu(), table.cpu(), math.sqrt(H), want)
+    close(out, want, F32_TOL, "embed")
+
+
+@pytest.mark.parametrize("din", DTYPES)
+@pytest.mark.parametrize("dout", DTYPES)
+@pytest.mark.parametrize("Rn,H,eps", [(1, 64, 1e-6), (5, 100, 1e-5), (9, 2304, 1e-6), (3, 5000, 1e-3)])
+def test_rmsnorm(din, dout, Rn, H, eps):
+    x = rnd((Rn, H), din, 3, std=3.0)
+    w = (1.0 + rnd((H,), torch.float32, 4, std=0.1))
+    out = torch.empty((Rn, H), dtype=dout, device=dev())
+    ops().rmsnorm(x, w, eps, out)
+    want = torch.empty((Rn, H), dtype=torch.float64)
+    R.rmsnorm(x.cpu(), w.cpu(), eps, want)
+    close(out, want, tol_of(dout), "rmsnorm")
+    rows = torch.tensor([Rn - 1, 0, Rn - 1], dtype=torch.int32, device=dev())
+    out2 = torch.empty((3, H), dtype=dout, device=dev())
+    ops().rmsnorm(x, w, eps, out2, rows)
+    close(out2, want[rows.cpu().long()], tol_of(dout), "rmsnorm rows")
+
+
+@pytest.mark.parametrize("dr", DTYPES)
+@pytest.mark.parametrize("post,nxt,n_part", [(True, True, 1), (True, False, 1), (False, True, 1), (True, True, 3),
+                                             (False, False, 2)])
+@pytest.mark.parametrize("Rn,H", [(1, 96), (6, 2304), (4, 1000)])
+def test_add_rmsnorm(dr, post, nxt, n_part, Rn, H):
+    h0 = rnd((Rn, H), torch.float32, 5, std=2.0)
+    res = rnd((n_part, Rn, H) if n_part > 1 else (Rn, H), dr, 6, std=0.5)
+    wp = (1.0 + rnd((H,), torch.float32, 7, std=0.1)) if post else None
+    wn = (1.0 + rnd((H,), torch.float32, 8, std=0.1)) if nxt else None
+    h = h0.clone()
+    out = torch.empty((Rn, H), dtype=dr, device=dev()) if nxt else None
+    ops().add_rmsnorm(h, res, wp, 1e-6, wn, 1e-5, out, n_part)
+    h_ref = h0.cpu().clone()
+    out_ref = torch.empty((Rn, H), dtype=torch.float64) if nxt else None
+    R.add_rmsnorm(h_ref, res.cpu(), wp.cpu() if post else None, 1e-6, wn.cpu() if nxt else None, 1e-5, out_ref, n_part)
+    close(h, h_ref, F32_TOL, "residual sum")
+    if nxt:
+        close(out, out_ref, tol_of(dr), "next norm")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("Rn,I", [(1, 8), (5, 320), (70, 9216)])
+def test_gated_act(dtype, act, Rn, I):
+    gu = rnd((Rn, 2 * I), dtype, 9, std=2.0)
+    out = torch.empty((Rn, I), dtype=dtype, device=dev())
+    ops().gated_act(gu, out, act)
+    want = torch.empty((Rn, I), dtype=torch.float64)
+    R.gated_act(gu.cpu(), want, act)
+    close(out, want, tol_of(dtype), "gated_act")
+
+
+def _paged(n_pages, nkv, hd, dtype, seed):
+    k = rnd((n_pages, nkv, R.PAGE, hd), dtype, seed)
+    v = rnd((n_pages, nkv, R.PAGE, hd), dtype, seed + 1)
+    return k, v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,rot,ring", [(4, 2, 16, 16, 0), (6, 1, 32, 32, 64), (3, 3, 48, 24, 128),
+                                                (8, 4, 256, 256, 0), (2, 1, 64, 0, 64)])
+def test_rope_store(dtype, nq, nkv, hd, rot, ring):
+    # three sequences; the second is padding (slot -1); the third is longer than a ring of 64
+    lens = [5, 3, 150]
+    starts = [0, 0, 0]
+    slots = [2, -1, 0]
+    T = sum(lens)
+    tok_pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(3), torch.tensor(lens)).int()
+    seq_slot = torch.tensor(slots).int()
+    seq_end = torch.tensor([s + n for s, n in zip(starts, lens)]).int()
+    inv = torch.tensor([10000.0 ** (-2.0 * i / max(rot, 1)) for i in range(rot // 2)], dtype=torch.float32)
+    n_pages, width = 12, 4
+    table = torch.tensor([[7, 3, 9, 1], [0, 0, 0, 0], [5, 2, 8, 11]], dtype=torch.int32)
+    qkv = rnd((T, nq + 2 * nkv, hd), dtype, 10)
+    k, v = _paged(n_pages, nkv, hd, dtype, 11)
+    qkv_ref, k_ref, v_ref = qkv.cpu().clone(), k.cpu().clone(), v.cpu().clone()
+    d = dev()
+    ops().rope_store(qkv, tok_pos.to(d), tok_seq.to(d), seq_slot.to(d), seq_end.to(d), inv.to(d), rot, nq, nkv, hd,
+                     k, v, table.to(d), ring, True)
+    R.rope_store(qkv_ref, tok_pos, tok_seq, seq_slot, seq_end, inv, rot, nq, nkv, hd, k_ref, v_ref, table, ring, True)
+    close(qkv, qkv_ref, tol_of(dtype), "rotated q/k")
+    close(k, k_ref, tol_of(dtype), "cached k")
+    close(v, v_ref, tol_of(dtype), "cached v")
+    # query-only rows (a layer that reads another layer's keys)
+    q = rnd((T, nq, hd), dtype, 12)
+    q_ref = q.cpu().clone()
+    ops().rope_store(q, tok_pos.to(d), tok_seq.to(d), None, None, inv.to(d), rot, nq, nkv, hd, store=False)
+    R.rope_store(q_ref, tok_pos, tok_seq, None, None, inv, rot, nq, nkv, hd, store=False)
+    close(q, q_ref, tol_of(dtype), "rotated q alone")
+
+
+def test_rope_angles_at_large_positions():
+    """theta = float32(pos) * inv_freq with accurate sin/cos, also thousands of radians out."""
+    nq, nkv, hd = 1, 1, 64
+    pos = torch.tensor([0, 1, 4095, 8191, 100000], dtype=torch.int32)
+    T = len(pos)
+    inv = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float32)
+    q = rnd((T, 1, hd), torch.float32, 13)
+    want = q.cpu().clone()
+    d = dev()
+    seq = torch.zeros(T, dtype=torch.int32)
+    got = q.clone()
+    ops().rope_store(got, pos.to(d), seq.to(d), None, None, inv.to(d), hd, 1, 1, hd, store=False)
+    R.rope_store(want, pos, seq, None, None, inv, hd, 1, 1, hd, store=False)
+    close(got, want, 1e-5, "rope at large positions")
+
+
+@pytest.mark.parametrize("M,N,K,cap", [(1, 1, 1, 0.0), (3, 70, 33, 0.0), (64, 64, 16, 0.0), (65, 130, 100, 5.0),
+                                       (8, 384, 96, 15.0), (200, 96, 320, 0.0)])
+def test_gemm_f32(M, N, K, cap):
+    x = rnd((M, K), torch.float32, 14)
+    w = rnd((N, K), torch.float32, 15)
+    out = torch.empty((M, N), dtype=torch.float32, device=dev())
+    ops().gemm_f32(x, w, out, cap)
+    want = torch.empty((M, N), dtype=torch.float64)
+    R.gemm_f32(x.cpu(), w.cpu(), want, cap)
+    close(out, want, F32_TOL, "gemm_f32")
+
+
+def test_gemm_f32_row_does_not_depend_on_batch():
+    x = rnd((37, 200), torch.float32, 16)
+    w = rnd((90, 200), torch.float32, 17)
+    full = torch.empty((37, 90), dtype=torch.float32, device=dev())
+    ops().gemm_f32(x, w, full)
+    one = torch.empty((1, 90), dtype=torch.float32, device=dev())
+    ops().gemm_f32(x[20:21].contiguous(), w, one)
+    assert torch.equal(full[20:21], one)
+
+
+@pytest.mark.parametrize("dout", DTYPES)
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(16, 32), (40, 72), (384, 96), (2304, 2048), (1000, 328)])
+def test_gemv_bf16(dout, M, N, K):
+    x = rnd((M, K), torch.bfloat16, 18)
+    w = rnd((N, K), torch.bfloat16, 19, std=0.05)
+    out = torch.empty((M, N), dtype=dout, device=dev())
+    ops().gemv_bf16(x, w, out)
+    want = torch.empty((M, N), dtype=torch.float64)
+    R.gemv_bf16(x.cpu(), w.cpu(), want)
+    close(out, want, tol_of(dout) if dout == torch.bfloat16 else 1e-4, "gemv_bf16")
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 12, 40, 64])
+@pytest.mark.parametrize("epi", [1, 3])
+@pytest.mark.parametrize("I,K", [(8, 16), (320, 96), (1000, 104)])
+def test_gemv_bf16_gated(M, epi, I, K):
+    x = rnd((M, K), torch.bfloat16, 20)
+    w = rnd((2 * I, K), torch.bfloat16, 21, std=0.2)
+    out = torch.empty((M, I), dtype=torch.bfloat16, device=dev())
+    ops().gemv_bf16(x, w, out, epi)
+    want = torch.empty((M, I), dtype=torch.float64)
+    R.gemv_bf16(x.cpu(), w.cpu(), want, epi)
+    close(out, want, BF16_TOL, "gemv gated")
+
+
+@pytest.mark.parametrize("M,N,K,cap", [(1, 256, 64, 30.0), (7, 1000, 96, 2.0), (64, 50, 40, 0.0)])
+def test_gemv_bf16_softcap(M, N, K, cap):
+    x = rnd((M, K), torch.bfloat16, 22, std=2.0)
+    w = rnd((N, K), torch.bfloat16, 23)
+    out = torch.empty((M, N), dtype=torch.float32, device=dev())
+    ops().gemv_bf16(x, w, out, 2, cap)
+    want = torch.empty((M, N), dtype=torch.float64)
+    R.gemv_bf16(x.cpu(), w.cpu(), want, 2, cap)
+    close(out, want, 1e-4, "gemv softcap")
+
+
+def test_gemv_refuses_what_it_cannot_do():
+    o = ops()
+    x = rnd((2, 12), torch.bfloat16, 24)
+    w = rnd((16, 12), torch.bfloat16, 25)
+    with pytest.raises(o.KernelError, match="multiple of 8"):
+        o.gemv_bf16(x, w, torch.empty((2, 16), dtype=torch.bfloat16, device=dev()))
+    x = rnd((65, 16), torch.bfloat16, 24)
+    w = rnd((16, 16), torch.bfloat16, 25)
+    with pytest.raises(o.KernelError, match="at most 64"):
+        o.gemv_bf16(x, w, torch.empty((65, 16), dtype=torch.bfloat16, device=dev()))
+
+
+ATTN_SHAPES = [(4, 2, 16), (6, 1, 32), (3, 3, 48), (2, 2, 64), (9, 1, 80), (8, 4, 128), (8, 4, 256)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES)
+@pytest.mark.parametrize("window,cap", [(0, 0.0), (7, 20.0), (64, 50.0)])
+def test_attn_prefill(dtype, nq, nkv, hd, window, cap):
+    lens = [1, 9, 70, 23]
+    T = sum(lens)
+    first = torch.tensor([0, 1, 10, 80], dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).int()
+    qkv = rnd((T, nq + 2 * nkv, hd), dtype, 26)
+    # one far key stands out: the first key of the long sequence matches its last query
+    qkv[10, nq] = qkv[79, 0] * 3.0
+    out = torch.empty((T, nq * hd), dtype=dtype, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    d = dev()
+    ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, scale, cap, window)
+    want = torch.empty((T, nq * hd), dtype=torch.float64)
+    R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, scale, cap, window)
+    close(out, want, tol_of(dtype), "attn_prefill")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attn_prefill_reads_another_layers_keys(dtype):
+    nq, nkv, hd = 4, 2, 32
+    lens = [6, 17]
+    T = sum(lens)
+    first = torch.tensor([0, 6], dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(2), torch.tensor(lens)).int()
+    src = rnd((T, nq + 2 * nkv, hd), dtype, 27)
+    q = rnd((T, nq, hd), dtype, 28)
+    d = dev()
+    out = torch.empty((T, nq * hd), dtype=dtype, device=d)
+    ops().attn_prefill(q, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, 0.3, 0.0, 0, kv_src=src,
+                       kv_row_heads=nq + 2 * nkv, kv_k_head0=nq)
+    want = torch.empty((T, nq * hd), dtype=torch.float64)
+    R.attn_prefill(q.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 0.3, 0.0, 0, kv_src=src.cpu(),
+                   kv_row_heads=nq + 2 * nkv, kv_k_head0=nq)
+    close(out, want, tol_of(dtype), "attn_prefill with kv_src")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES)
+@pytest.mark.parametrize("window,ring,chunk", [(0, 0, 64), (0, 0, 256), (16, 64, 64), (100, 128, 64), (128, 128, 128)])
+def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk):
+    # sequences of unequal lengths in scattered pages; one padding row; lengths at page and chunk edges
+    lens = [1, 64, 65, 300, 7, 129]
+    slots = [3, 0, 5, 1, -1, 4]
+    n_seq = len(lens)
+    pages_per_seq = 6
+    n_pages = 40
+    g = torch.Generator().manual_seed(29)
+    perm = torch.randperm(n_pages, generator=g)[: 6 * pages_per_seq].view(6, pages_per_seq).int()
+    k, v = _paged(n_pages, nkv, hd, dtype, 30)
+    qkv = rnd((n_seq, nq + 2 * nkv, hd), dtype, 32)
+    # a far key that matters: position 0 of the 300-token sequence answers head 0's query (when it is visible)
+    k[perm[1, 0].item(), 0, 0] = (qkv[3, 0] * 4.0).to(dtype)
+    d = dev()
+    seq_slot = torch.tensor(slots, dtype=torch.int32)
+    seq_len = torch.tensor(lens, dtype=torch.int32)
+    max_chunks = max((n + chunk - 1) // chunk for n in lens)
+    scratch = torch.empty(ops().attn_decode_scratch_floats(n_seq, nq, hd, max_chunks), dtype=torch.float32, device=d)
+    out = torch.full((n_seq, nq * hd), 7.0, dtype=dtype, device=d)
+    scale, cap = 1.0 / math.sqrt(hd), 30.0
+    ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
+                      window, ring, chunk, max_chunks)
+    want = torch.empty((n_seq, nq * hd), dtype=torch.float64)
+    R.attn_decode(qkv.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, scale, cap, window,
+                  ring, chunk, max_chunks)
+    close(out, want, tol_of(dtype), "attn_decode")
+
+
+def test_attn_decode_marks_an_undersized_launch():
+    nq, nkv, hd = 2, 1, 32
+    d = dev()
+    k, v = _paged(8, nkv, hd, torch.float32, 33)
+    qkv = rnd((1, nq + 2 * nkv, hd), torch.float32, 34)
+    table = torch.arange(8, dtype=torch.int32).view(1, 8).to(d)
+    scratch = torch.empty(ops().attn_decode_scratch_floats(1, nq, hd, 1), dtype=torch.float32, device=d)
+    out = torch.zeros((1, nq * hd), dtype=torch.float32, device=d)
+    ops().attn_decode(qkv, k, v, table, torch.tensor([0], dtype=torch.int32, device=d),
+                      torch.tensor([200], dtype=torch.int32, device=d), scratch, out, nq, nkv, hd, 1.0, 0.0, 0, 0, 64, 1)
+    assert torch.isnan(out).all()
+
+
+@pytest.mark.parametrize("Rn,V", [(1, 7), (5, 384), (3, 256000), (64, 1000)])
+def test_argmax_lowest_id_wins(Rn, V):
+    logits = rnd((Rn, V), torch.float32, 35)
+    logits[0, V // 2] = 50.0
+    logits[0, V - 1] = 50.0
+    if Rn > 1:
+        logits[1, 0] = 50.0
+        logits[1, 3] = 50.0
+    out = torch.empty((Rn,), dtype=torch.int32, device=dev())
+    ops().argmax(logits, out)
+    want = torch.empty((Rn,), dtype=torch.int32)
+    R.argmax(logits.cpu(), want)
+    assert out.cpu().tolist() == want.tolist()
+    assert out[0].item() == V // 2
+
+
+@pytest.mark.parametrize("V", [50, 384, 5000, 256000])
+@pytest.mark.parametrize("temp,top_p", [(1.0, 1.0), (0.6, 0.95), (0.3, 0.5), (1.0, 0.05)])
+def test_sample_matches_the_host_sampler(V, temp, top_p):
+    Rn = 6
+    spread = [0.5, 2.0, 8.0][V % 3]
+    logits = rnd((Rn, V), torch.float32, 36, std=spread)
+    d = dev()
+    ids = torch.arange(100, 100 + Rn, dtype=torch.int32, device=d)
+    idx = torch.arange(Rn, dtype=torch.int32, device=d) * 3
+    out = torch.empty((Rn,), dtype=torch.int32, device=d)
+    u = torch.empty((Rn,), dtype=torch.float32, device=d)
+    ops().sample(logits, out, temp, top_p, 1234567, ids, idx, u)
+    for r in range(Rn):
+        u_ref = R.philox_uniform(1234567, 100 + r, 3 * r)
+        assert abs(u[r].item() - u_ref) < 1e-7
+        assert out[r].item() == R.sample_row(logits[r].cpu(), temp, top_p, u_ref), f"row {r}"
+
+
+def test_sample_with_ties_at_the_nucleus_edge():
+    V = 40
+    logits = torch.zeros((1, V), dtype=torch.float32, device=dev())     # all equal: the nucleus is the first ids
+    d = dev()
+    seen = set()
+    for i in range(200):
+        out = torch.empty((1,), dtype=torch.int32, device=d)
+        ops().sample(logits, out, 1.0, 0.25, 99, torch.tensor([i], dtype=torch.int32, device=d),
+                     torch.tensor([0], dtype=torch.int32, device=d))
+        seen.add(out.item())
+    assert seen == set(range(10))
+
+
+def test_sample_does_not_depend_on_the_batch():
+    V = 1000
+    logits = rnd((4, V), torch.float32, 37, std=3.0)
+    d = dev()
+    ids = torch.tensor([5, 6, 7, 8], dtype=torch.int32, device=d)
+    idx = torch.tensor([0, 1, 2, 3], dtype=torch.int32, device=d)
+    out = torch.empty((4,), dtype=torch.int32, device=d)
+    ops().sample(logits, out, 0.8, 0.9, 42, ids, idx)
+    one = torch.empty((1,), dtype=torch.int32, device=d)
+    ops().sample(logits[2:3].contiguous(), one, 0.8, 0.9, 42, ids[2:3].contiguous(), idx[2:3].contiguous())
+    assert one.item() == out[2].item()
+
+
+def test_repeat_penalty_and_mask():
+    V = 100
+    logits = rnd((2, V), torch.float32, 38)
+    ref = logits.cpu().clone()
+    recent = torch.tensor([[3, 3, 7, -1], [99, 0, 0, 5]], dtype=torch.int32)
+    ops().repeat_penalty(logits, recent.to(dev()), 1.3)
+    R.repeat_penalty(ref, recent, 1.3)
+    close(logits, ref, 1e-6, "repeat penalty")
+    ids = torch.tensor([1, 50], dtype=torch.int32)
+    ops().mask_tokens(logits, ids.to(dev()))
+    assert torch.isinf(logits[:, 1]).all() and torch.isinf(logits[:, 50]).all()
+    assert torch.isfinite(logits[:, 2]).all()
