@@ -1,0 +1,244 @@
+// Prompt attention in bfloat16 on the tensor cores (mma.sync.m16n8k16, float
+// accumulation), one head size per compiled library (JANIS_HEAD_DIM).
+//
+// Packed sequences of unequal lengths that start at position 0.  One CTA owns 64
+// consecutive queries of one sequence and one query head: its 4 warps hold 16
+// query rows each, walk the key tiles of 64 that the causal mask and the window
+// leave, and keep the running maximum, the running sum and the unnormalised output
+// in registers (online softmax).  Per tile: S = Q K^T from shared memory (ldmatrix),
+// s * scale, cap * tanh(s / cap), mask on absolute positions, exp in float, P
+// rounded to bfloat16 as the left operand of P V.  tanhf and expf are the accurate
+// ones.  Shared-memory rows are XOR-swizzled in 16-byte pieces against ldmatrix
+// bank conflicts.
+#include "common.cuh"
+
+#ifndef JANIS_HEAD_DIM
+#error "compile with -DJANIS_HEAD_DIM=<head size, a multiple of 16>"
+#endif
+
+namespace janis {
+namespace pf {
+
+constexpr int HD = JANIS_HEAD_DIM;
+constexpr int BM = 64, BN = 64, WARPS = 4, THREADS = WARPS * 32;
+constexpr int CHUNKS = HD / 8;                       // 16-byte pieces per row
+constexpr int swz_pow2(int n) { return n % 8 == 0 ? 8 : (n % 4 == 0 ? 4 : (n % 2 == 0 ? 2 : 1)); }
+constexpr int SWZ_MASK = swz_pow2(CHUNKS) - 1;
+constexpr int ROW_BYTES = HD * 2;
+constexpr int TILE_BYTES = BM * ROW_BYTES;           // BM == BN
+constexpr int SMEM_BYTES = 3 * TILE_BYTES;           // Q, K, V
+
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
+    return base + row * ROW_BYTES + ((chunk ^ (row & SWZ_MASK)) << 4);
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+    const int n = pred ? 16 : 0;      // n = 0 writes zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 64 rows x HD of bf16 from global rows (row stride `stride` elements) into a swizzled tile;
+// rows >= n_valid are filled with zeros.
+__device__ __forceinline__ void load_tile(uint32_t smem, const bf16* src, size_t stride, int n_valid) {
+    for (int idx = threadIdx.x; idx < BM * CHUNKS; idx += THREADS) {
+        const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+        const bool ok = row < n_valid;
+        cp_async16(tile_addr(smem, row, chunk), src + (size_t)(ok ? row : 0) * stride + chunk * 8, ok);
+    }
+}
+
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__ kv_src,
+                        const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
+                        bf16* __restrict__ out, int nq, int nkv, int q_row_heads, int kv_row_heads,
+                        int kv_k_head0, float scale, float cap, int window) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    // which sequence and which tile of 64 queries is this CTA's
+    int tile = blockIdx.x, seq = -1, q0 = 0, len = 0;
+    for (int s = 0; s < n_seq; ++s) {
+        const int n = seq_len[s];
+        const int nt = (n + BM - 1) / BM;
+        if (tile < nt) { seq = s; q0 = tile * BM; len = n; break; }
+        tile -= nt;
+    }
+    if (seq < 0) return;
+    const int head = blockIdx.y;
+    const int kvh = head / (nq / nkv);
+    const int first = seq_first_row[seq];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
+
+    const size_t q_stride = (size_t)q_row_heads * HD, kv_stride = (size_t)kv_row_heads * HD;
+    load_tile(sQ, q_src + (size_t)(first + q0) * q_stride + (size_t)head * HD, q_stride, min(BM, len - q0));
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const int row_lo = q0 + warp * 16 + g;            // this thread's two query positions
+    const int row_hi = row_lo + 8;
+    const int q_last = min(q0 + BM, len) - 1;
+    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
+    const bf16* kbase = kv_src + (size_t)first * kv_stride + (size_t)(kv_k_head0 + kvh) * HD;
+    const bf16* vbase = kbase + (size_t)nkv * HD;
+
+    for (int k0 = (j_first / BN) * BN; k0 <= q_last; k0 += BN) {
+        __syncthreads();                              // everyone is done with the previous K and V
+        const int n_keys = min(BN, len - k0);
+        load_tile(sK, kbase + (size_t)k0 * kv_stride, kv_stride, n_keys);
+        load_tile(sV, vbase + (size_t)k0 * kv_stride, kv_stride, n_keys);
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();
+
+        // S = Q K^T for this warp's 16 rows and the 64 keys of the tile
+        float s[BN / 8][4];
+#pragma unroll
+        for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            uint32_t a[4];
+            ldmatrix_x4(a, tile_addr(sQ, warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+#pragma unroll
+            for (int jp = 0; jp < BN / 16; ++jp) {
+                uint32_t b[4];
+                ldmatrix_x4(b, tile_addr(sK, jp * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 2 + ((lane >> 3) & 1)));
+                mma16816(s[2 * jp], a, b[0], b[1]);
+                mma16816(s[2 * jp + 1], a, b[2], b[3]);
+            }
+        }
+
+        // scale, cap, mask, online softmax
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = k0 + j * 8 + t * 2 + (c & 1);
+                const int row = (c & 2) ? row_hi : row_lo;
+                float v = s[j][c] * scale;
+                if (cap > 0.f) v = cap * tanhf(v / cap);
+                const bool seen = key <= row && key < len && (window <= 0 || key > row - window);
+                v = seen ? v : -INFINITY;
+                s[j][c] = v;
+                mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            m_use[r] = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet
+            corr[r] = expf(m_run[r] - m_use[r]);               // exp(-inf) = 0
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+        uint32_t p[BN / 16][4];
+#pragma unroll
+        for (int j = 0; j < BN / 8; ++j) {
+            const float p0 = expf(s[j][0] - m_use[0]), p1 = expf(s[j][1] - m_use[0]);
+            const float p2 = expf(s[j][2] - m_use[1]), p3 = expf(s[j][3] - m_use[1]);
+            l_run[0] += p0 + p1;
+            l_run[1] += p2 + p3;
+            p[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+            p[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+            for (int ip = 0; ip < HD / 16; ++ip) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, tile_addr(sV, kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), ip * 2 + (lane >> 4)));
+                mma16816(o[2 * ip], p[kk], b[0], b[1]);
+                mma16816(o[2 * ip + 1], p[kk], b[2], b[3]);
+            }
+        }
+    }
+
+    // the sums of a row are spread over the four threads that share it
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    const float inv_lo = 1.0f / l_run[0], inv_hi = 1.0f / l_run[1];
+    bf16* out_lo = out + (size_t)(first + row_lo) * nq * HD + (size_t)head * HD + t * 2;
+    bf16* out_hi = out + (size_t)(first + row_hi) * nq * HD + (size_t)head * HD + t * 2;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        if (row_lo < len) *reinterpret_cast<uint32_t*>(out_lo + i * 8) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
+        if (row_hi < len) *reinterpret_cast<uint32_t*>(out_hi + i * 8) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
+    }
+}
+
+}  // namespace pf
+}  // namespace janis
+
+using namespace janis;
+
+// q_src: [T, q_row_heads, hd] with the queries in its first nq heads; keys and values of position j of
+// sequence s are read from row seq_first_row[s] + j of kv_src [T, kv_row_heads, hd], key heads starting at
+// head kv_k_head0, value heads nkv later.  n_tiles_bound >= sum over sequences of ceil(len / 64).
+JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, const int* seq_first_row,
+                                        const int* seq_len, int n_seq, int n_tiles_bound, void* out, int nq,
+                                        int nkv, int q_row_heads, int kv_row_heads, int kv_k_head0, float scale,
+                                        float cap, int window, cudaStream_t stream) {
+    if (n_seq <= 0 || n_tiles_bound <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return fail("attn_prefill_mma: %d query heads do not divide over %d key heads", nq, nkv);
+    if (((uintptr_t)q_src | (uintptr_t)kv_src | (uintptr_t)out) & 15)
+        return fail("attn_prefill_mma: operands must be 16-byte aligned");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(pf::attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             pf::SMEM_BYTES);
+        if (e != cudaSuccess) return fail("attn_prefill_mma: shared memory of %d bytes refused: %s", pf::SMEM_BYTES,
+                                          cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(n_tiles_bound, nq);
+    pf::attn_prefill_mma_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
+        (const bf16*)q_src, (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
+        kv_row_heads, kv_k_head0, scale, cap, window);
+    return launched("attn_prefill_mma");
+}

@@ -32,7 +32,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemv_bf16.cu", "sampling.cu"]
-ATTENTION_SOURCES = ["attention.cu"]
+ATTENTION_SOURCES = ["attention.cu", "attention_prefill_mma.cu"]
 HEADERS = ["common.cuh"]
 
 

@@ -62,17 +62,23 @@ class Stepper:
         self._graphs: dict[tuple[int, int], tuple] = {}
         self._decode_meta = None
         self._decode_logits = None
-        self.launch_counter = 0     # kernels launched by the last step (decode steps: per replay)
+        self._stage: list = []
+        self._stage_done: list = []
+        self._stage_next = 0
+        self.h2d_bytes = 0          # bytes of the last decode step's host-to-device copy
+        self.launch_counter = 0     # kernels launched by the last decode step (per replay when graphed)
 
     # ------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], copy: bool = True) -> torch.Tensor | None:
+    def step(self, entries: Sequence[StepEntry], copy: bool = True, tokens_on_device: bool = False):
         """Run one step.  Returns float32 [wanted, vocab] on the device, or None when nothing is wanted.
-        With copy=False a decode step returns a view of a buffer that the next step overwrites."""
+        With copy=False a decode step returns a view of a buffer that the next step overwrites.
+        With tokens_on_device=True a decode step takes its tokens from `token_buffer` as it stands
+        (the entries' token values are ignored)."""
         entries = list(entries)
         mode = self._validate(entries)
         if mode == "prefill":
             return self._prefill(entries)
-        return self._decode(entries, copy)
+        return self._decode(entries, copy, tokens_on_device)
 
     def _validate(self, entries) -> str:
         if not entries:
@@ -164,7 +170,7 @@ class Stepper:
             self.cache.advance(e.slot, n)
 
     # ------------------------------------------------------------------
-    def _decode(self, entries, copy: bool) -> torch.Tensor | None:
+    def _decode(self, entries, copy: bool, tokens_on_device: bool = False) -> torch.Tensor | None:
         n_seq = len(entries)
         B = _bucket_batch(n_seq)
         pos = [self.cache.length(e.slot) for e in entries]
@@ -173,13 +179,14 @@ class Stepper:
         self.cache.sync()
         bound = _bucket_len(max(pos) + 1)
         graphs = self.use_graphs and B <= self.MAX_GRAPH_BATCH
+        dev = self.rt.device
         if self._decode_meta is None:
-            self._decode_meta = torch.zeros((7, self.MAX_GRAPH_BATCH), dtype=torch.int32, device=self.rt.device)
+            self._decode_meta = torch.zeros((7, self.MAX_GRAPH_BATCH), dtype=torch.int32, device=dev)
         if self._decode_logits is None or self._decode_logits.shape[0] < B:
             self._graphs.clear()        # graphs hold the address of the old buffer
-            rows = max(B, 8)
-            self._decode_logits = torch.empty((rows, self.model.vocab), dtype=torch.float32, device=self.rt.device)
-        host = np.zeros((7, self.MAX_GRAPH_BATCH if graphs else max(B, 1)), dtype=np.int32)
+            self._decode_logits = torch.empty((max(B, 8), self.model.vocab), dtype=torch.float32, device=dev)
+        width = self.MAX_GRAPH_BATCH if B <= self.MAX_GRAPH_BATCH else B
+        host = np.zeros((7, width), dtype=np.int32)
         host[0, :n_seq] = [int(e.tokens[0]) for e in entries]
         host[1, :n_seq] = pos
         host[2, :B] = np.arange(B)
@@ -189,22 +196,27 @@ class Stepper:
         host[5, :B] = 1
         host[5, :n_seq] = np.asarray(pos) + 1
         host[6, :B] = np.arange(B)
-        if graphs:
+        if B <= self.MAX_GRAPH_BATCH:
             meta = self._decode_meta
-            meta.copy_(torch.from_numpy(host))
+            self._upload(host, meta, skip_tokens=tokens_on_device)
         else:
-            meta = torch.from_numpy(host).to(self.rt.device)
+            meta = torch.from_numpy(host).to(dev)
         ctx = StepContext(rt=self.rt, ws=self.ws, mode="decode", n_tok=B, n_seq=B, tokens=meta[0, :B],
                           tok_pos=meta[1, :B], tok_seq=meta[2, :B], seq_slot=meta[3, :B], seq_start=meta[4, :B],
                           seq_end=meta[5, :B], seq_first_row=meta[6, :B], len_bound=bound)
         logits = self._decode_logits[:B]
         key = (B, bound)
         if graphs and key in self._graphs:
-            self._graphs[key].replay()
+            g, n_launch = self._graphs[key]
+            g.replay()
+            self.launch_counter = n_launch
         else:
+            before = self.rt.ops.launch_count() if hasattr(self.rt.ops, "launch_count") else 0
             self._decode_body(ctx, logits)
+            n_launch = (self.rt.ops.launch_count() if hasattr(self.rt.ops, "launch_count") else 0) - before
+            self.launch_counter = n_launch
             if graphs:
-                self._graphs[key] = self._capture(ctx, logits)
+                self._graphs[key] = (self._capture(ctx, logits), n_launch)
         for e, p in zip(entries, pos):
             self.cache.advance(e.slot, p + 1)
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
@@ -213,9 +225,43 @@ class Stepper:
         if len(wanted) == n_seq:
             res = logits[:n_seq]
         else:
-            res = logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.rt.device))
+            res = logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=dev))
             copy = False
         return res.clone() if copy else res
+
+    def token_buffer(self, n: int) -> torch.Tensor:
+        """The device buffer that a decode step reads its tokens from (int32 [n]).  A sampler that
+        writes the next tokens here feeds them to the next step without a trip to the host
+        (`step(..., tokens_on_device=True)`); the reference's greedy loop keeps the token on the
+        device in the same way (`qwen/model.go:354-404`)."""
+        if n > self.MAX_GRAPH_BATCH:
+            raise StepError(f"device-fed tokens are limited to {self.MAX_GRAPH_BATCH} sequences")
+        if self._decode_meta is None:
+            self._decode_meta = torch.zeros((7, self.MAX_GRAPH_BATCH), dtype=torch.int32, device=self.rt.device)
+        return self._decode_meta[0, :n]
+
+    def _upload(self, host: np.ndarray, meta: torch.Tensor, skip_tokens: bool) -> None:
+        """Host tables of a decode step -> the static device tables, through pinned staging buffers.
+        A staging buffer is reused only after the copy that read it has run."""
+        if torch.device(self.rt.device).type != "cuda":
+            (meta[1:] if skip_tokens else meta).copy_(torch.from_numpy(host[1:] if skip_tokens else host))
+            return
+        if not self._stage:
+            self._stage = [torch.empty((7, self.MAX_GRAPH_BATCH), dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._stage_done = [None] * len(self._stage)
+        i = self._stage_next
+        self._stage_next = (i + 1) % len(self._stage)
+        if self._stage_done[i] is not None:
+            self._stage_done[i].synchronize()
+        self._stage[i].numpy()[...] = host
+        if skip_tokens:
+            meta[1:].copy_(self._stage[i][1:], non_blocking=True)
+        else:
+            meta.copy_(self._stage[i], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._stage_done[i] = ev
+        self.h2d_bytes = (6 if skip_tokens else 7) * self.MAX_GRAPH_BATCH * 4
 
     def _decode_body(self, ctx: StepContext, logits: torch.Tensor) -> None:
         h = self.model.forward(ctx, self.cache)

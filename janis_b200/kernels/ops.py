@@ -73,6 +73,7 @@ def attention_lib(head_dim: int):
         lib.janis_attn_decode_scratch.restype = c_longlong
         lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P]
         lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
+        lib.janis_attn_prefill_mma.argtypes = [P, P, P, P, I, I, P, I, I, I, I, I, F, F, I, P]
         if lib.janis_attn_head_dim() != head_dim:
             raise KernelError(f"attention library for head size {head_dim} reports {lib.janis_attn_head_dim()}")
         _attn[head_dim] = lib
@@ -83,9 +84,19 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(lib, rc: int) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many of this library's kernels have been launched (or recorded into a graph) so far."""
+    return _launches
+
+
+def _check(lib, rc: int, kernels: int = 1) -> None:
+    global _launches
     if rc != 0:
         raise KernelError(lib.janis_last_error().decode("utf-8", "replace"))
+    _launches += kernels
 
 
 def _t(x: torch.Tensor, name: str, dtype=None, shape=None) -> int:
@@ -244,11 +255,16 @@ def linear_bf16(x, w, out):
 # ---------------------------------------------------------------------------
 
 def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, hd: int, scale: float, cap: float,
-                 window: int, kv_src=None, kv_row_heads=None, kv_k_head0=None):
+                 window: int, kv_src=None, kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True):
     """Causal (and windowed when window > 0) attention over packed sequences that start at position 0.
     qkv: [T, nq + 2 nkv, hd], or [T, nq, hd] when keys and values come from `kv_src`, another layer's
-    [T, kv_row_heads, hd] rows whose key heads start at head kv_k_head0 (values nkv heads later)."""
+    [T, kv_row_heads, hd] rows whose key heads start at head kv_k_head0 (values nkv heads later).
+    bfloat16 with `seq_len` (int32 [n_seq], the sequences' lengths) runs on the tensor cores; float32
+    runs the CUDA-core kernel, which is exact 32-bit."""
     T = qkv.shape[0]
+    if qkv.dtype == torch.bfloat16 and seq_len is not None and tensor_cores:
+        return _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src,
+                                 kv_row_heads, kv_k_head0)
     if kv_src is None:
         _t(qkv, "qkv", _FLOATS, (T, nq + 2 * nkv, hd))
         kv_src, kv_row_heads, kv_k_head0 = qkv, nq + 2 * nkv, nq
@@ -267,6 +283,32 @@ def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, h
                                        _t(seq_first_row, "seq_first_row", torch.int32), out.data_ptr(), T, nq, nkv,
                                        q_row_heads, kv_row_heads, kv_k_head0, float(scale), float(cap),
                                        int(window), _stream()))
+    return out
+
+
+def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src, kv_row_heads,
+                      kv_k_head0):
+    T = qkv.shape[0]
+    if kv_src is None:
+        _t(qkv, "qkv", torch.bfloat16, (T, nq + 2 * nkv, hd))
+        kv_src, kv_row_heads, kv_k_head0 = qkv, nq + 2 * nkv, nq
+    else:
+        _t(qkv, "qkv", torch.bfloat16, (T, None, hd))
+        if qkv.shape[1] < nq:
+            raise KernelError("attn_prefill: query rows hold fewer heads than nq")
+    _t(kv_src, "kv_src", torch.bfloat16, (T, kv_row_heads, hd))
+    if kv_k_head0 + 2 * nkv > kv_row_heads:
+        raise KernelError("attn_prefill: key/value heads lie outside the rows of kv_src")
+    _t(out, "out", torch.bfloat16, (T, nq * hd))
+    n_seq = seq_len.numel()
+    _t(seq_len, "seq_len", torch.int32, (n_seq,))
+    _t(seq_first_row, "seq_first_row", torch.int32, (n_seq,))
+    lib = attention_lib(hd)
+    tiles = (T + 63) // 64 + n_seq          # >= sum of ceil(len / 64)
+    _check(lib, lib.janis_attn_prefill_mma(qkv.data_ptr(), kv_src.data_ptr(), seq_first_row.data_ptr(),
+                                           seq_len.data_ptr(), n_seq, tiles, out.data_ptr(), nq, nkv,
+                                           qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),
+                                           int(window), _stream()))
     return out
 
 
@@ -296,7 +338,7 @@ def attn_decode(qkv, kpool, vpool, page_table, seq_slot, seq_len, scratch, out, 
                                       _t(seq_slot, "seq_slot", torch.int32), _t(seq_len, "seq_len", torch.int32),
                                       scratch.data_ptr(), scratch.numel(), out.data_ptr(), n_seq, nq, nkv,
                                       qkv.shape[1], float(scale), float(cap), int(window), int(ring_len),
-                                      int(chunk), int(max_chunks), _stream()))
+                                      int(chunk), int(max_chunks), _stream()), kernels=2)
     return out
 
 

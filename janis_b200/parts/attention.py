@@ -98,11 +98,12 @@ class SoftmaxAttention(Mixer):
                 if line.has_readers:
                     ctx.shared[("kv", line.index)] = (qkv, heads, nq)
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
-                                 self.softcap, self.window)
+                                 self.softcap, self.window, seq_len=ctx.seq_end)
             else:
                 src, src_heads, k0 = ctx.shared[("kv", line.index)]
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
-                                 self.softcap, self.window, kv_src=src, kv_row_heads=src_heads, kv_k_head0=k0)
+                                 self.softcap, self.window, kv_src=src, kv_row_heads=src_heads, kv_k_head0=k0,
+                                 seq_len=ctx.seq_end)
         else:
             chunk, max_chunks = self._decode_geometry(ctx, rt.sm_count)
             scratch = ws.buf("attn.partial", (ops.attn_decode_scratch_floats(ctx.n_seq, nq, hd, max_chunks),),

@@ -264,6 +264,31 @@ def test_attn_prefill(dtype, nq, nkv, hd, window, cap):
     close(out, want, tol_of(dtype), "attn_prefill")
 
 
+@pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES + [(2, 1, 96), (2, 2, 112)])
+@pytest.mark.parametrize("window,cap", [(0, 0.0), (7, 20.0), (64, 50.0), (100, 30.0)])
+def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap):
+    """The bfloat16 tensor-core kernel: tiles of 64 queries and keys, so lengths around 64 and 128,
+    a window that cuts inside and across tiles, and a far key that must win."""
+    lens = [1, 63, 64, 65, 200, 129]
+    T = sum(lens)
+    first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).int()
+    seq_len = torch.tensor(lens, dtype=torch.int32)
+    qkv = rnd((T, nq + 2 * nkv, hd), torch.bfloat16, 40)
+    r0 = int(first[4])
+    qkv[r0, nq] = qkv[r0 + 199, 0] * 3.0          # position 0 of the 200-token sequence answers its last query
+    out = torch.full((T, nq * hd), 9.0, dtype=torch.bfloat16, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    d = dev()
+    ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, scale, cap, window,
+                       seq_len=seq_len.to(d))
+    want = torch.empty((T, nq * hd), dtype=torch.float64)
+    R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, scale, cap, window)
+    # P is rounded to bfloat16 before P V: one more rounding step than the CUDA-core kernel
+    close(out, want, 2 * BF16_TOL, "attn_prefill on tensor cores")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attn_prefill_reads_another_layers_keys(dtype):
     nq, nkv, hd = 4, 2, 32
@@ -277,11 +302,12 @@ def test_attn_prefill_reads_another_layers_keys(dtype):
     d = dev()
     out = torch.empty((T, nq * hd), dtype=dtype, device=d)
     ops().attn_prefill(q, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, 0.3, 0.0, 0, kv_src=src,
-                       kv_row_heads=nq + 2 * nkv, kv_k_head0=nq)
+                       kv_row_heads=nq + 2 * nkv, kv_k_head0=nq,
+                       seq_len=torch.tensor(lens, dtype=torch.int32, device=d))
     want = torch.empty((T, nq * hd), dtype=torch.float64)
     R.attn_prefill(q.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 0.3, 0.0, 0, kv_src=src.cpu(),
                    kv_row_heads=nq + 2 * nkv, kv_k_head0=nq)
-    close(out, want, tol_of(dtype), "attn_prefill with kv_src")
+    close(out, want, tol_of(dtype) * (2 if dtype == torch.bfloat16 else 1), "attn_prefill with kv_src")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
