@@ -1,0 +1,141 @@
+"""The generation loop's decisions with a fake backend, apart from any model (the reference tests
+its session the same way with a fake forward, `qwen/session_pin_test.go:55-129`)."""
+from __future__ import annotations
+
+import pytest
+
+from janis_b200.engine.generate import GenerationError, Reply, generate, plan_batches
+
+
+class FakeBackend:
+    """Next token = (last token + 1) % 100; prompts prefill to (last prompt token + 1).  Counts what the
+    loop asks of it and checks that places are opened and closed exactly once."""
+
+    def __init__(self, max_batch=4, max_context=64, room=1000):
+        self.max_batch, self.max_context, self.room = max_batch, max_context, room
+        self.open_handles, self.next_handle = set(), 0
+        self.closed = []
+        self.prefills, self.decodes = [], []
+        self.live_peak = 0
+
+    def fits(self, final_lengths):
+        return sum(final_lengths) <= self.room
+
+    def open(self):
+        h = self.next_handle
+        self.next_handle += 1
+        self.open_handles.add(h)
+        self.live_peak = max(self.live_peak, len(self.open_handles))
+        return h
+
+    def close(self, h):
+        assert h in self.open_handles, "closed twice or never opened"
+        self.open_handles.remove(h)
+        self.closed.append(h)
+
+    def prefill(self, handles, prompts, request_ids, banned):
+        assert set(handles) <= self.open_handles
+        self.prefills.append((list(request_ids), banned))
+        out = [(p[-1] + 1) % 100 for p in prompts]
+        if banned:
+            out = [t if t not in banned else (t + 1) % 100 for t in out]
+        return out
+
+    def decode(self, handles, last_tokens, request_ids, token_index, replies):
+        assert set(handles) <= self.open_handles and len(handles) == len(last_tokens)
+        for idx, r in zip(token_index, replies):
+            assert idx == len(r)
+        self.decodes.append(list(request_ids))
+        return [(t + 1) % 100 for t in last_tokens]
+
+
+def test_length_limit_and_order_of_replies():
+    b = FakeBackend()
+    out = generate(b, [[10], [20, 21], [30]], max_tokens=3)
+    assert [r.tokens for r in out] == [[11, 12, 13], [22, 23, 24], [31, 32, 33]]
+    assert all(r.finish_reason == "length" for r in out)
+    assert len(b.prefills) == 1 and len(b.decodes) == 2            # the last token is not fed back
+    assert not b.open_handles and sorted(b.closed) == [0, 1, 2]
+
+
+def test_stop_token_ends_a_reply_and_is_not_part_of_it():
+    b = FakeBackend()
+    out = generate(b, [[10], [47]], max_tokens=10, stop=[13, 50])
+    assert out[0].tokens == [11, 12] and out[0].finish_reason == "stop"
+    assert out[1].tokens == [48, 49] and out[1].finish_reason == "stop"
+
+
+def test_shorter_requests_leave_the_batch_earlier():
+    b = FakeBackend()
+    out = generate(b, [[10], [20], [30]], max_tokens=6, stop=[12, 23])
+    assert [r.tokens for r in out] == [[11], [21, 22], [31, 32, 33, 34, 35, 36]]
+    assert b.decodes[0] == [0, 1, 2] and b.decodes[1] == [1, 2] and all(d == [2] for d in b.decodes[2:])
+    assert b.closed[:2] == [0, 1]                                  # places come back as sequences end
+
+
+def test_first_token_can_be_a_stop():
+    b = FakeBackend()
+    out = generate(b, [[10]], max_tokens=5, stop=[11])
+    assert out[0].tokens == [] and out[0].finish_reason == "stop" and not b.decodes
+    b = FakeBackend()
+    out = generate(b, [[10]], max_tokens=3, stop=[11], mask_stop_on_first=True)
+    assert b.prefills[0][1] == [11] and out[0].tokens == [12, 13, 14]
+
+
+def test_requests_beyond_one_batch_run_in_later_batches():
+    b = FakeBackend(max_batch=2)
+    out = generate(b, [[i] for i in range(5)], max_tokens=2)
+    assert [r.tokens for r in out] == [[i + 1, i + 2] for i in range(5)]
+    assert [p[0] for p in b.prefills] == [[0, 1], [2, 3], [4]] and b.live_peak == 2
+    b = FakeBackend(max_batch=8, room=30)                          # room decides: 3 requests of 10 tokens at most
+    generate(b, [[1]] * 7, max_tokens=9)
+    assert [len(p[0]) for p in b.prefills] == [3, 3, 1]
+    with pytest.raises(GenerationError, match="more than the cache holds"):
+        generate(FakeBackend(room=5), [[1, 2, 3]], max_tokens=9)
+
+
+def test_plan_batches_keeps_order():
+    assert plan_batches([5, 5, 5, 5], 3, lambda ls: sum(ls) <= 12) == [[0, 1], [2, 3]]
+    assert plan_batches([], 3, lambda ls: True) == []
+
+
+def test_context_is_a_limit_too():
+    b = FakeBackend(max_context=8)
+    out = generate(b, [[1, 2, 3, 4, 5]], max_tokens=50)
+    assert len(out[0].tokens) == 3 and out[0].finish_reason == "length"   # 5 + 3 = 8
+    with pytest.raises(GenerationError, match="no room"):
+        generate(b, [[0] * 8], max_tokens=5)
+
+
+def test_empty_prompt_and_default_length():
+    b = FakeBackend(max_context=10 ** 6, room=10 ** 9)
+    out = generate(b, [[], [5]], max_tokens=0)                     # <= 0 means the reference's default of 512
+    assert out[0].tokens == [] and out[0].finish_reason == "empty"
+    assert len(out[1].tokens) == 512
+
+
+def test_callbacks_and_cancel():
+    b = FakeBackend(max_batch=2)
+    heard = []
+    calls = [0]
+
+    def cancel():
+        calls[0] += 1
+        return calls[0] >= 3
+
+    out = generate(b, [[10], [20], [30]], max_tokens=10, on_token=lambda i, t: heard.append((i, t)), cancel=cancel)
+    assert out[0].tokens == [11, 12, 13] and out[1].tokens == [21, 22, 23]
+    assert [r.finish_reason for r in out] == ["cancel", "cancel", "cancel"] and out[2].tokens == []
+    assert heard == [(0, 11), (1, 21), (0, 12), (1, 22), (0, 13), (1, 23)]
+    assert not b.open_handles
+
+
+def test_places_are_closed_when_the_backend_fails():
+    class Broken(FakeBackend):
+        def decode(self, *a):
+            raise RuntimeError("boom")
+
+    b = Broken()
+    with pytest.raises(RuntimeError, match="boom"):
+        generate(b, [[1], [2]], max_tokens=4)
+    assert not b.open_handles
