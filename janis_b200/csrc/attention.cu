@@ -198,6 +198,45 @@ __device__ __forceinline__ void chunk_range(int len, int window, int chunk, int&
     n_chunks = (len + chunk - 1) / chunk - first_chunk;
 }
 
+// What a decode CTA leaves for the merge: the warps' states folded in warp order.
+template <typename T>
+__device__ __forceinline__ void write_partial(Lane<T>& st, float (*sm)[Geo<T>::RG][HD + 2], float* __restrict__ partial,
+                                              int s, int nq, int h0, int nh_here, int warp, int lig, int grp) {
+    typedef Geo<T> G;
+    st.merge_groups();
+    if (grp == 0) {
+#pragma unroll
+        for (int r = 0; r < G::RG; ++r) {
+            if (lig == 0) { sm[warp][r][0] = st.m[r]; sm[warp][r][1] = st.l[r]; }
+#pragma unroll
+            for (int cc = 0; cc < G::CPL; ++cc)
+#pragma unroll
+                for (int e = 0; e < G::VEC; ++e)
+                    sm[warp][r][2 + (cc * G::LPK + lig) * G::VEC + e] = st.acc[r][cc * G::VEC + e];
+        }
+    }
+    __syncthreads();
+    const int max_chunks = gridDim.x;
+    for (int idx = threadIdx.x; idx < nh_here * (HD + 2); idx += blockDim.x) {
+        const int r = idx / (HD + 2), d = idx % (HD + 2);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATTN_WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
+        float v;
+        if (d == 0) v = mx;
+        else {
+            v = 0.f;
+#pragma unroll
+            for (int w = 0; w < ATTN_WARPS; ++w) {
+                const float mw = sm[w][r][0];
+                if (mw != -INFINITY) v += sm[w][r][d] * expf(mw - mx);
+            }
+        }
+        partial[(((size_t)s * nq + h0 + r) * max_chunks + blockIdx.x) * (HD + 2) + d] = v;
+    }
+}
+
+// Decode attention, keys and values read straight from global memory into registers.
 template <typename T>
 __global__ void __launch_bounds__(ATTN_WARPS * 32)
 attn_decode_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool, const T* __restrict__ vpool,
@@ -239,43 +278,157 @@ attn_decode_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool, const
         const size_t off = (((size_t)page * nkv + kvh) * JANIS_PAGE + idx % JANIS_PAGE) * HD;
         st.key(kpool + off, vpool + off, valid, cap, lig);
     }
-    st.merge_groups();
-    if (grp == 0) {
-#pragma unroll
-        for (int r = 0; r < G::RG; ++r) {
-            if (lig == 0) { sm[warp][r][0] = st.m[r]; sm[warp][r][1] = st.l[r]; }
-#pragma unroll
-            for (int cc = 0; cc < G::CPL; ++cc)
-#pragma unroll
-                for (int e = 0; e < G::VEC; ++e)
-                    sm[warp][r][2 + (cc * G::LPK + lig) * G::VEC + e] = st.acc[r][cc * G::VEC + e];
-        }
-    }
-    __syncthreads();
-    const int max_chunks = gridDim.x;
-    for (int idx = threadIdx.x; idx < nh_here * (HD + 2); idx += blockDim.x) {
-        const int r = idx / (HD + 2), d = idx % (HD + 2);
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < ATTN_WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
-        float v;
-        if (d == 0) v = mx;
-        else {
-            v = 0.f;
-#pragma unroll
-            for (int w = 0; w < ATTN_WARPS; ++w) {
-                const float mw = sm[w][r][0];
-                if (mw != -INFINITY) v += sm[w][r][d] * expf(mw - mx);
-            }
-        }
-        partial[(((size_t)s * nq + h0 + r) * max_chunks + blockIdx.x) * (HD + 2) + d] = v;
-    }
+    write_partial<T>(st, sm, partial, s, nq, h0, nh_here, warp, lig, grp);
 }
 
+// ---------------------------------------------------------------------------
+// The same step with keys and values staged through shared memory by the TMA
+// engine: one thread issues bulk copies (cp.async.bulk) of whole tiles of a
+// cache page, three stages deep, and an mbarrier per stage tells the warps when
+// the bytes have landed.  A (page, head) of the cache is contiguous, so a tile of
+// TILE keys is one copy of TILE * hd elements for keys and one for values.  The
+// register kernel above keeps ~16 KB in flight per SM and is bound by latency;
+// this one keeps up to 3 stages per CTA in flight.
+// Every wait is bounded: a barrier that does not complete makes the CTA give up,
+// count the event in g_wait_timeouts and return (its output is then garbage and the
+// host finds the count in janis_attn_wait_timeouts()).
+// ---------------------------------------------------------------------------
+__device__ int g_wait_timeouts = 0;
+
+constexpr int pow2_floor(int n) { return n >= 64 ? 64 : (n >= 32 ? 32 : (n >= 16 ? 16 : (n >= 8 ? 8 : (n >= 4 ? 4 : (n >= 2 ? 2 : 1))))); }
+constexpr int max_int(int a, int b) { return a > b ? a : b; }
+
+template <typename T> struct Staged {
+    static constexpr int STAGES = 3;
+    static constexpr int KEYS_PER_PASS = ATTN_WARPS * Geo<T>::KPW;        // keys the CTA handles at a time
+    static constexpr int TILE = max_int(KEYS_PER_PASS, pow2_floor(32768 / (2 * HD * (int)sizeof(T))));
+    static constexpr int TILE_BYTES = TILE * HD * (int)sizeof(T);
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;                      // keys, then values
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;
+    static_assert(TILE <= JANIS_PAGE && JANIS_PAGE % TILE == 0, "a tile must divide a page");
+    static_assert(TILE % KEYS_PER_PASS == 0, "a tile must be whole passes");
+    static_assert(SMEM_BYTES <= 200 * 1024, "stages do not fit shared memory");
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, int bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// true when the phase with this parity has completed; false after a bounded number of tries
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ATTN_WARPS * 32)
+attn_decode_staged_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool, const T* __restrict__ vpool,
+                          const int* __restrict__ page_table, int table_stride, const int* __restrict__ seq_slot,
+                          const int* __restrict__ seq_len, float* __restrict__ partial, int nq, int nkv,
+                          int q_row_heads, float scale, float cap, int window, int ring_len, int chunk) {
+    typedef Geo<T> G;
+    typedef Staged<T> S;
+    extern __shared__ __align__(128) unsigned char stage_mem[];
+    __shared__ float sm[ATTN_WARPS][G::RG][HD + 2];
+    __shared__ __align__(8) unsigned long long full[S::STAGES];
+    const int s = blockIdx.z;
+    const int slot = seq_slot[s];
+    if (slot < 0) return;
+    const int len = seq_len[s];
+    int lo, first_chunk, n_chunks;
+    chunk_range(len, window, chunk, lo, first_chunk, n_chunks);
+    if ((int)blockIdx.x >= n_chunks) return;
+    const int c = first_chunk + blockIdx.x;
+    const int k_begin = max(lo, c * chunk), k_end = min(len, (c + 1) * chunk);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rep = nq / nkv;
+    const int groups = (rep + G::RG - 1) / G::RG;
+    const int kvh = blockIdx.y / groups, hg = blockIdx.y % groups;
+    const int h0 = kvh * rep + hg * G::RG;
+    const int nh_here = min(G::RG, rep - hg * G::RG);
+    const int lig = lane % G::LPK, grp = lane / G::LPK;
+
+    const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(stage_mem);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(full);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S::STAGES; ++i) mbar_init(bar0 + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    // tiles of TILE positions, aligned to TILE, that cover [k_begin, k_end)
+    const int t_first = (k_begin / S::TILE) * S::TILE;
+    const int n_tiles = (k_end - t_first + S::TILE - 1) / S::TILE;
+    const int* table = page_table + (size_t)slot * table_stride;
+    auto issue = [&](int i) {       // thread 0: bring tile i into its stage
+        const int p0 = t_first + i * S::TILE;
+        const int idx = ring_len > 0 ? p0 % ring_len : p0;
+        const int page = table[idx / JANIS_PAGE];
+        const size_t off = (((size_t)page * nkv + kvh) * JANIS_PAGE + idx % JANIS_PAGE) * HD;
+        const int st_i = i % S::STAGES;
+        const uint32_t dst = stage0 + st_i * S::STAGE_BYTES, bar = bar0 + 8 * st_i;
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // earlier reads of this stage are done
+        mbar_expect_tx(bar, S::STAGE_BYTES);
+        bulk_load(dst, kpool + off, S::TILE_BYTES, bar);
+        bulk_load(dst + S::TILE_BYTES, vpool + off, S::TILE_BYTES, bar);
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < S::STAGES && i < n_tiles; ++i) issue(i);
+
+    Lane<T> st;
+    st.init();
+    const T* qrow = qkv + (size_t)s * q_row_heads * HD;
+#pragma unroll
+    for (int r = 0; r < G::RG; ++r) st.load_q(qrow + (size_t)(h0 + r) * HD, r, r < nh_here, scale, lig);
+
+    for (int i = 0; i < n_tiles; ++i) {
+        const int st_i = i % S::STAGES;
+        const bool landed = mbar_wait(bar0 + 8 * st_i, (i / S::STAGES) & 1);
+        if (landed) {
+            const T* ks = reinterpret_cast<const T*>(stage_mem + (size_t)st_i * S::STAGE_BYTES);
+            const T* vs = reinterpret_cast<const T*>(stage_mem + (size_t)st_i * S::STAGE_BYTES + S::TILE_BYTES);
+            const int p0 = t_first + i * S::TILE;
+#pragma unroll
+            for (int pass = 0; pass < S::TILE / S::KEYS_PER_PASS; ++pass) {
+                const int r = pass * S::KEYS_PER_PASS + warp * G::KPW + grp;      // row of the tile
+                const int j = p0 + r;
+                st.key(ks + (size_t)r * HD, vs + (size_t)r * HD, j >= k_begin && j < k_end, cap, lig);
+            }
+        }
+        // everyone has read the stage (or given up): the same barrier tells all of a timeout
+        if (!__syncthreads_and(landed ? 1 : 0)) {
+            if (threadIdx.x == 0) atomicAdd(&g_wait_timeouts, 1);
+            return;
+        }
+        if (threadIdx.x == 0 && i + S::STAGES < n_tiles) issue(i + S::STAGES);
+    }
+    write_partial<T>(st, sm, partial, s, nq, h0, nh_here, warp, lig, grp);
+}
+
+// Merge of the chunks in ascending order.  One CTA per (sequence, head): the chunks' weights
+// exp(m_c - m) / l are formed once in shared memory, then each thread sums its features.
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ partial, const int* __restrict__ seq_slot,
                                   const int* __restrict__ seq_len, T* __restrict__ out, int nq, int max_chunks,
                                   int window, int chunk) {
+    extern __shared__ float wgt[];            // max_chunks weights
+    __shared__ float red[32];
     const int s = blockIdx.x, h = blockIdx.y;
     T* o = out + ((size_t)s * nq + h) * HD;
     if (seq_slot[s] < 0) {
@@ -289,21 +442,33 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const int* 
         return;
     }
     const float* p = partial + ((size_t)s * nq + h) * max_chunks * (HD + 2);
+    // the maximum over chunks (any order gives the same value)
     float mx = -INFINITY;
-    for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, p[(size_t)c * (HD + 2)]);
-    float l = 0.f;
-    for (int c = 0; c < n_chunks; ++c) {
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) mx = fmaxf(mx, p[(size_t)c * (HD + 2)]);
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < (int)((blockDim.x + 31) >> 5); ++w) mx = fmaxf(mx, red[w]);
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
         const float mc = p[(size_t)c * (HD + 2)];
-        if (mc != -INFINITY) l += p[(size_t)c * (HD + 2) + 1] * expf(mc - mx);
+        wgt[c] = mc == -INFINITY ? 0.f : expf(mc - mx);
     }
+    __syncthreads();
+    float l = 0.f;                               // in chunk order, the same in every thread
+    for (int c = 0; c < n_chunks; ++c) l += p[(size_t)c * (HD + 2) + 1] * wgt[c];
     const float inv = 1.0f / l;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float a = 0.f;
-        for (int c = 0; c < n_chunks; ++c) {
-            const float mc = p[(size_t)c * (HD + 2)];
-            if (mc != -INFINITY) a += p[(size_t)c * (HD + 2) + 2 + d] * expf(mc - mx);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;     // four running sums keep four loads in flight
+        int c = 0;
+        for (; c + 4 <= n_chunks; c += 4) {
+            a0 += p[(size_t)(c + 0) * (HD + 2) + 2 + d] * wgt[c + 0];
+            a1 += p[(size_t)(c + 1) * (HD + 2) + 2 + d] * wgt[c + 1];
+            a2 += p[(size_t)(c + 2) * (HD + 2) + 2 + d] * wgt[c + 2];
+            a3 += p[(size_t)(c + 3) * (HD + 2) + 2 + d] * wgt[c + 3];
         }
-        o[d] = from_float<T>(a * inv);
+        for (; c < n_chunks; ++c) a0 += p[(size_t)c * (HD + 2) + 2 + d] * wgt[c];
+        o[d] = from_float<T>(((a0 + a1) + (a2 + a3)) * inv);
     }
 }
 
@@ -346,6 +511,51 @@ JANIS_EXPORT int janis_attn_prefill(const void* qkv, const void* kv_src, int dty
     return launched("attn_prefill");
 }
 
+static int g_decode_kernel = 1;     // 1: staged through shared memory by bulk copies; 0: straight into registers
+
+// Which decode kernel janis_attn_decode launches (both give the same results up to rounding).
+JANIS_EXPORT void janis_attn_set_decode_kernel(int which) { g_decode_kernel = which ? 1 : 0; }
+
+// How often a decode CTA has given up waiting for its bulk copies since the library was loaded
+// (0 unless something is badly wrong).  Synchronises the device.
+JANIS_EXPORT int janis_attn_wait_timeouts() {
+    int n = -1;
+    if (cudaMemcpyFromSymbol(&n, g_wait_timeouts, sizeof(int)) != cudaSuccess) return -1;
+    return n;
+}
+
+template <typename T>
+static int launch_decode(const T* qkv, const T* kpool, const T* vpool, const int* page_table, int table_stride,
+                         const int* seq_slot, const int* seq_len, float* partial, T* out, int n_seq, int nq, int nkv,
+                         int q_row_heads, float scale, float cap, int window, int ring_len, int chunk, int max_chunks,
+                         cudaStream_t stream) {
+    const int rep = nq / nkv;
+    dim3 grid(max_chunks, nkv * ((rep + Geo<T>::RG - 1) / Geo<T>::RG), n_seq);
+    if (g_decode_kernel == 1) {
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 Staged<T>::SMEM_BYTES);
+            if (e != cudaSuccess) return fail("attn_decode: shared memory of %d bytes refused: %s", Staged<T>::SMEM_BYTES,
+                                              cudaGetErrorString(e));
+            configured = true;
+        }
+        attn_decode_staged_kernel<T><<<grid, ATTN_WARPS * 32, Staged<T>::SMEM_BYTES, stream>>>(
+            qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv, q_row_heads, scale, cap,
+            window, ring_len, chunk);
+    } else {
+        attn_decode_kernel<T><<<grid, ATTN_WARPS * 32, 0, stream>>>(qkv, kpool, vpool, page_table, table_stride, seq_slot,
+                                                                   seq_len, partial, nq, nkv, q_row_heads, scale, cap,
+                                                                   window, ring_len, chunk);
+    }
+    if (launched("attn_decode")) return 1;
+    dim3 mgrid(n_seq, nq);
+    const int mthreads = HD < 256 ? (HD < 32 ? 32 : HD) : 256;
+    attn_merge_kernel<T><<<mgrid, mthreads, max_chunks * sizeof(float), stream>>>(partial, seq_slot, seq_len, out, nq,
+                                                                                   max_chunks, window, chunk);
+    return launched("attn_merge");
+}
+
 JANIS_EXPORT int janis_attn_decode(const void* qkv, const void* kpool, const void* vpool, int dtype,
                                    const int* page_table, int table_stride, const int* seq_slot,
                                    const int* seq_len, float* partial, long long partial_floats, void* out,
@@ -362,29 +572,16 @@ JANIS_EXPORT int janis_attn_decode(const void* qkv, const void* kpool, const voi
         return fail("attn_decode: scratch of %lld floats is too small, %lld needed", partial_floats,
                     janis_attn_decode_scratch(n_seq, nq, max_chunks));
     if (n_seq > 65535) return fail("attn_decode: too many sequences (%d)", n_seq);
-    const int rep = nq / nkv;
-    dim3 mgrid(n_seq, nq);
-    const int mthreads = HD < 256 ? (HD < 32 ? 32 : HD) : 256;
-    if (dtype == JANIS_F32) {
-        dim3 grid(max_chunks, nkv * ((rep + Geo<float>::RG - 1) / Geo<float>::RG), n_seq);
-        attn_decode_kernel<float><<<grid, ATTN_WARPS * 32, 0, stream>>>(
-            (const float*)qkv, (const float*)kpool, (const float*)vpool, page_table, table_stride, seq_slot, seq_len,
-            partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk);
-        if (launched("attn_decode")) return 1;
-        attn_merge_kernel<float><<<mgrid, mthreads, 0, stream>>>(partial, seq_slot, seq_len, (float*)out, nq,
-                                                                  max_chunks, window, chunk);
-    } else if (dtype == JANIS_BF16) {
-        dim3 grid(max_chunks, nkv * ((rep + Geo<bf16>::RG - 1) / Geo<bf16>::RG), n_seq);
-        attn_decode_kernel<bf16><<<grid, ATTN_WARPS * 32, 0, stream>>>(
-            (const bf16*)qkv, (const bf16*)kpool, (const bf16*)vpool, page_table, table_stride, seq_slot, seq_len,
-            partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk);
-        if (launched("attn_decode")) return 1;
-        attn_merge_kernel<bf16><<<mgrid, mthreads, 0, stream>>>(partial, seq_slot, seq_len, (bf16*)out, nq,
-                                                                 max_chunks, window, chunk);
-    } else {
-        return fail("attn_decode: unknown dtype %d", dtype);
-    }
-    return launched("attn_merge");
+    if (max_chunks > 8192) return fail("attn_decode: too many chunks (%d)", max_chunks);
+    if (dtype == JANIS_F32)
+        return launch_decode<float>((const float*)qkv, (const float*)kpool, (const float*)vpool, page_table, table_stride,
+                                    seq_slot, seq_len, partial, (float*)out, n_seq, nq, nkv, q_row_heads, scale, cap,
+                                    window, ring_len, chunk, max_chunks, stream);
+    if (dtype == JANIS_BF16)
+        return launch_decode<bf16>((const bf16*)qkv, (const bf16*)kpool, (const bf16*)vpool, page_table, table_stride,
+                                   seq_slot, seq_len, partial, (bf16*)out, n_seq, nq, nkv, q_row_heads, scale, cap,
+                                   window, ring_len, chunk, max_chunks, stream);
+    return fail("attn_decode: unknown dtype %d", dtype);
 }
 
 JANIS_EXPORT const char* janis_last_error() { return error_buffer(); }

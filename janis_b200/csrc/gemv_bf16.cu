@@ -3,16 +3,24 @@
 // is the 16-row operand of mma.sync.m16n8k16 and the batch rows are the 8-wide
 // operand: every weight byte is read once, whatever M is.
 //
-// One CTA owns 16 rows of W; its warps split K between them in blocks of 32 and
-// the partial sums are added in warp order through shared memory, so a result
-// does not depend on the grid.  Each thread reads 16 contiguous bytes of two rows
-// of W straight into registers; the k order inside a block of 32 is permuted the
+// A tile of 16 rows of W belongs to one CTA, or to a thread-block cluster of CL CTAs
+// when N is small (the o and down projections have few rows and long K): the warps of
+// the cluster split K between them in blocks of 32, each CTA adds its warps' partial
+// sums in warp order in its own shared memory, and CTA 0 of the cluster adds the CTAs'
+// sums in rank order through distributed shared memory.  So more SMs pull on the same
+// rows without any scratch in global memory, and a result does not depend on the grid
+// beyond the fixed order of that sum.  Each thread reads 16 contiguous bytes of two
+// rows of W straight into registers; the k order inside a block of 32 is permuted the
 // same way for both operands, which leaves the dot product unchanged.
 //
 // Epilogues: none; gated activation over rows of W that alternate 8 gate rows and
 // 8 up rows (one mma tile then holds matching pairs); cap * tanh(v / cap).
 // Accumulation is float; the output is bfloat16 or float.  K must be a multiple of 8.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace janis {
 
@@ -37,14 +45,17 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read once: do 
     return v;
 }
 
-template <int MT, int U, typename TO>
+template <int MT, int U, int CL, typename TO>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __restrict__ out, int M, int N,
                  int K, int epi, float cap) {
     __shared__ float red[GEMV_WARPS][MT][32][4];
+    __shared__ float cta_sum[MT * 128];        // this CTA's sum over its warps; read by CTA 0 of the cluster
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.x * 16;
+    const int rank = CL > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int tile = blockIdx.x / CL;
+    const int r0 = tile * 16;
     // rows past the end read the last row; their results are never stored
     const int row_lo = min(r0 + g, N - 1), row_hi = min(r0 + g + 8, N - 1);
     const bf16* wlo = W + (size_t)row_lo * K + t * 8;
@@ -63,12 +74,13 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
 
+    constexpr int SPLIT = GEMV_WARPS * CL;     // warps that share the K of a tile
     const int nblk = (K + 31) / 32;
-    for (int kb = warp; kb < nblk; kb += GEMV_WARPS * U) {
+    for (int kb = rank * GEMV_WARPS + warp; kb < nblk; kb += SPLIT * U) {
         uint4 a_lo[U], a_hi[U], b[U][MT];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int k0 = (kb + u * GEMV_WARPS) * 32;
+            const int k0 = (kb + u * SPLIT) * 32;
             const bool in = k0 + t * 8 < K;          // K % 8 == 0: a 16-byte piece is all in or all out
             a_lo[u] = in ? ldg_stream(wlo + k0) : make_uint4(0, 0, 0, 0);
             a_hi[u] = in ? ldg_stream(whi + k0) : make_uint4(0, 0, 0, 0);
@@ -89,20 +101,43 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
 #pragma unroll
         for (int c = 0; c < 4; ++c) red[warp][i][lane][c] = acc[i][c];
     __syncthreads();
+    // the CTA's sum, warps in index order; layout [tile i][lane][c]
+    for (int idx = threadIdx.x; idx < MT * 128; idx += blockDim.x) {
+        const int i = idx / 128, ln = (idx / 4) % 32, c = idx % 4;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GEMV_WARPS; ++w) v += red[w][i][ln][c];
+        cta_sum[idx] = v;
+    }
+    if (CL > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                              // every CTA's sum is in its shared memory
+        if (rank == 0) {
+            for (int idx = threadIdx.x; idx < MT * 128; idx += blockDim.x) {
+                float v = cta_sum[idx];
+#pragma unroll
+                for (int r = 1; r < CL; ++r) v += cluster.map_shared_rank(cta_sum, r)[idx];   // rank order
+                red[0][idx / 128][(idx / 4) % 32][idx % 4] = v;
+            }
+        }
+        cluster.sync();                              // nobody leaves while its shared memory is being read
+        if (rank != 0) return;
+    } else {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < MT * 128; idx += blockDim.x)
+            red[0][idx / 128][(idx / 4) % 32][idx % 4] = cta_sum[idx];
+    }
+    __syncthreads();
+    const float (*tot)[32][4] = red[0];             // the tile's full sums
 
     if (epi == EPI_GATED_GELU || epi == EPI_GATED_SILU) {
         // rows g of the tile are gate rows, rows g + 8 the matching up rows
         const int I = N / 2;
         for (int idx = threadIdx.x; idx < MT * 32 * 2; idx += blockDim.x) {
             const int i = idx / 64, ln = (idx / 2) % 32, p = idx % 2;
-            float gate = 0.f, up = 0.f;
-#pragma unroll
-            for (int w = 0; w < GEMV_WARPS; ++w) {
-                gate += red[w][i][ln][p];
-                up += red[w][i][ln][p + 2];
-            }
+            const float gate = tot[i][ln][p], up = tot[i][ln][p + 2];
             const int m = i * 8 + (ln & 3) * 2 + p;
-            const int j = blockIdx.x * 8 + (ln >> 2);
+            const int j = tile * 8 + (ln >> 2);
             if (m < M && j < I) {
                 const float a = epi == EPI_GATED_GELU ? gelu_tanh(gate) : gate / (1.0f + expf(-gate));
                 out[(size_t)m * I + j] = from_float<TO>(a * up);
@@ -112,9 +147,7 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
     }
     for (int idx = threadIdx.x; idx < MT * 32 * 4; idx += blockDim.x) {
         const int i = idx / 128, ln = (idx / 4) % 32, c = idx % 4;
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < GEMV_WARPS; ++w) v += red[w][i][ln][c];
+        float v = tot[i][ln][c];
         const int m = i * 8 + (ln & 3) * 2 + (c & 1);
         const int n = r0 + (ln >> 2) + (c >> 1) * 8;
         if (m < M && n < N) {
@@ -128,20 +161,47 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
 
 using namespace janis;
 
-template <int MT, int U>
-static int launch_gemv(const bf16* x, const bf16* W, void* out, int out_dtype, int M, int N, int K, int epi,
-                       float cap, cudaStream_t stream) {
-    const int grid = (N + 15) / 16;
-    if (out_dtype == JANIS_BF16)
-        gemv_bf16_kernel<MT, U, bf16><<<grid, GEMV_WARPS * 32, 0, stream>>>(x, W, (bf16*)out, M, N, K, epi, cap);
-    else
-        gemv_bf16_kernel<MT, U, float><<<grid, GEMV_WARPS * 32, 0, stream>>>(x, W, (float*)out, M, N, K, epi, cap);
+template <int MT, int U, int CL, typename TO>
+static int launch_one(const bf16* x, const bf16* W, TO* out, int M, int N, int K, int epi, float cap,
+                      cudaStream_t stream) {
+    const int tiles = (N + 15) / 16;
+    if (CL == 1) {
+        gemv_bf16_kernel<MT, U, 1, TO><<<tiles, GEMV_WARPS * 32, 0, stream>>>(x, W, out, M, N, K, epi, cap);
+        return launched("gemv_bf16");
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * CL);
+    cfg.blockDim = dim3(GEMV_WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<MT, U, CL, TO>, x, W, out, M, N, K, epi, cap);
+    if (e != cudaSuccess) return fail("gemv_bf16: cluster launch failed: %s", cudaGetErrorString(e));
     return launched("gemv_bf16");
 }
 
-// x [M, K] bf16, W [N, K] bf16, out [M, N] (or [M, N/2] with a gated epilogue)
+template <int MT, int U>
+static int launch_gemv(const bf16* x, const bf16* W, void* out, int out_dtype, int M, int N, int K, int epi,
+                       float cap, int cluster, cudaStream_t stream) {
+#define JANIS_GEMV(CL)                                                                                          \
+    (out_dtype == JANIS_BF16 ? launch_one<MT, U, CL, bf16>(x, W, (bf16*)out, M, N, K, epi, cap, stream)          \
+                             : launch_one<MT, U, CL, float>(x, W, (float*)out, M, N, K, epi, cap, stream))
+    if (cluster >= 4) return JANIS_GEMV(4);
+    if (cluster >= 2) return JANIS_GEMV(2);
+    return JANIS_GEMV(1);
+#undef JANIS_GEMV
+}
+
+// x [M, K] bf16, W [N, K] bf16, out [M, N] (or [M, N/2] with a gated epilogue).
+// cluster: CTAs that share a tile's K (1, 2 or 4); 0 lets the kernel choose from N and K.
 JANIS_EXPORT int janis_gemv_bf16(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K,
-                                 int epi, float cap, cudaStream_t stream) {
+                                 int epi, float cap, int cluster, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64) return fail("gemv_bf16: at most 64 rows, found %d", M);
     if (K <= 0 || K % 8) return fail("gemv_bf16: K must be a positive multiple of 8, found %d", K);
@@ -149,11 +209,18 @@ JANIS_EXPORT int janis_gemv_bf16(const void* x, const void* W, void* out, int ou
     if ((epi == EPI_GATED_GELU || epi == EPI_GATED_SILU) && N % 16)
         return fail("gemv_bf16: a gated epilogue needs N to be a multiple of 16, found %d", N);
     if (epi < 0 || epi > 3) return fail("gemv_bf16: unknown epilogue %d", epi);
+    if (cluster < 0 || cluster > 4) return fail("gemv_bf16: cluster must be 0, 1, 2 or 4, found %d", cluster);
     if (((uintptr_t)x | (uintptr_t)W) & 15) return fail("gemv_bf16: operands must be 16-byte aligned");
+    if (cluster == 0) {
+        // enough CTAs to fill the GPU a few times over, as long as every warp keeps some blocks of K
+        const int tiles = (N + 15) / 16, nblk = (K + 31) / 32;
+        cluster = 1;
+        while (cluster < 4 && tiles * cluster < 600 && nblk >= GEMV_WARPS * cluster * 2 * 2) cluster *= 2;
+    }
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-    if (M <= 8) return launch_gemv<1, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, stream);
-    if (M <= 16) return launch_gemv<2, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, stream);
-    if (M <= 32) return launch_gemv<4, 2>(xp, wp, out, out_dtype, M, N, K, epi, cap, stream);
-    return launch_gemv<8, 1>(xp, wp, out, out_dtype, M, N, K, epi, cap, stream);
+    if (M <= 8) return launch_gemv<1, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
+    if (M <= 16) return launch_gemv<2, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
+    if (M <= 32) return launch_gemv<4, 2>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
+    return launch_gemv<8, 1>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
 }

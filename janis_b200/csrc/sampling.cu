@@ -59,9 +59,46 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
     const float* row = logits + (size_t)blockIdx.x * V;
     float v = -INFINITY;
     int i = 0x7fffffff;
-    for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    // four independent loads per round keep the memory pipe busy (one dependent load per round is
+    // bound by latency); a thread sees its ids in ascending order, so `>` keeps the lowest id
+    int j = threadIdx.x;
+    if ((V & 3) == 0 && (((uintptr_t)row) & 15) == 0) {
+        // 16-byte loads, two in flight per round; within a load the ids ascend, across rounds too
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int V4 = V >> 2;
+        int q = threadIdx.x;
+        for (; q + (int)blockDim.x < V4; q += 2 * blockDim.x) {
+            const float4 a = row4[q], b = row4[q + blockDim.x];
+            const int ja = q * 4, jb = (q + blockDim.x) * 4;
+            if (a.x > v) { v = a.x; i = ja; }
+            if (a.y > v) { v = a.y; i = ja + 1; }
+            if (a.z > v) { v = a.z; i = ja + 2; }
+            if (a.w > v) { v = a.w; i = ja + 3; }
+            if (b.x > v) { v = b.x; i = jb; }
+            if (b.y > v) { v = b.y; i = jb + 1; }
+            if (b.z > v) { v = b.z; i = jb + 2; }
+            if (b.w > v) { v = b.w; i = jb + 3; }
+        }
+        for (; q < V4; q += blockDim.x) {
+            const float4 a = row4[q];
+            const int ja = q * 4;
+            if (a.x > v) { v = a.x; i = ja; }
+            if (a.y > v) { v = a.y; i = ja + 1; }
+            if (a.z > v) { v = a.z; i = ja + 2; }
+            if (a.w > v) { v = a.w; i = ja + 3; }
+        }
+        j = V;                                             // nothing left for the scalar loops
+    }
+    for (; j + 3 * (int)blockDim.x < V; j += 4 * blockDim.x) {
+        const float x0 = row[j], x1 = row[j + blockDim.x], x2 = row[j + 2 * blockDim.x], x3 = row[j + 3 * blockDim.x];
+        if (x0 > v) { v = x0; i = j; }                       // NaN never wins
+        if (x1 > v) { v = x1; i = j + blockDim.x; }
+        if (x2 > v) { v = x2; i = j + 2 * blockDim.x; }
+        if (x3 > v) { v = x3; i = j + 3 * blockDim.x; }
+    }
+    for (; j < V; j += blockDim.x) {
         const float x = row[j];
-        if (x > v || (x == v && j < i)) { v = x; i = j; }   // NaN never wins
+        if (x > v) { v = x; i = j; }
     }
     float bv;
     int bi;

@@ -53,6 +53,7 @@ class DecoderModel:
         self.hidden = embedding.hidden
         self.vocab = head.vocab
         self._check_schedule()
+        self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.parts())
 
     def _check_schedule(self) -> None:
         if not self.schedule:

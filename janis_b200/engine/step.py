@@ -58,7 +58,7 @@ class Stepper:
         self.model, self.cache, self.rt = model, cache, rt
         self.ws = Workspace(rt.device)
         self.max_step_tokens = max(1, int(max_step_tokens))
-        self.use_graphs = bool(use_graphs) and torch.device(rt.device).type == "cuda"
+        self.use_graphs = bool(use_graphs) and torch.device(rt.device).type == "cuda" and model.graph_safe
         self._graphs: dict[tuple[int, int], tuple] = {}
         self._decode_meta = None
         self._decode_logits = None

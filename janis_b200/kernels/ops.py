@@ -53,7 +53,7 @@ def core():
         lib.janis_gated_act.argtypes = [P, P, I, I, I, I, I, P]
         lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
         lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
-        lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, P]
+        lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
         lib.janis_argmax.argtypes = [P, P, I, I, P]
         lib.janis_sample.argtypes = [P, P, P, I, I, F, F, c_ulonglong, P, P, P]
         lib.janis_repeat_penalty.argtypes = [P, P, I, I, I, F, P]
@@ -74,6 +74,9 @@ def attention_lib(head_dim: int):
         lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P]
         lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
         lib.janis_attn_prefill_mma.argtypes = [P, P, P, P, I, I, P, I, I, I, I, I, F, F, I, P]
+        lib.janis_attn_set_decode_kernel.argtypes = [I]
+        lib.janis_attn_set_decode_kernel.restype = None
+        lib.janis_attn_wait_timeouts.restype = I
         if lib.janis_attn_head_dim() != head_dim:
             raise KernelError(f"attention library for head size {head_dim} reports {lib.janis_attn_head_dim()}")
         _attn[head_dim] = lib
@@ -224,16 +227,17 @@ def gemm_f32(x, w, out, cap: float = 0.0):
     return out
 
 
-def gemv_bf16(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0):
+def gemv_bf16(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0, cluster: int = 0):
     """out = x[M<=64, K] w[N, K]^T, bfloat16 operands, float accumulation; out bfloat16 or float32
-    [M, N], or [M, N/2] with a gated epilogue (rows of w alternate 8 gate rows and 8 up rows)."""
+    [M, N], or [M, N/2] with a gated epilogue (rows of w alternate 8 gate rows and 8 up rows).
+    cluster: how many CTAs of a thread-block cluster share the K of a tile (1, 2, 4; 0 = chosen from N, K)."""
     M, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if epilogue in (EPI_GATED_GELU, EPI_GATED_SILU) else N
     lib = core()
     _check(lib, lib.janis_gemv_bf16(_t(x, "x", torch.bfloat16, (M, K)), _t(w, "w", torch.bfloat16, (N, K)),
                                     _t(out, "out", _FLOATS, (M, n_out)), _DT[out.dtype], M, N, K, epilogue,
-                                    float(cap), _stream()))
+                                    float(cap), int(cluster), _stream()))
     return out
 
 
@@ -310,6 +314,17 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
                                            qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),
                                            int(window), _stream()))
     return out
+
+
+def attn_set_decode_kernel(hd: int, staged: bool) -> None:
+    """Choose the decode kernel of the head size's library: staged through shared memory by bulk copies
+    (the default) or straight from global memory into registers."""
+    attention_lib(hd).janis_attn_set_decode_kernel(1 if staged else 0)
+
+
+def attn_wait_timeouts(hd: int) -> int:
+    """How often a decode CTA gave up waiting for its bulk copies (0 in a healthy run); synchronises."""
+    return int(attention_lib(hd).janis_attn_wait_timeouts())
 
 
 def attn_decode_scratch_floats(n_seq: int, nq: int, hd: int, max_chunks: int) -> int:

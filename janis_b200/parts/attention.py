@@ -73,8 +73,10 @@ class SoftmaxAttention(Mixer):
     def _decode_geometry(self, ctx: StepContext, sm_count: int):
         bound = max(ctx.len_bound, 1)
         span = min(bound, self.window) if self.window else bound
+        # the largest chunk that still leaves about 1.5 CTAs per SM: long chunks amortise the staging
+        # pipeline's start, enough CTAs keep every SM pulling on the cache
         chunk = 64
-        while chunk < 1024 and ctx.n_seq * self.n_kv_heads * ((span + 2 * chunk - 1) // (2 * chunk)) >= 2 * sm_count:
+        while chunk < 1024 and ctx.n_seq * self.n_kv_heads * ((span + 2 * chunk - 1) // (2 * chunk)) >= (3 * sm_count) // 2:
             chunk *= 2
         max_chunks = (bound + chunk - 1) // chunk
         if self.window:

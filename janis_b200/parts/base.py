@@ -119,6 +119,10 @@ class StepContext:
 
 
 class Part:
+    # False for a part whose step cannot be recorded into a CUDA graph (it synchronises, allocates by
+    # data-dependent sizes, or copies from the host); decode steps are then launched kernel by kernel.
+    graph_safe = True
+
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}
 

@@ -98,7 +98,7 @@ def gemm_f32(x, w, out, cap=0.0):
     return out
 
 
-def gemv_bf16(x, w, out, epilogue=EPI_NONE, cap=0.0):
+def gemv_bf16(x, w, out, epilogue=EPI_NONE, cap=0.0, cluster=0):
     v = x.double() @ w.double().T
     if epilogue in (EPI_GATED_GELU, EPI_GATED_SILU):
         M, N = v.shape

@@ -204,6 +204,20 @@ def test_gemv_bf16(dout, M, N, K):
     close(out, want, tol_of(dout) if dout == torch.bfloat16 else 1e-4, "gemv_bf16")
 
 
+@pytest.mark.parametrize("cluster", [1, 2, 4])
+@pytest.mark.parametrize("M,N,K", [(1, 2304, 2048), (8, 2304, 9216), (20, 100, 64), (64, 48, 1032), (3, 16, 8)])
+def test_gemv_bf16_clusters_share_k(cluster, M, N, K):
+    """A tile's K split over the CTAs of a thread-block cluster and added through distributed shared
+    memory: the same product, whatever the cluster size (and K shorter than the cluster's reach)."""
+    x = rnd((M, K), torch.bfloat16, 50)
+    w = rnd((N, K), torch.bfloat16, 51, std=0.05)
+    out = torch.empty((M, N), dtype=torch.float32, device=dev())
+    ops().gemv_bf16(x, w, out, cluster=cluster)
+    want = torch.empty((M, N), dtype=torch.float64)
+    R.gemv_bf16(x.cpu(), w.cpu(), want)
+    close(out, want, 1e-4, f"gemv_bf16 cluster {cluster}")
+
+
 @pytest.mark.parametrize("M", [1, 5, 8, 12, 40, 64])
 @pytest.mark.parametrize("epi", [1, 3])
 @pytest.mark.parametrize("I,K", [(8, 16), (320, 96), (1000, 104)])
@@ -313,7 +327,8 @@ def test_attn_prefill_reads_another_layers_keys(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES)
 @pytest.mark.parametrize("window,ring,chunk", [(0, 0, 64), (0, 0, 256), (16, 64, 64), (100, 128, 64), (128, 128, 128)])
-def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk):
+@pytest.mark.parametrize("staged", [True, False])
+def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, staged):
     # sequences of unequal lengths in scattered pages; one padding row; lengths at page and chunk edges
     lens = [1, 64, 65, 300, 7, 129]
     slots = [3, 0, 5, 1, -1, 4]
@@ -333,8 +348,13 @@ def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk):
     scratch = torch.empty(ops().attn_decode_scratch_floats(n_seq, nq, hd, max_chunks), dtype=torch.float32, device=d)
     out = torch.full((n_seq, nq * hd), 7.0, dtype=dtype, device=d)
     scale, cap = 1.0 / math.sqrt(hd), 30.0
-    ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
-                      window, ring, chunk, max_chunks)
+    ops().attn_set_decode_kernel(hd, staged)
+    try:
+        ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
+                          window, ring, chunk, max_chunks)
+    finally:
+        ops().attn_set_decode_kernel(hd, True)
+    assert ops().attn_wait_timeouts(hd) == 0
     want = torch.empty((n_seq, nq * hd), dtype=torch.float64)
     R.attn_decode(qkv.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, scale, cap, window,
                   ring, chunk, max_chunks)
