@@ -29,21 +29,23 @@ namespace janis {
 constexpr int HD = JANIS_HEAD_DIM;
 constexpr int ATTN_WARPS = 4;
 
-constexpr int pow2_divisor_up_to_8(int n) { return n % 8 == 0 ? 8 : (n % 4 == 0 ? 4 : (n % 2 == 0 ? 2 : 1)); }
+constexpr int pow2_divisor_up_to(int n, int cap) {
+    return (cap >= 16 && n % 16 == 0) ? 16 : (n % 8 == 0 ? 8 : (n % 4 == 0 ? 4 : (n % 2 == 0 ? 2 : 1)));
+}
 constexpr int clamp_int(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
 
-template <typename T> struct Geo {
+template <typename T, int LMAX = 8, int BUDGET = 64> struct Geo {
     static constexpr int VEC = Vec16<T>::N;                 // elements in 16 bytes
     static constexpr int NCHUNK = HD / VEC;                 // 16-byte pieces of a key
-    static constexpr int LPK = pow2_divisor_up_to_8(NCHUNK);  // lanes that share a key
+    static constexpr int LPK = pow2_divisor_up_to(NCHUNK, LMAX);  // lanes that share a key (at most LMAX)
     static constexpr int CPL = NCHUNK / LPK;                // pieces per lane
     static constexpr int EPL = CPL * VEC;                   // elements per lane
     static constexpr int KPW = 32 / LPK;                    // keys a warp handles at a time
-    static constexpr int RG = clamp_int(64 / EPL, 1, 8);    // query heads handled together
+    static constexpr int RG = clamp_int(BUDGET / EPL, 1, 8);  // query heads handled together (register budget)
 };
 
-template <typename T> struct Lane {
-    typedef Geo<T> G;
+template <typename T, int LMAX = 8, int BUDGET = 64> struct Lane {
+    typedef Geo<T, LMAX, BUDGET> G;
     float q[G::RG][G::EPL];
     float acc[G::RG][G::EPL];
     float m[G::RG], l[G::RG];
@@ -199,10 +201,11 @@ __device__ __forceinline__ void chunk_range(int len, int window, int chunk, int&
 }
 
 // What a decode CTA leaves for the merge: the warps' states folded in warp order.
-template <typename T>
-__device__ __forceinline__ void write_partial(Lane<T>& st, float (*sm)[Geo<T>::RG][HD + 2], float* __restrict__ partial,
-                                              int s, int nq, int h0, int nh_here, int warp, int lig, int grp) {
-    typedef Geo<T> G;
+template <typename T, int LMAX, int BUDGET, int WARPS>
+__device__ __forceinline__ void write_partial(Lane<T, LMAX, BUDGET>& st, float (*sm)[Geo<T, LMAX, BUDGET>::RG][HD + 2],
+                                              float* __restrict__ partial, int s, int nq, int h0, int nh_here, int warp,
+                                              int lig, int grp) {
+    typedef Geo<T, LMAX, BUDGET> G;
     st.merge_groups();
     if (grp == 0) {
 #pragma unroll
@@ -221,13 +224,13 @@ __device__ __forceinline__ void write_partial(Lane<T>& st, float (*sm)[Geo<T>::R
         const int r = idx / (HD + 2), d = idx % (HD + 2);
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < ATTN_WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
+        for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
         float v;
         if (d == 0) v = mx;
         else {
             v = 0.f;
 #pragma unroll
-            for (int w = 0; w < ATTN_WARPS; ++w) {
+            for (int w = 0; w < WARPS; ++w) {
                 const float mw = sm[w][r][0];
                 if (mw != -INFINITY) v += sm[w][r][d] * expf(mw - mx);
             }
@@ -278,7 +281,7 @@ attn_decode_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool, const
         const size_t off = (((size_t)page * nkv + kvh) * JANIS_PAGE + idx % JANIS_PAGE) * HD;
         st.key(kpool + off, vpool + off, valid, cap, lig);
     }
-    write_partial<T>(st, sm, partial, s, nq, h0, nh_here, warp, lig, grp);
+    write_partial<T, 8, 64, ATTN_WARPS>(st, sm, partial, s, nq, h0, nh_here, warp, lig, grp);
 }
 
 // ---------------------------------------------------------------------------
@@ -297,11 +300,21 @@ __device__ int g_wait_timeouts = 0;
 
 constexpr int pow2_floor(int n) { return n >= 64 ? 64 : (n >= 32 ? 32 : (n >= 16 ? 16 : (n >= 8 ? 8 : (n >= 4 ? 4 : (n >= 2 ? 2 : 1))))); }
 constexpr int max_int(int a, int b) { return a > b ? a : b; }
+constexpr int pow2_ceil(int n) { return n <= 1 ? 1 : (n <= 2 ? 2 : (n <= 4 ? 4 : (n <= 8 ? 8 : (n <= 16 ? 16 : 32)))); }
+
+#ifndef JANIS_STAGES
+#define JANIS_STAGES 3            // stages of the bulk-copy pipeline
+#endif
+#ifndef JANIS_STAGE_BUDGET
+#define JANIS_STAGE_BUDGET 32768  // bytes of keys and values a stage aims at
+#endif
 
 template <typename T> struct Staged {
-    static constexpr int STAGES = 3;
-    static constexpr int KEYS_PER_PASS = ATTN_WARPS * Geo<T>::KPW;        // keys the CTA handles at a time
-    static constexpr int TILE = max_int(KEYS_PER_PASS, pow2_floor(32768 / (2 * HD * (int)sizeof(T))));
+    static constexpr int STAGES = JANIS_STAGES;
+    static constexpr int LMAX = 16, BUDGET = 32;
+    static constexpr int WARPS = clamp_int(JANIS_PAGE / Geo<T, LMAX>::KPW, 1, 8);   // a pass never exceeds a page
+    static constexpr int KEYS_PER_PASS = WARPS * Geo<T, LMAX>::KPW;        // keys the CTA handles at a time
+    static constexpr int TILE = max_int(KEYS_PER_PASS, pow2_floor(JANIS_STAGE_BUDGET / (2 * HD * (int)sizeof(T))));
     static constexpr int TILE_BYTES = TILE * HD * (int)sizeof(T);
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;                      // keys, then values
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;
@@ -321,6 +334,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, int byt
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// m16n8k16 whose 16-row operand has rows 8..15 zero (a1 = a3 = 0): d += A B
+__device__ __forceinline__ void mma_rows8(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    const uint32_t z = 0u;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
 // true when the phase with this parity has completed; false after a bounded number of tries
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (int it = 0; it < (1 << 22); ++it) {
@@ -336,15 +358,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(ATTN_WARPS * 32)
+__global__ void __launch_bounds__(Staged<T>::WARPS * 32)
 attn_decode_staged_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool, const T* __restrict__ vpool,
                           const int* __restrict__ page_table, int table_stride, const int* __restrict__ seq_slot,
                           const int* __restrict__ seq_len, float* __restrict__ partial, int nq, int nkv,
                           int q_row_heads, float scale, float cap, int window, int ring_len, int chunk) {
-    typedef Geo<T> G;
     typedef Staged<T> S;
+    typedef Geo<T, S::LMAX, S::BUDGET> G;
     extern __shared__ __align__(128) unsigned char stage_mem[];
-    __shared__ float sm[ATTN_WARPS][G::RG][HD + 2];
     __shared__ __align__(8) unsigned long long full[S::STAGES];
     const int s = blockIdx.z;
     const int slot = seq_slot[s];
@@ -391,7 +412,7 @@ attn_decode_staged_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool
     if (threadIdx.x == 0)
         for (int i = 0; i < S::STAGES && i < n_tiles; ++i) issue(i);
 
-    Lane<T> st;
+    Lane<T, S::LMAX, S::BUDGET> st;
     st.init();
     const T* qrow = qkv + (size_t)s * q_row_heads * HD;
 #pragma unroll
@@ -418,7 +439,256 @@ attn_decode_staged_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool
         }
         if (threadIdx.x == 0 && i + S::STAGES < n_tiles) issue(i + S::STAGES);
     }
-    write_partial<T>(st, sm, partial, s, nq, h0, nh_here, warp, lig, grp);
+    // every tile has been consumed and nothing is in flight: the stages' memory now holds the warps' states
+    static_assert(sizeof(float) * S::WARPS * G::RG * (HD + 2) <= S::SMEM_BYTES, "the merge does not fit the stages");
+    float (*sm)[G::RG][HD + 2] = reinterpret_cast<float (*)[G::RG][HD + 2]>(stage_mem);
+    write_partial<T, S::LMAX, S::BUDGET, S::WARPS>(st, sm, partial, s, nq, h0, nh_here, warp, lig, grp);
+}
+
+// ---------------------------------------------------------------------------
+// Decode attention in bfloat16 with the scores on the tensor cores.  The kernels above spend
+// most of their issue slots on the softmax of each key, repeated in every lane that shares
+// the key; here the work of a tile is spread differently:
+//   scores : S = Q K^T by mma.sync.m16n8k16.  The rows of the 16-row operand are the query
+//            heads of this key/value head (RB <= 8 of them, the rest zero), the 8 columns are
+//            8 keys of the staged tile.  Each thread reads 16 contiguous bytes of a key and
+//            uses them for two k-steps; the query fragments are permuted the same way.
+//   softmax: the 8 x RB scores of a warp sit one pair per lane, so cap, mask, max, exp run
+//            once per score, not once per lane group.
+//   values : every lane owns 8 features (16 bytes) of the head and adds p * v for each key of
+//            its warp; p comes by shuffle from the lane that holds it.
+// Staging (bulk copies, mbarriers, bounded waits), chunking and the merge are those of the
+// staged kernel.  Needs a tile of 32 or 64 keys: head sizes up to 256.
+// ---------------------------------------------------------------------------
+struct MmaDecode {
+    static constexpr int WARPS = 4;
+    static constexpr int STAGES = JANIS_STAGES;
+    static constexpr int TILE = HD <= 128 ? 64 : 32;                 // keys per stage
+    static constexpr int NT = TILE / 32;                              // 8-key column tiles per warp and stage
+    static constexpr int TILE_BYTES = TILE * HD * 2;
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int KB = (HD + 31) / 32;                         // blocks of 32 features
+    static constexpr int CH = HD / 8;                                 // 16-byte pieces of a value row
+    static constexpr int CHL = CH >= 32 ? 32 : pow2_ceil(CH);         // lanes set aside for a value row (a power of two)
+    static constexpr int CPV = (CH + 31) / 32;                        // pieces per lane
+    static constexpr int KPI = 32 / CHL;                              // keys per load instruction
+    static constexpr bool OK = HD <= 256;
+};
+
+template <int RB>
+__global__ void __launch_bounds__(MmaDecode::WARPS * 32)
+attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
+                       const int* __restrict__ page_table, int table_stride, const int* __restrict__ seq_slot,
+                       const int* __restrict__ seq_len, float* __restrict__ partial, int nq, int nkv, int q_row_heads,
+                       float scale, float cap, int window, int ring_len, int chunk) {
+    typedef MmaDecode S;
+    extern __shared__ __align__(128) unsigned char stage_mem[];
+    __shared__ __align__(8) unsigned long long full[S::STAGES];
+    const int s = blockIdx.z;
+    const int slot = seq_slot[s];
+    if (slot < 0) return;
+    const int len = seq_len[s];
+    int lo, first_chunk, n_chunks;
+    chunk_range(len, window, chunk, lo, first_chunk, n_chunks);
+    if ((int)blockIdx.x >= n_chunks) return;
+    const int c = first_chunk + blockIdx.x;
+    const int k_begin = max(lo, c * chunk), k_end = min(len, (c + 1) * chunk);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int rep = nq / nkv;
+    const int groups = (rep + RB - 1) / RB;
+    const int kvh = blockIdx.y / groups, hg = blockIdx.y % groups;
+    const int h0 = kvh * rep + hg * RB;
+    const int nh_here = min(RB, rep - hg * RB);
+
+    const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(stage_mem);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(full);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S::STAGES; ++i) mbar_init(bar0 + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+    const int t_first = (k_begin / S::TILE) * S::TILE;
+    const int n_tiles = (k_end - t_first + S::TILE - 1) / S::TILE;
+    const int* table = page_table + (size_t)slot * table_stride;
+    auto issue = [&](int i) {
+        const int p0 = t_first + i * S::TILE;
+        const int idx = ring_len > 0 ? p0 % ring_len : p0;
+        const int page = table[idx / JANIS_PAGE];
+        const size_t off = (((size_t)page * nkv + kvh) * JANIS_PAGE + idx % JANIS_PAGE) * HD;
+        const int st_i = i % S::STAGES;
+        const uint32_t dst = stage0 + st_i * S::STAGE_BYTES, bar = bar0 + 8 * st_i;
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_expect_tx(bar, S::STAGE_BYTES);
+        bulk_load(dst, kpool + off, S::TILE_BYTES, bar);
+        bulk_load(dst + S::TILE_BYTES, vpool + off, S::TILE_BYTES, bar);
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < S::STAGES && i < n_tiles; ++i) issue(i);
+
+    // query fragments: row g of the 16-row operand is head h0 + g (zero beyond nh_here); a thread keeps, for
+    // each block of 32 features, the 8 features t*8 .. t*8+7 as the pairs that two k-steps want
+    uint32_t qf[S::KB][4];
+    {
+        const bf16* qrow = qkv + (size_t)s * q_row_heads * HD + (size_t)(h0 + g) * HD;
+#pragma unroll
+        for (int kb = 0; kb < S::KB; ++kb) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (g < nh_here && kb * 32 + t * 8 < HD) v = *reinterpret_cast<const uint4*>(qrow + kb * 32 + t * 8);
+            qf[kb][0] = v.x; qf[kb][1] = v.y; qf[kb][2] = v.z; qf[kb][3] = v.w;
+        }
+    }
+    // values: lane -> (key within a load instruction, 16-byte piece)
+    const int ksub = lane / S::CHL, piece = lane % S::CHL;
+    float acc[RB][S::CPV * 8];
+#pragma unroll
+    for (int r = 0; r < RB; ++r)
+#pragma unroll
+        for (int e = 0; e < S::CPV * 8; ++e) acc[r][e] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;          // of row g, the same in the four lanes that share it
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+
+    for (int i = 0; i < n_tiles; ++i) {
+        const int st_i = i % S::STAGES;
+        const bool landed = mbar_wait(bar0 + 8 * st_i, (i / S::STAGES) & 1);
+        if (landed) {
+            const unsigned char* ks = stage_mem + (size_t)st_i * S::STAGE_BYTES;
+            const unsigned char* vs = ks + S::TILE_BYTES;
+            const int kw = warp * 8 * S::NT;                     // this warp's first key in the tile
+            const int p0 = t_first + i * S::TILE + kw;           // its position
+            // ---- scores
+            float sc[S::NT][2];
+#pragma unroll
+            for (int nt = 0; nt < S::NT; ++nt) {
+                float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                const unsigned char* krow = ks + (size_t)(kw + nt * 8 + g) * HD * 2 + t * 16;
+#pragma unroll
+                for (int kb = 0; kb < S::KB; ++kb) {
+                    uint4 kv = make_uint4(0, 0, 0, 0);
+                    if (kb * 32 + t * 8 < HD) kv = *reinterpret_cast<const uint4*>(krow + kb * 64);
+                    mma_rows8(c0, qf[kb][0], qf[kb][1], kv.x, kv.y);
+                    mma_rows8(c1, qf[kb][2], qf[kb][3], kv.z, kv.w);
+                }
+                sc[nt][0] = c0[0] + c1[0];
+                sc[nt][1] = c0[1] + c1[1];
+            }
+            // ---- cap, mask, running maximum and sum of row g over this warp's keys
+            float mx = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < S::NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = p0 + nt * 8 + t * 2 + e;
+                    float v = sc[nt][e] * scale;
+                    if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+                    v = (j >= k_begin && j < k_end && g < nh_here) ? v : -INFINITY;
+                    sc[nt][e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = expf(m_run - m_use);               // exp(-inf) = 0 the first time
+            float psum = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < S::NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    sc[nt][e] = expf(sc[nt][e] - m_use);          // now the weight p of (row g, key)
+                    psum += sc[nt][e];
+                }
+            l_run = l_run * corr + psum;
+            m_run = m_new;
+            // ---- values: acc[r] = acc[r] * corr_r + sum over keys of p[r][key] * v[key]
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                const float cr = __shfl_sync(0xffffffffu, corr, r * 4);
+#pragma unroll
+                for (int e = 0; e < S::CPV * 8; ++e) acc[r][e] *= cr;
+            }
+#pragma unroll
+            for (int nt = 0; nt < S::NT; ++nt) {
+#pragma unroll
+                for (int j0 = 0; j0 < 8; j0 += S::KPI) {
+                    const int jk = j0 + ksub;                      // key of this lane, 0..7 within the column tile
+                    const int pos = p0 + nt * 8 + jk;
+                    const bool use = ksub < S::KPI && jk < 8 && pos >= k_begin && pos < k_end;
+                    float pw[RB];
+#pragma unroll
+                    for (int r = 0; r < RB; ++r) {               // p[r][jk] lives in lane r*4 + jk/2, register jk%2
+                        const float pe = __shfl_sync(0xffffffffu, sc[nt][0], r * 4 + ((jk & 7) >> 1));
+                        const float po = __shfl_sync(0xffffffffu, sc[nt][1], r * 4 + ((jk & 7) >> 1));
+                        pw[r] = (jk & 1) ? po : pe;
+                    }
+                    if (use) {
+#pragma unroll
+                        for (int cp = 0; cp < S::CPV; ++cp) {
+                            const int pc = piece + cp * 32;
+                            if (pc < S::CH) {
+                                float vf[8];
+                                Vec16<bf16>::load(reinterpret_cast<const bf16*>(vs + (size_t)(kw + nt * 8 + jk) * HD * 2) + pc * 8, vf);
+#pragma unroll
+                                for (int r = 0; r < RB; ++r)
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) acc[r][cp * 8 + e] = fmaf(pw[r], vf[e], acc[r][cp * 8 + e]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (!__syncthreads_and(landed ? 1 : 0)) {
+            if (threadIdx.x == 0) atomicAdd(&g_wait_timeouts, 1);
+            return;
+        }
+        if (threadIdx.x == 0 && i + S::STAGES < n_tiles) issue(i + S::STAGES);
+    }
+    // ---- this warp's state into shared memory (the stages are free now), then the warps in order
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+#pragma unroll
+    for (int o = S::CHL; o < 32; o <<= 1)                      // lanes that took different keys of a load
+#pragma unroll
+        for (int r = 0; r < RB; ++r)
+#pragma unroll
+            for (int e = 0; e < S::CPV * 8; ++e) acc[r][e] += __shfl_xor_sync(0xffffffffu, acc[r][e], o);
+    static_assert(sizeof(float) * S::WARPS * RB * (HD + 2) <= S::SMEM_BYTES, "the merge does not fit the stages");
+    float (*sm)[RB][HD + 2] = reinterpret_cast<float (*)[RB][HD + 2]>(stage_mem);
+    if (t == 0 && g < RB) { sm[warp][g][0] = m_run; sm[warp][g][1] = l_run; }
+    if (ksub == 0) {
+#pragma unroll
+        for (int r = 0; r < RB; ++r)
+#pragma unroll
+            for (int cp = 0; cp < S::CPV; ++cp) {
+                const int pc = piece + cp * 32;
+                if (pc < S::CH) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) sm[warp][r][2 + pc * 8 + e] = acc[r][cp * 8 + e];
+                }
+            }
+    }
+    __syncthreads();
+    const int max_chunks = gridDim.x;
+    for (int idx = threadIdx.x; idx < nh_here * (HD + 2); idx += blockDim.x) {
+        const int r = idx / (HD + 2), d = idx % (HD + 2);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < S::WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
+        float v;
+        if (d == 0) v = mx;
+        else {
+            v = 0.f;
+#pragma unroll
+            for (int w = 0; w < S::WARPS; ++w) {
+                const float mw = sm[w][r][0];
+                if (mw != -INFINITY) v += sm[w][r][d] * expf(mw - mx);
+            }
+        }
+        partial[(((size_t)s * nq + h0 + r) * max_chunks + blockIdx.x) * (HD + 2) + d] = v;
+    }
 }
 
 // Merge of the chunks in ascending order.  One CTA per (sequence, head): the chunks' weights
@@ -511,10 +781,11 @@ JANIS_EXPORT int janis_attn_prefill(const void* qkv, const void* kv_src, int dty
     return launched("attn_prefill");
 }
 
-static int g_decode_kernel = 1;     // 1: staged through shared memory by bulk copies; 0: straight into registers
+static int g_decode_kernel = 2;     // 2: staged, scores on the tensor cores (bfloat16, head sizes <= 256);
+                                    // 1: staged, CUDA cores; 0: straight from global memory into registers
 
 // Which decode kernel janis_attn_decode launches (both give the same results up to rounding).
-JANIS_EXPORT void janis_attn_set_decode_kernel(int which) { g_decode_kernel = which ? 1 : 0; }
+JANIS_EXPORT void janis_attn_set_decode_kernel(int which) { g_decode_kernel = which < 0 ? 0 : (which > 2 ? 2 : which); }
 
 // How often a decode CTA has given up waiting for its bulk copies since the library was loaded
 // (0 unless something is badly wrong).  Synchronises the device.
@@ -524,14 +795,56 @@ JANIS_EXPORT int janis_attn_wait_timeouts() {
     return n;
 }
 
+template <int RB>
+static int launch_decode_mma_rb(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table,
+                                int table_stride, const int* seq_slot, const int* seq_len, float* partial, int n_seq, int nq,
+                                int nkv, int q_row_heads, float scale, float cap, int window, int ring_len, int chunk,
+                                int max_chunks, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             MmaDecode::SMEM_BYTES);
+        if (e != cudaSuccess) return fail("attn_decode: shared memory of %d bytes refused: %s", MmaDecode::SMEM_BYTES,
+                                          cudaGetErrorString(e));
+        configured = true;
+    }
+    const int rep = nq / nkv;
+    dim3 grid(max_chunks, nkv * ((rep + RB - 1) / RB), n_seq);
+    attn_decode_mma_kernel<RB><<<grid, MmaDecode::WARPS * 32, MmaDecode::SMEM_BYTES, stream>>>(
+        qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv, q_row_heads, scale, cap, window,
+        ring_len, chunk);
+    return launched("attn_decode");
+}
+
+static int launch_decode_mma(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table, int table_stride,
+                             const int* seq_slot, const int* seq_len, float* partial, int n_seq, int nq, int nkv,
+                             int q_row_heads, float scale, float cap, int window, int ring_len, int chunk, int max_chunks,
+                             cudaStream_t stream) {
+    const int rep = nq / nkv;
+#define JANIS_RB(RB)                                                                                                   \
+    return launch_decode_mma_rb<RB>(qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, n_seq, nq, nkv, \
+                                    q_row_heads, scale, cap, window, ring_len, chunk, max_chunks, stream)
+    if (rep == 1) JANIS_RB(1);
+    if (rep == 2) JANIS_RB(2);
+    if (rep <= 4) JANIS_RB(4);
+    JANIS_RB(8);
+#undef JANIS_RB
+}
+
 template <typename T>
 static int launch_decode(const T* qkv, const T* kpool, const T* vpool, const int* page_table, int table_stride,
                          const int* seq_slot, const int* seq_len, float* partial, T* out, int n_seq, int nq, int nkv,
                          int q_row_heads, float scale, float cap, int window, int ring_len, int chunk, int max_chunks,
                          cudaStream_t stream) {
     const int rep = nq / nkv;
-    dim3 grid(max_chunks, nkv * ((rep + Geo<T>::RG - 1) / Geo<T>::RG), n_seq);
-    if (g_decode_kernel == 1) {
+    if (g_decode_kernel == 2 && sizeof(T) == 2 && MmaDecode::OK) {
+        if (launch_decode_mma((const bf16*)qkv, (const bf16*)kpool, (const bf16*)vpool, page_table, table_stride, seq_slot,
+                              seq_len, partial, n_seq, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, max_chunks,
+                              stream))
+            return 1;
+    } else if (g_decode_kernel >= 1) {
+        typedef Geo<T, Staged<T>::LMAX, Staged<T>::BUDGET> GS;
+        dim3 grid(max_chunks, nkv * ((rep + GS::RG - 1) / GS::RG), n_seq);
         static bool configured = false;
         if (!configured) {
             cudaError_t e = cudaFuncSetAttribute(attn_decode_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -540,15 +853,16 @@ static int launch_decode(const T* qkv, const T* kpool, const T* vpool, const int
                                               cudaGetErrorString(e));
             configured = true;
         }
-        attn_decode_staged_kernel<T><<<grid, ATTN_WARPS * 32, Staged<T>::SMEM_BYTES, stream>>>(
+        attn_decode_staged_kernel<T><<<grid, Staged<T>::WARPS * 32, Staged<T>::SMEM_BYTES, stream>>>(
             qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv, q_row_heads, scale, cap,
             window, ring_len, chunk);
     } else {
+        dim3 grid(max_chunks, nkv * ((rep + Geo<T>::RG - 1) / Geo<T>::RG), n_seq);
         attn_decode_kernel<T><<<grid, ATTN_WARPS * 32, 0, stream>>>(qkv, kpool, vpool, page_table, table_stride, seq_slot,
                                                                    seq_len, partial, nq, nkv, q_row_heads, scale, cap,
                                                                    window, ring_len, chunk);
     }
-    if (launched("attn_decode")) return 1;
+    if (!(g_decode_kernel == 2 && sizeof(T) == 2 && MmaDecode::OK) && launched("attn_decode")) return 1;
     dim3 mgrid(n_seq, nq);
     const int mthreads = HD < 256 ? (HD < 32 ? 32 : HD) : 256;
     attn_merge_kernel<T><<<mgrid, mthreads, max_chunks * sizeof(float), stream>>>(partial, seq_slot, seq_len, out, nq,

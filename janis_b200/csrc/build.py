@@ -174,7 +174,9 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     if head_dim % 16 or not 16 <= head_dim <= 512:
         raise BuildError(f"attention kernels take head sizes that are multiples of 16 from 16 to 512, "
                          f"found {head_dim}")
-    return _load(f"janis_attn_hd{head_dim}", ATTENTION_SOURCES, [f"JANIS_HEAD_DIM={head_dim}"])
+    extra = [d for d in os.environ.get("JANIS_ATTN_DEFINES", "").split(",") if d]      # tuning experiments
+    tag = "_" + "_".join(d.replace("=", "") for d in extra) if extra else ""
+    return _load(f"janis_attn_hd{head_dim}{tag}", ATTENTION_SOURCES, [f"JANIS_HEAD_DIM={head_dim}", *extra])
 
 
 def build_all(head_dims=(16, 32, 64, 128, 256), verbose_ptxas: bool = False) -> list[str]:

@@ -316,10 +316,11 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
     return out
 
 
-def attn_set_decode_kernel(hd: int, staged: bool) -> None:
-    """Choose the decode kernel of the head size's library: staged through shared memory by bulk copies
-    (the default) or straight from global memory into registers."""
-    attention_lib(hd).janis_attn_set_decode_kernel(1 if staged else 0)
+def attn_set_decode_kernel(hd: int, which: int = 2) -> None:
+    """Choose the decode kernel of the head size's library: 2 = staged by bulk copies with the scores on the
+    tensor cores (bfloat16 and head sizes <= 256; the default), 1 = staged, CUDA cores (also what float32
+    runs), 0 = straight from global memory into registers."""
+    attention_lib(hd).janis_attn_set_decode_kernel(int(which))
 
 
 def attn_wait_timeouts(hd: int) -> int:

@@ -73,11 +73,19 @@ class SoftmaxAttention(Mixer):
     def _decode_geometry(self, ctx: StepContext, sm_count: int):
         bound = max(ctx.len_bound, 1)
         span = min(bound, self.window) if self.window else bound
-        # the largest chunk that still leaves about 1.5 CTAs per SM: long chunks amortise the staging
-        # pipeline's start, enough CTAs keep every SM pulling on the cache
-        chunk = 64
-        while chunk < 1024 and ctx.n_seq * self.n_kv_heads * ((span + 2 * chunk - 1) // (2 * chunk)) >= (3 * sm_count) // 2:
-            chunk *= 2
+        # A CTA per (sequence, key/value head, chunk); two CTAs fit an SM.  Cost of a choice, in tiles of 32
+        # keys: waves of CTAs x (tiles of a chunk + a fixed share for starting the pipeline and for the
+        # merge).  Long chunks amortise the fixed share, short ones fill the SMs and avoid a ragged last wave.
+        pairs = ctx.n_seq * self.n_kv_heads
+        resident = 2 * sm_count
+        best = None
+        for chunk in range(64, 2049, 64):
+            n_chunks = (span + chunk - 1) // chunk + (1 if self.window and span >= self.window else 0)
+            waves = (pairs * n_chunks + resident - 1) // resident
+            cost = waves * (chunk // 32 + 6)
+            if best is None or cost < best[0]:
+                best = (cost, chunk)
+        chunk = best[1]
         max_chunks = (bound + chunk - 1) // chunk
         if self.window:
             max_chunks = min(max_chunks, (self.window + chunk - 1) // chunk + 1)

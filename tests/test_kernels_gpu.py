@@ -254,7 +254,7 @@ def test_gemv_refuses_what_it_cannot_do():
         o.gemv_bf16(x, w, torch.empty((65, 16), dtype=torch.bfloat16, device=dev()))
 
 
-ATTN_SHAPES = [(4, 2, 16), (6, 1, 32), (3, 3, 48), (2, 2, 64), (9, 1, 80), (8, 4, 128), (8, 4, 256)]
+ATTN_SHAPES = [(4, 2, 16), (6, 1, 32), (3, 3, 48), (2, 2, 64), (9, 1, 80), (8, 4, 128), (8, 4, 256), (20, 2, 64)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -327,8 +327,8 @@ def test_attn_prefill_reads_another_layers_keys(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES)
 @pytest.mark.parametrize("window,ring,chunk", [(0, 0, 64), (0, 0, 256), (16, 64, 64), (100, 128, 64), (128, 128, 128)])
-@pytest.mark.parametrize("staged", [True, False])
-def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, staged):
+@pytest.mark.parametrize("kernel", [2, 1, 0])
+def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, kernel):
     # sequences of unequal lengths in scattered pages; one padding row; lengths at page and chunk edges
     lens = [1, 64, 65, 300, 7, 129]
     slots = [3, 0, 5, 1, -1, 4]
@@ -348,12 +348,14 @@ def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, staged):
     scratch = torch.empty(ops().attn_decode_scratch_floats(n_seq, nq, hd, max_chunks), dtype=torch.float32, device=d)
     out = torch.full((n_seq, nq * hd), 7.0, dtype=dtype, device=d)
     scale, cap = 1.0 / math.sqrt(hd), 30.0
-    ops().attn_set_decode_kernel(hd, staged)
+    if kernel == 2 and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core decode kernel is bfloat16 only")
+    ops().attn_set_decode_kernel(hd, kernel)
     try:
         ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
                           window, ring, chunk, max_chunks)
     finally:
-        ops().attn_set_decode_kernel(hd, True)
+        ops().attn_set_decode_kernel(hd, 2)
     assert ops().attn_wait_timeouts(hd) == 0
     want = torch.empty((n_seq, nq * hd), dtype=torch.float64)
     R.attn_decode(qkv.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, scale, cap, window,
