@@ -100,6 +100,27 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     }
 }
 
+// the same for bfloat16 and groups of 8: a thread takes 8 gates and their 8 ups as two 16-byte loads
+__global__ void gated_act8_bf16_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, size_t n_groups, int act) {
+    for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_groups; q += (size_t)gridDim.x * blockDim.x) {
+        float g[8], u[8], o[8];
+        Vec16<bf16>::load(gu + q * 16, g);
+        Vec16<bf16>::load(gu + q * 16 + 8, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = (act == 0 ? gelu_tanh(g[e]) : g[e] / (1.0f + expf(-g[e]))) * u[e];
+        Vec16<bf16>::store(out + q * 8, o);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// x = cap * tanh(x / cap) in place over float values (the cap on logits that a library product made)
+// ---------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    const float inv = 1.0f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
 // ---------------------------------------------------------------------------
 // rotary encoding of q and k in place, and the write of k (rotated) and v into
 // the paged cache.  qkv: [T, row_heads, hd], heads q, then k, then v (a layer that
@@ -220,11 +241,24 @@ JANIS_EXPORT int janis_gated_act(const void* gu, void* out, int dtype, int rows,
     const int nb = (int)((n + nt - 1) / nt < 148 * 16 ? (n + nt - 1) / nt : 148 * 16);
     if (dtype == JANIS_F32)
         gated_act_kernel<float><<<nb, nt, 0, stream>>>((const float*)gu, (float*)out, rows, I, group, act);
-    else if (dtype == JANIS_BF16)
+    else if (dtype == JANIS_BF16 && group == 8 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+        const size_t n_groups = n / 8;        // rows * I / 8: group q of a row-major [rows, 2I] starts at 16 q
+        const size_t want = (n_groups + nt - 1) / nt;
+        gated_act8_bf16_kernel<<<(int)(want < 148 * 32 ? want : 148 * 32), nt, 0, stream>>>((const bf16*)gu, (bf16*)out,
+                                                                                             n_groups, act);
+    } else if (dtype == JANIS_BF16)
         gated_act_kernel<bf16><<<nb, nt, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I, group, act);
     else
         return fail("gated_act: unknown dtype %d", dtype);
     return launched("gated_act");
+}
+
+JANIS_EXPORT int janis_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0 || !(cap > 0.f)) return 0;
+    const int nt = 256;
+    const long long want = (n + nt - 1) / nt;
+    softcap_kernel<<<(int)(want < 148 * 32 ? want : 148 * 32), nt, 0, stream>>>(x, (size_t)n, cap);
+    return launched("softcap");
 }
 
 JANIS_EXPORT int janis_rope_store(void* qkv, int dtype, const int* tok_pos, const int* tok_seq,

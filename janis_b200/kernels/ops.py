@@ -19,7 +19,8 @@ import torch
 from ..csrc import build
 
 PAGE = 64                      # tokens per cache page (JANIS_PAGE in the CUDA sources)
-GEMV_MAX_ROWS = 64
+GEMV_MAX_ROWS = 64             # what the skinny kernel accepts
+GEMV_FAST_ROWS = 16            # up to here it beats the library product (above, each warp re-reads too much of x)
 EPI_NONE, EPI_GATED_GELU, EPI_SOFTCAP, EPI_GATED_SILU = 0, 1, 2, 3
 GATE_GROUP = 8                 # fused gate/up rows alternate in groups of 8
 ACT_GELU_TANH, ACT_SILU = 0, 1
@@ -51,6 +52,7 @@ def core():
         lib.janis_rmsnorm.argtypes = [P, I, P, P, P, I, I, I, F, P]
         lib.janis_add_rmsnorm.argtypes = [P, P, I, I, c_longlong, P, F, P, F, P, I, I, I, P]
         lib.janis_gated_act.argtypes = [P, P, I, I, I, I, I, P]
+        lib.janis_softcap.argtypes = [P, c_longlong, F, P]
         lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
         lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
         lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
@@ -241,16 +243,32 @@ def gemv_bf16(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0, cluster: in
     return out
 
 
+def softcap(x, cap: float):
+    """x = cap * tanh(x / cap) in place, float32."""
+    lib = core()
+    _check(lib, lib.janis_softcap(_t(x, "x", torch.float32), x.numel(), float(cap), _stream()))
+    return x
+
+
 def linear_bf16(x, w, out):
-    """out[M, N] = x w^T in bfloat16 with float accumulation: the skinny kernel up to 64 rows,
+    """out[M, N] = x w^T in bfloat16 with float accumulation: the skinny kernel up to 16 rows,
     the library product (cuBLAS) above."""
     M = x.shape[0]
-    if M <= GEMV_MAX_ROWS:
+    if M <= GEMV_FAST_ROWS:
         return gemv_bf16(x, w, out)
     _t(x, "x", torch.bfloat16)
     _t(w, "w", torch.bfloat16)
     _t(out, "out", torch.bfloat16, (M, w.shape[0]))
     torch.mm(x, w.t(), out=out)
+    return out
+
+
+def matmul_bf16_to_f32(x, w, out):
+    """out[M, N] float32 = x[M, K] w[N, K]^T, bfloat16 operands, the library product (cuBLAS)."""
+    _t(x, "x", torch.bfloat16)
+    _t(w, "w", torch.bfloat16)
+    _t(out, "out", torch.float32, (x.shape[0], w.shape[0]))
+    torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     return out
 
 

@@ -55,8 +55,10 @@ class LMHead(Part):
         R = y.shape[0]
         if ctx.rt.dtype == torch.float32:
             return ops.gemm_f32(y, self.table, out, self.softcap)
-        step = ops.GEMV_MAX_ROWS
-        for r0 in range(0, R, step):
-            r1 = min(R, r0 + step)
-            ops.gemv_bf16(y[r0:r1], self.table, out[r0:r1], ops.EPI_SOFTCAP, self.softcap)
+        if R <= ops.GEMV_FAST_ROWS:
+            return ops.gemv_bf16(y, self.table, out, ops.EPI_SOFTCAP, self.softcap)
+        # many rows: the library's product with float32 output, then the cap
+        ops.matmul_bf16_to_f32(y, self.table, out)
+        if self.softcap > 0:
+            ops.softcap(out, self.softcap)
         return out

@@ -8,7 +8,7 @@ with act="silu" it is the SwiGLU of the reference's other models
 gate and up are one product: their rows are interleaved at load in groups of 8
 (8 gate rows, the 8 matching up rows, ...), which puts each gate value beside
 its up value in one tile of the skinny decode kernel, so the activation is
-applied to float accumulators before anything is written.  Above 64 rows the
+applied to float accumulators before anything is written.  Above 16 rows the
 product comes from the library and a separate kernel applies the activation.
 """
 from __future__ import annotations
@@ -61,7 +61,7 @@ class GatedMLP(FeedForward):
         rt, ws, ops = ctx.rt, ctx.ws, ctx.rt.ops
         T, I = ctx.n_tok, self.intermediate
         a = ws.buf("ffn.act", (T, I), rt.dtype)
-        if rt.dtype == torch.bfloat16 and T <= ops.GEMV_MAX_ROWS:
+        if rt.dtype == torch.bfloat16 and T <= ops.GEMV_FAST_ROWS:
             ops.gemv_bf16(x, self.w_gu, a, ops.EPI_GATED_GELU if self.act == 0 else ops.EPI_GATED_SILU)
         else:
             gu = ws.buf("ffn.gu", (T, 2 * I), rt.dtype)

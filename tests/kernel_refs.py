@@ -14,6 +14,7 @@ import torch
 
 PAGE = 64
 GEMV_MAX_ROWS = 64
+GEMV_FAST_ROWS = 16
 EPI_NONE, EPI_GATED_GELU, EPI_SOFTCAP, EPI_GATED_SILU = 0, 1, 2, 3
 GATE_GROUP = 8
 ACT_GELU_TANH, ACT_SILU = 0, 1
@@ -108,6 +109,16 @@ def gemv_bf16(x, w, out, epilogue=EPI_NONE, cap=0.0, cluster=0):
         v = cap * torch.tanh(v / cap)
     out.copy_(v.to(out.dtype))
     return out
+
+
+def matmul_bf16_to_f32(x, w, out):
+    out.copy_((x.double() @ w.double().T).float())
+    return out
+
+
+def softcap(x, cap):
+    x.copy_((cap * torch.tanh(x.double() / cap)).float())
+    return x
 
 
 def linear_bf16(x, w, out):

@@ -242,6 +242,17 @@ def test_gemv_bf16_softcap(M, N, K, cap):
     close(out, want, 1e-4, "gemv softcap")
 
 
+def test_softcap_and_library_product_with_float_output():
+    x = rnd((70, 96), torch.bfloat16, 60, std=3.0)
+    w = rnd((1000, 96), torch.bfloat16, 61)
+    out = torch.empty((70, 1000), dtype=torch.float32, device=dev())
+    ops().matmul_bf16_to_f32(x, w, out)
+    close(out, x.double().cpu() @ w.double().cpu().T, 1e-4, "library product, float32 out")
+    want = 15.0 * torch.tanh(out.double().cpu() / 15.0)
+    ops().softcap(out, 15.0)
+    close(out, want, F32_TOL, "softcap")
+
+
 def test_gemv_refuses_what_it_cannot_do():
     o = ops()
     x = rnd((2, 12), torch.bfloat16, 24)
