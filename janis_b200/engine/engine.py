@@ -94,16 +94,32 @@ class Engine:
 
 
 class _Backend:
-    """What the generation loop needs, on top of the engine's step function and sampler."""
+    """What the generation loop needs, on top of the engine's step function and sampler.
+
+    A decode step is started and read in two calls.  The chosen tokens are written into the step
+    function's device token buffer, from where the next step can take them without the host
+    (`last_tokens=None`), and copied to pinned host memory behind an event, so that reading step k
+    does not wait for step k+1, which may already be queued."""
 
     def __init__(self, engine: Engine, params: SamplingParams):
         self.e = engine
         self.params = params
         self.max_batch = engine.max_batch
         self.max_context = engine.max_context
+        on_gpu = torch.device(engine.rt.device).type == "cuda"
+        # the repetition penalty needs the reply so far on the host before the next token is picked
+        self.lookahead = on_gpu and not params.repeat_penalty > 1.0
+        self._pinned = [torch.empty((Stepper.MAX_GRAPH_BATCH,), dtype=torch.int32).pin_memory() for _ in range(4)] \
+            if on_gpu else None
+        self._turn = 0
 
     def fits(self, final_lengths) -> bool:
         return self.e.cache.can_hold(final_lengths)
+
+    def keeps_layout(self, n_live: int, n_rows: int) -> bool:
+        """Holes are cheap while they do not push the step into a larger padded batch than it needs."""
+        from .step import _bucket_batch
+        return n_rows <= Stepper.MAX_GRAPH_BATCH and _bucket_batch(n_live) == _bucket_batch(n_rows)
 
     def open(self) -> int:
         return self.e.cache.alloc_slot()
@@ -111,19 +127,36 @@ class _Backend:
     def close(self, handle: int) -> None:
         self.e.cache.free_slot(handle)
 
-    def _pick(self, logits, request_ids, token_index, replies, banned=None):
-        toks = self.e.sampler.sample(logits, self.params, request_ids, token_index, replies, banned)
-        return toks.tolist()          # the one read-back of a step: a token id per sequence
-
     def prefill(self, handles, prompts, request_ids, banned):
         entries = [StepEntry(h, p, (len(p) - 1,)) for h, p in zip(handles, prompts)]
         logits = self.e.stepper.step(entries, copy=False)
-        return self._pick(logits, request_ids, [0] * len(handles), None, banned)
+        toks = self.e.sampler.sample(logits, self.params, request_ids, [0] * len(handles), None, banned)
+        return toks.tolist()
 
-    def decode(self, handles, last_tokens, request_ids, token_index, replies):
-        entries = [StepEntry(h, (t,), (0,)) for h, t in zip(handles, last_tokens)]
-        logits = self.e.stepper.step(entries, copy=False)
-        return self._pick(logits, request_ids, token_index, replies)
+    def decode_start(self, handles, last_tokens, request_ids, token_index, replies):
+        n = len(handles)
+        st = self.e.stepper
+        entries = [StepEntry(h, ((last_tokens[i] if last_tokens is not None else 0),), (0,))
+                   for i, h in enumerate(handles)]
+        logits = st.step(entries, copy=False, tokens_on_device=last_tokens is None)
+        ids = [r if r is not None else 0 for r in request_ids]
+        if n > Stepper.MAX_GRAPH_BATCH or self._pinned is None:
+            return self.e.sampler.sample(logits, self.params, ids, token_index, replies)
+        out = st.token_buffer(n)
+        self.e.sampler.sample(logits, self.params, ids, token_index, replies, out=out)
+        host = self._pinned[self._turn % len(self._pinned)]
+        self._turn += 1
+        host[:n].copy_(out, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return (host, done, n)
+
+    def decode_finish(self, ticket):
+        if isinstance(ticket, torch.Tensor):
+            return ticket.tolist()
+        host, done, n = ticket
+        done.synchronize()            # the one wait of a step: n token ids
+        return host[:n].tolist()
 
 
 # ---------------------------------------------------------------------------

@@ -34,7 +34,7 @@ class StepError(ValueError):
 
 @dataclass
 class StepEntry:
-    slot: int
+    slot: int | None                # None: a padding row of a decode step (touches no cache, changes no other row)
     tokens: Sequence[int]
     want: Sequence[int] = ()        # places among `tokens` whose logits are asked for
 
@@ -87,6 +87,11 @@ class Stepper:
         V = self.model.vocab
         fresh = decode = 0
         for e in entries:
+            if e.slot is None:
+                if len(e.tokens) != 1:
+                    raise StepError("a padding row brings exactly one token")
+                decode += 1
+                continue
             if e.slot in seen:
                 raise StepError(f"slot {e.slot} appears twice in one step")
             seen.add(e.slot)
@@ -113,6 +118,8 @@ class Stepper:
                                 "started goes on one token at a time")
         if fresh and decode:
             raise StepError("the sequences of a step either all start or all go on by one token")
+        if not seen:
+            raise StepError("a step of padding rows alone")
         return "prefill" if fresh else "decode"
 
     # ------------------------------------------------------------------
@@ -173,9 +180,10 @@ class Stepper:
     def _decode(self, entries, copy: bool, tokens_on_device: bool = False) -> torch.Tensor | None:
         n_seq = len(entries)
         B = _bucket_batch(n_seq)
-        pos = [self.cache.length(e.slot) for e in entries]
+        pos = [self.cache.length(e.slot) if e.slot is not None else 0 for e in entries]
         for e, p in zip(entries, pos):
-            self.cache.reserve(e.slot, p + 1)
+            if e.slot is not None:
+                self.cache.reserve(e.slot, p + 1)
         self.cache.sync()
         bound = _bucket_len(max(pos) + 1)
         graphs = self.use_graphs and B <= self.MAX_GRAPH_BATCH
@@ -191,7 +199,7 @@ class Stepper:
         host[1, :n_seq] = pos
         host[2, :B] = np.arange(B)
         host[3, :] = -1
-        host[3, :n_seq] = [e.slot for e in entries]
+        host[3, :n_seq] = [e.slot if e.slot is not None else -1 for e in entries]
         host[4, :n_seq] = pos
         host[5, :B] = 1
         host[5, :n_seq] = np.asarray(pos) + 1
@@ -218,7 +226,8 @@ class Stepper:
             if graphs:
                 self._graphs[key] = (self._capture(ctx, logits), n_launch)
         for e, p in zip(entries, pos):
-            self.cache.advance(e.slot, p + 1)
+            if e.slot is not None:
+                self.cache.advance(e.slot, p + 1)
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if not wanted:
             return None

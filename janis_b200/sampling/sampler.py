@@ -48,9 +48,10 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, request_ids: Sequence[int],
                token_index: Sequence[int], recent: Sequence[Sequence[int]] | None = None,
-               banned: Sequence[int] | None = None, return_uniform: bool = False):
+               banned: Sequence[int] | None = None, return_uniform: bool = False, out: torch.Tensor | None = None):
         """One token per row of float32 `logits` [R, V] (changed in place by penalty and masking).
-        Returns int32 [R] on the device (and the uniform numbers used, when asked)."""
+        Returns int32 [R] on the device, written into `out` when given (and the uniform numbers used,
+        when asked)."""
         ops, dev = self.rt.ops, self.rt.device
         p = params.normalized()
         R = logits.shape[0]
@@ -64,7 +65,8 @@ class Sampler:
             ops.repeat_penalty(logits, torch.from_numpy(table).to(dev), p.repeat_penalty)
         if banned:
             ops.mask_tokens(logits, torch.tensor(sorted(set(int(b) for b in banned)), dtype=torch.int32, device=dev))
-        out = torch.empty((R,), dtype=torch.int32, device=dev)
+        if out is None:
+            out = torch.empty((R,), dtype=torch.int32, device=dev)
         if p.temp <= 0.0:
             ops.argmax(logits, out)
             return (out, None) if return_uniform else out

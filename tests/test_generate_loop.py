@@ -17,6 +17,7 @@ class FakeBackend:
         self.closed = []
         self.prefills, self.decodes = [], []
         self.live_peak = 0
+        self.device_tokens, self.in_flight, self.layouts = None, 0, []
 
     def fits(self, final_lengths):
         return sum(final_lengths) <= self.room
@@ -41,12 +42,37 @@ class FakeBackend:
             out = [t if t not in banned else (t + 1) % 100 for t in out]
         return out
 
-    def decode(self, handles, last_tokens, request_ids, token_index, replies):
-        assert set(handles) <= self.open_handles and len(handles) == len(last_tokens)
-        for idx, r in zip(token_index, replies):
-            assert idx == len(r)
-        self.decodes.append(list(request_ids))
-        return [(t + 1) % 100 for t in last_tokens]
+    lookahead = False
+
+    def keeps_layout(self, n_live, n_rows):
+        return n_live * 2 > n_rows                 # re-form once half the rows are holes
+
+    def decode_start(self, handles, last_tokens, request_ids, token_index, replies):
+        live = [h is not None for h in handles]
+        assert all(h in self.open_handles for h, ok in zip(handles, live) if ok)
+        if last_tokens is None:                    # tokens stay "on the device": the ones of the step before
+            assert self.lookahead and self.device_tokens is not None and len(self.device_tokens) == len(handles)
+            last_tokens = self.device_tokens
+            for idx, r, ok in zip(token_index, replies, live):
+                assert not ok or idx == len(r) + 1     # the step before has not been read yet
+        else:
+            for idx, r, ok in zip(token_index, replies, live):
+                assert not ok or idx == len(r)
+        self.decodes.append([r for r, ok in zip(request_ids, live) if ok])
+        self.layouts.append(list(request_ids))
+        out = [(t + 1) % 100 for t in last_tokens]
+        self.device_tokens = out
+        self.in_flight += 1
+        assert self.in_flight <= 2
+        return out
+
+    def decode_finish(self, ticket):
+        self.in_flight -= 1
+        return ticket
+
+
+class LookaheadBackend(FakeBackend):
+    lookahead = True
 
 
 def test_length_limit_and_order_of_replies():
@@ -132,10 +158,46 @@ def test_callbacks_and_cancel():
 
 def test_places_are_closed_when_the_backend_fails():
     class Broken(FakeBackend):
-        def decode(self, *a):
+        def decode_start(self, *a):
             raise RuntimeError("boom")
 
     b = Broken()
     with pytest.raises(RuntimeError, match="boom"):
         generate(b, [[1], [2]], max_tokens=4)
     assert not b.open_handles
+
+
+@pytest.mark.parametrize("max_tokens,stop", [(6, ()), (6, (12, 23)), (9, (33, 11, 52)), (1, ()), (3, (21,))])
+def test_lookahead_gives_the_same_replies(max_tokens, stop):
+    """Starting a step before the one before it has been read changes no reply: ends by length are known
+    beforehand, a stop token is seen a step late and the token computed past it is dropped."""
+    prompts = [[10], [20], [30], [40, 41], [50]]
+    plain = generate(FakeBackend(max_batch=3), prompts, max_tokens=max_tokens, stop=stop)
+    b = LookaheadBackend(max_batch=3)
+    ahead = generate(b, prompts, max_tokens=max_tokens, stop=stop)
+    assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
+    assert not b.open_handles and b.in_flight == 0
+
+
+def test_lookahead_keeps_rows_in_place_and_reforms_when_half_are_holes():
+    b = LookaheadBackend(max_batch=4)
+    out = generate(b, [[10], [20], [30], [40]], max_tokens=8, stop=(12, 22, 33))
+    assert [r.tokens for r in out] == [[11], [21], [31, 32], [41, 42, 43, 44, 45, 46, 47, 48]]
+    # requests 0 and 1 meet their stop token in the first decode step; the second step, started before the
+    # first was read, still has their rows.  With two of four rows empty no third step is started ahead:
+    # the second is read (request 2 stops there) and the layout is formed anew from what is still open
+    assert b.layouts[0] == [0, 1, 2, 3] and b.layouts[1] == [0, 1, 2, 3]
+    assert b.layouts[2] == [3] and all(l == [3] for l in b.layouts[2:])
+
+
+def test_lookahead_and_cancel():
+    b = LookaheadBackend(max_batch=2)
+    calls = [0]
+
+    def cancel():
+        calls[0] += 1
+        return calls[0] >= 4
+
+    out = generate(b, [[10], [20], [30]], max_tokens=10, cancel=cancel)
+    assert [r.finish_reason for r in out] == ["cancel"] * 3 and out[2].tokens == []
+    assert out[0].tokens == [11, 12, 13, 14] and not b.open_handles and b.in_flight == 0
