@@ -1,15 +1,21 @@
 // Prompt attention in bfloat16 on the tensor cores (mma.sync.m16n8k16, float
 // accumulation), one head size per compiled library (JANIS_HEAD_DIM).
 //
-// Packed sequences of unequal lengths that start at position 0.  One CTA owns 64
-// consecutive queries of one sequence and one query head: its 4 warps hold 16
-// query rows each, walk the key tiles of 64 that the causal mask and the window
-// leave, and keep the running maximum, the running sum and the unnormalised output
-// in registers (online softmax).  Per tile: S = Q K^T from shared memory (ldmatrix),
-// s * scale, cap * tanh(s / cap), mask on absolute positions, exp in float, P
-// rounded to bfloat16 as the left operand of P V.  tanhf and expf are the accurate
-// ones.  Shared-memory rows are XOR-swizzled in 16-byte pieces against ldmatrix
-// bank conflicts.
+// Packed sequences of unequal lengths that start at position 0.  One CTA owns BM
+// consecutive queries of one sequence and one query head: each of its warps holds 16
+// query rows, walks the key tiles of 64 that the causal mask and the window leave,
+// and keeps the running maximum, the running sum and the unnormalised output in
+// registers (online softmax).  Keys and values of the next tile are copied into the
+// other half of a double buffer (cp.async) while the tensor cores work on this one.
+// Per tile: S = Q K^T from shared memory (ldmatrix), s * scale, cap * tanh(s / cap),
+// mask on absolute positions, exp, P rounded to bfloat16 as the left operand of P V.
+//
+// tanh and exp here are built on ex2.approx and rcp.approx: tanh(x) = 1 - 2 / (e^2x + 1)
+// has an absolute error near 2e-7, far below the rounding of P to bfloat16 that
+// follows; a score needs about 14 instructions instead of about 50 with tanhf and
+// expf, which had made the softmax, not the products, the kernel's main cost.  The
+// float32 path of the library does not use this kernel.
+// Shared-memory rows are XOR-swizzled in 16-byte pieces against ldmatrix bank conflicts.
 #include "common.cuh"
 
 #ifndef JANIS_HEAD_DIM
@@ -20,13 +26,17 @@ namespace janis {
 namespace pf {
 
 constexpr int HD = JANIS_HEAD_DIM;
-constexpr int BM = 64, BN = 64, WARPS = 4, THREADS = WARPS * 32;
-constexpr int CHUNKS = HD / 8;                       // 16-byte pieces per row
+constexpr int BN = HD <= 256 ? 64 : 32;               // keys per tile
+constexpr int WARPS = HD <= 256 ? 8 : 4;              // 16 query rows each
+constexpr int BM = WARPS * 16, THREADS = WARPS * 32;
+constexpr int CHUNKS = HD / 8;                        // 16-byte pieces per row
 constexpr int swz_pow2(int n) { return n % 8 == 0 ? 8 : (n % 4 == 0 ? 4 : (n % 2 == 0 ? 2 : 1)); }
 constexpr int SWZ_MASK = swz_pow2(CHUNKS) - 1;
 constexpr int ROW_BYTES = HD * 2;
-constexpr int TILE_BYTES = BM * ROW_BYTES;           // BM == BN
-constexpr int SMEM_BYTES = 3 * TILE_BYTES;           // Q, K, V
+constexpr int Q_BYTES = BM * ROW_BYTES;
+constexpr int KV_BYTES = BN * ROW_BYTES;              // one of K or V, one stage
+constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES;    // Q, then two stages of (K, V)
+static_assert(SMEM_BYTES <= 227 * 1024, "tiles do not fit shared memory");
 
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
     return base + row * ROW_BYTES + ((chunk ^ (row & SWZ_MASK)) << 4);
@@ -62,10 +72,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// 64 rows x HD of bf16 from global rows (row stride `stride` elements) into a swizzled tile;
+__device__ __forceinline__ float ex2(float x) {        // 2^x; ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float fast_tanh(float x) {  // 1 - 2 / (e^2x + 1); exact limits at +-inf
+    const float e = ex2(x * 2.8853900817779268f);      // 2 log2(e)
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(e + 1.0f));
+    return 1.0f - 2.0f * r;
+}
+
+// `rows` rows x HD of bf16 from global rows (row stride `stride` elements) into a swizzled tile;
 // rows >= n_valid are filled with zeros.
-__device__ __forceinline__ void load_tile(uint32_t smem, const bf16* src, size_t stride, int n_valid) {
-    for (int idx = threadIdx.x; idx < BM * CHUNKS; idx += THREADS) {
+__device__ __forceinline__ void load_tile(uint32_t smem, const bf16* src, size_t stride, int rows, int n_valid) {
+    for (int idx = threadIdx.x; idx < rows * CHUNKS; idx += THREADS) {
         const int row = idx / CHUNKS, chunk = idx % CHUNKS;
         const bool ok = row < n_valid;
         cp_async16(tile_addr(smem, row, chunk), src + (size_t)(ok ? row : 0) * stride + chunk * 8, ok);
@@ -78,8 +101,9 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
                         bf16* __restrict__ out, int nq, int nkv, int q_row_heads, int kv_row_heads,
                         int kv_k_head0, float scale, float cap, int window) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    // which sequence and which tile of 64 queries is this CTA's
-    int tile = blockIdx.x, seq = -1, q0 = 0, len = 0;
+    // Which sequence and which tile of BM queries is this CTA's.  Tiles are handed out from the end of
+    // the list: the last tiles of a sequence see the most keys and should start first.
+    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, seq = -1, q0 = 0, len = 0;
     for (int s = 0; s < n_seq; ++s) {
         const int n = seq_len[s];
         const int nt = (n + BM - 1) / BM;
@@ -94,106 +118,129 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     const int g = lane >> 2, t = lane & 3;
 
     const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem_raw);
-    const uint32_t sK = sQ + TILE_BYTES, sV = sK + TILE_BYTES;
+    const uint32_t sKV = sQ + Q_BYTES;                // stage s: K at sKV + s * 2 KV_BYTES, V right after
 
     const size_t q_stride = (size_t)q_row_heads * HD, kv_stride = (size_t)kv_row_heads * HD;
-    load_tile(sQ, q_src + (size_t)(first + q0) * q_stride + (size_t)head * HD, q_stride, min(BM, len - q0));
+    const int q_last = min(q0 + BM, len) - 1;
+    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
+    const int k_first = (j_first / BN) * BN;
+    const int n_tiles = (q_last - k_first) / BN + 1;
+    const bf16* kbase = kv_src + (size_t)first * kv_stride + (size_t)(kv_k_head0 + kvh) * HD;
+    const bf16* vbase = kbase + (size_t)nkv * HD;
+    auto load_kv = [&](int it) {
+        const int k0 = k_first + it * BN;
+        const uint32_t dst = sKV + (it & 1) * 2 * KV_BYTES;
+        const int n_keys = min(BN, len - k0);
+        load_tile(dst, kbase + (size_t)k0 * kv_stride, kv_stride, BN, n_keys);
+        load_tile(dst + KV_BYTES, vbase + (size_t)k0 * kv_stride, kv_stride, BN, n_keys);
+    };
+    load_tile(sQ, q_src + (size_t)(first + q0) * q_stride + (size_t)head * HD, q_stride, BM, min(BM, len - q0));
+    load_kv(0);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
 
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i)
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+    // running maximum in units of log2(e): exp(s - m) = 2^(s log2e - m log2e)
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const float LOG2E = 1.4426950408889634f;
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+    const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
 
     const int row_lo = q0 + warp * 16 + g;            // this thread's two query positions
     const int row_hi = row_lo + 8;
-    const int q_last = min(q0 + BM, len) - 1;
-    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
-    const bf16* kbase = kv_src + (size_t)first * kv_stride + (size_t)(kv_k_head0 + kvh) * HD;
-    const bf16* vbase = kbase + (size_t)nkv * HD;
+    const int warp_first = q0 + warp * 16, warp_last = warp_first + 15;
 
-    for (int k0 = (j_first / BN) * BN; k0 <= q_last; k0 += BN) {
-        __syncthreads();                              // everyone is done with the previous K and V
-        const int n_keys = min(BN, len - k0);
-        load_tile(sK, kbase + (size_t)k0 * kv_stride, kv_stride, n_keys);
-        load_tile(sV, vbase + (size_t)k0 * kv_stride, kv_stride, n_keys);
-        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+    for (int it = 0; it < n_tiles; ++it) {
+        const int k0 = k_first + it * BN;
+        if (it + 1 < n_tiles) load_kv(it + 1);        // the other stage: its readers finished a tile ago
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");     // this tile (and Q) has landed
         __syncthreads();
+        const uint32_t sK = sKV + (it & 1) * 2 * KV_BYTES, sV = sK + KV_BYTES;
 
-        // S = Q K^T for this warp's 16 rows and the 64 keys of the tile
-        float s[BN / 8][4];
+        // a warp whose rows see none of this tile's keys (all later, or all outside the window) skips it
+        const bool any = k0 <= warp_last && (window <= 0 || k0 + BN - 1 > warp_first - window);
+        if (any) {
+            // S = Q K^T for this warp's 16 rows and the 64 keys of the tile
+            float s[BN / 8][4];
 #pragma unroll
-        for (int j = 0; j < BN / 8; ++j)
+            for (int j = 0; j < BN / 8; ++j)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+                for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-            uint32_t a[4];
-            ldmatrix_x4(a, tile_addr(sQ, warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t a[4];
+                ldmatrix_x4(a, tile_addr(sQ, warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
 #pragma unroll
-            for (int jp = 0; jp < BN / 16; ++jp) {
-                uint32_t b[4];
-                ldmatrix_x4(b, tile_addr(sK, jp * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 2 + ((lane >> 3) & 1)));
-                mma16816(s[2 * jp], a, b[0], b[1]);
-                mma16816(s[2 * jp + 1], a, b[2], b[3]);
+                for (int jp = 0; jp < BN / 16; ++jp) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, tile_addr(sK, jp * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 2 + ((lane >> 3) & 1)));
+                    mma16816(s[2 * jp], a, b[0], b[1]);
+                    mma16816(s[2 * jp + 1], a, b[2], b[3]);
+                }
+            }
+            // scale, cap, mask; scores end up in units of log2(e)
+            const bool inner = k0 + BN - 1 <= warp_first && k0 + BN <= len &&
+                               (window <= 0 || k0 > warp_last - window);   // every key seen by every row
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float v = cap > 0.f ? cap2 * fast_tanh(s[j][c] * scale * inv_cap) : s[j][c] * scale2;
+                    if (!inner) {
+                        const int key = k0 + j * 8 + t * 2 + (c & 1);
+                        const int row = (c & 2) ? row_hi : row_lo;
+                        const bool seen = key <= row && key < len && (window <= 0 || key > row - window);
+                        v = seen ? v : -INFINITY;
+                    }
+                    s[j][c] = v;
+                    mx[c >> 1] = fmaxf(mx[c >> 1], v);
+                }
+            float corr[2], m_use[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                m_use[r] = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet
+                corr[r] = ex2(m_run[r] - m_use[r]);                // 2^(-inf) = 0
+                m_run[r] = m_new;
+                l_run[r] *= corr[r];
+            }
+            uint32_t p[BN / 16][4];
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) {
+                const float p0 = ex2(s[j][0] - m_use[0]), p1 = ex2(s[j][1] - m_use[0]);
+                const float p2 = ex2(s[j][2] - m_use[1]), p3 = ex2(s[j][3] - m_use[1]);
+                l_run[0] += p0 + p1;
+                l_run[1] += p2 + p3;
+                p[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+                p[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                o[i][0] *= corr[0];
+                o[i][1] *= corr[0];
+                o[i][2] *= corr[1];
+                o[i][3] *= corr[1];
+            }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+                for (int ip = 0; ip < HD / 16; ++ip) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, tile_addr(sV, kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), ip * 2 + (lane >> 4)));
+                    mma16816(o[2 * ip], p[kk], b[0], b[1]);
+                    mma16816(o[2 * ip + 1], p[kk], b[2], b[3]);
+                }
             }
         }
-
-        // scale, cap, mask, online softmax
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int j = 0; j < BN / 8; ++j)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int key = k0 + j * 8 + t * 2 + (c & 1);
-                const int row = (c & 2) ? row_hi : row_lo;
-                float v = s[j][c] * scale;
-                if (cap > 0.f) v = cap * tanhf(v / cap);
-                const bool seen = key <= row && key < len && (window <= 0 || key > row - window);
-                v = seen ? v : -INFINITY;
-                s[j][c] = v;
-                mx[c >> 1] = fmaxf(mx[c >> 1], v);
-            }
-        float corr[2], m_use[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);
-            m_use[r] = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet
-            corr[r] = expf(m_run[r] - m_use[r]);               // exp(-inf) = 0
-            m_run[r] = m_new;
-            l_run[r] *= corr[r];
-        }
-        uint32_t p[BN / 16][4];
-#pragma unroll
-        for (int j = 0; j < BN / 8; ++j) {
-            const float p0 = expf(s[j][0] - m_use[0]), p1 = expf(s[j][1] - m_use[0]);
-            const float p2 = expf(s[j][2] - m_use[1]), p3 = expf(s[j][3] - m_use[1]);
-            l_run[0] += p0 + p1;
-            l_run[1] += p2 + p3;
-            p[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
-            p[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
-        }
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-            o[i][0] *= corr[0];
-            o[i][1] *= corr[0];
-            o[i][2] *= corr[1];
-            o[i][3] *= corr[1];
-        }
-        // O += P V
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-#pragma unroll
-            for (int ip = 0; ip < HD / 16; ++ip) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, tile_addr(sV, kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), ip * 2 + (lane >> 4)));
-                mma16816(o[2 * ip], p[kk], b[0], b[1]);
-                mma16816(o[2 * ip + 1], p[kk], b[2], b[3]);
-            }
-        }
+        __syncthreads();                              // this stage may be overwritten by the load after next
     }
 
     // the sums of a row are spread over the four threads that share it
@@ -217,9 +264,12 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
 
 using namespace janis;
 
+JANIS_EXPORT int janis_attn_prefill_tile() { return pf::BM; }
+
 // q_src: [T, q_row_heads, hd] with the queries in its first nq heads; keys and values of position j of
 // sequence s are read from row seq_first_row[s] + j of kv_src [T, kv_row_heads, hd], key heads starting at
-// head kv_k_head0, value heads nkv later.  n_tiles_bound >= sum over sequences of ceil(len / 64).
+// head kv_k_head0, value heads nkv later.  n_tiles_bound >= sum over sequences of ceil(len / tile), tile =
+// janis_attn_prefill_tile().
 JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, const int* seq_first_row,
                                         const int* seq_len, int n_seq, int n_tiles_bound, void* out, int nq,
                                         int nkv, int q_row_heads, int kv_row_heads, int kv_k_head0, float scale,

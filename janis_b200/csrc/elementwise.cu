@@ -81,6 +81,53 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TR* __restrict__
     for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_float<TO>(hr[i] * inv2 * w_next[i]);
 }
 
+// The same with the row held in registers (H <= 256 * EPT): every input is read once.
+template <typename TR, typename TO, int EPT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_reg_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_part, size_t part_stride,
+                       const float* __restrict__ w_post, float eps_post, const float* __restrict__ w_next,
+                       float eps_next, TO* __restrict__ y, int H) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const TR* rr = res + (size_t)r * H;
+    float* hr = h + (size_t)r * H;
+    float v[EPT], hv[EPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int i = threadIdx.x + k * 256;
+        v[k] = 0.f;
+        if (i < H) {
+            float a = to_float(rr[i]);
+            for (int p = 1; p < n_part; ++p) a += to_float(rr[p * part_stride + i]);
+            v[k] = a;
+            hv[k] = hr[i];
+        }
+        ss = fmaf(v[k], v[k], ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = w_post ? 1.0f / sqrtf(ss / (float)H + eps_post) : 1.0f;
+    float ss2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < H) {
+            hv[k] = hv[k] + (w_post ? v[k] * inv * w_post[i] : v[k]);
+            hr[i] = hv[k];
+            ss2 = fmaf(hv[k], hv[k], ss2);
+        }
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)H + eps_next);
+    TO* yr = y + (size_t)r * H;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < H) yr[i] = from_float<TO>(hv[k] * inv2 * w_next[i]);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // gated activation over a fused [rows, 2*I] product whose columns alternate in
 // groups of `group`: group g of gate columns, then group g of up columns.
@@ -220,15 +267,26 @@ JANIS_EXPORT int janis_add_rmsnorm(float* h, const void* res, int res_dtype, int
     if (n_part < 1) return fail("add_rmsnorm: n_part must be >= 1");
     if (w_next != nullptr && y == nullptr) return fail("add_rmsnorm: a next norm needs an output");
     const int nt = row_threads(H);
-#define JANIS_CASE(TR, TO)                                                                                     \
-    add_rmsnorm_kernel<TR, TO><<<R, nt, 0, stream>>>(h, (const TR*)res, n_part, (size_t)part_stride, w_post,    \
-                                                     eps_post, w_next, eps_next, (TO*)y, H)
+    // rows up to 8192 wide stay in registers (each input read once); wider rows take three passes
+#define JANIS_REG(TR, TO, EPT)                                                                                  \
+    add_rmsnorm_reg_kernel<TR, TO, EPT><<<R, 256, 0, stream>>>(h, (const TR*)res, n_part, (size_t)part_stride,   \
+                                                               w_post, eps_post, w_next, eps_next, (TO*)y, H)
+#define JANIS_CASE(TR, TO)                                                                                      \
+    do {                                                                                                        \
+        if (H <= 1024) JANIS_REG(TR, TO, 4);                                                                    \
+        else if (H <= 2048) JANIS_REG(TR, TO, 8);                                                               \
+        else if (H <= 4096) JANIS_REG(TR, TO, 16);                                                              \
+        else if (H <= 8192) JANIS_REG(TR, TO, 32);                                                              \
+        else add_rmsnorm_kernel<TR, TO><<<R, nt, 0, stream>>>(h, (const TR*)res, n_part, (size_t)part_stride,    \
+                                                              w_post, eps_post, w_next, eps_next, (TO*)y, H);   \
+    } while (0)
     if (res_dtype == JANIS_F32 && y_dtype == JANIS_F32) JANIS_CASE(float, float);
     else if (res_dtype == JANIS_F32 && y_dtype == JANIS_BF16) JANIS_CASE(float, bf16);
     else if (res_dtype == JANIS_BF16 && y_dtype == JANIS_F32) JANIS_CASE(bf16, float);
     else if (res_dtype == JANIS_BF16 && y_dtype == JANIS_BF16) JANIS_CASE(bf16, bf16);
     else return fail("add_rmsnorm: unknown dtypes %d -> %d", res_dtype, y_dtype);
 #undef JANIS_CASE
+#undef JANIS_REG
     return launched("add_rmsnorm");
 }
 

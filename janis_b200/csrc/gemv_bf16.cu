@@ -24,7 +24,7 @@ namespace cg = cooperative_groups;
 
 namespace janis {
 
-constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_WARPS = 8;        // warps of a CTA that split K (4 when N alone gives CTAs enough)
 
 enum { EPI_NONE = 0, EPI_GATED_GELU = 1, EPI_SOFTCAP = 2, EPI_GATED_SILU = 3 };
 
@@ -45,11 +45,11 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read once: do 
     return v;
 }
 
-template <int MT, int U, int CL, typename TO>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+template <int MT, int U, int CL, int NW, typename TO>
+__global__ void __launch_bounds__(NW * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __restrict__ out, int M, int N,
                  int K, int epi, float cap) {
-    __shared__ float red[GEMV_WARPS][MT][32][4];
+    __shared__ float red[NW][MT][32][4];
     __shared__ float cta_sum[MT * 128];        // this CTA's sum over its warps; read by CTA 0 of the cluster
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -74,9 +74,9 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
 
-    constexpr int SPLIT = GEMV_WARPS * CL;     // warps that share the K of a tile
+    constexpr int SPLIT = NW * CL;             // warps that share the K of a tile
     const int nblk = (K + 31) / 32;
-    for (int kb = rank * GEMV_WARPS + warp; kb < nblk; kb += SPLIT * U) {
+    for (int kb = rank * NW + warp; kb < nblk; kb += SPLIT * U) {
         uint4 a_lo[U], a_hi[U], b[U][MT];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -106,7 +106,7 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
         const int i = idx / 128, ln = (idx / 4) % 32, c = idx % 4;
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < GEMV_WARPS; ++w) v += red[w][i][ln][c];
+        for (int w = 0; w < NW; ++w) v += red[w][i][ln][c];
         cta_sum[idx] = v;
     }
     if (CL > 1) {
@@ -161,12 +161,20 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
 
 using namespace janis;
 
+static int g_gemv_small_ctas = 1;
+// tuning switch: 0 launches tall products with 8-warp CTAs too
+JANIS_EXPORT void janis_gemv_small_ctas(int on) { g_gemv_small_ctas = on ? 1 : 0; }
+
 template <int MT, int U, int CL, typename TO>
 static int launch_one(const bf16* x, const bf16* W, TO* out, int M, int N, int K, int epi, float cap,
                       cudaStream_t stream) {
     const int tiles = (N + 15) / 16;
     if (CL == 1) {
-        gemv_bf16_kernel<MT, U, 1, TO><<<tiles, GEMV_WARPS * 32, 0, stream>>>(x, W, out, M, N, K, epi, cap);
+        // many tiles: CTAs of 4 warps, so that more of them are resident and the last wave is short
+        if (tiles >= 1024 && g_gemv_small_ctas)
+            gemv_bf16_kernel<MT, U, 1, 4, TO><<<tiles, 4 * 32, 0, stream>>>(x, W, out, M, N, K, epi, cap);
+        else
+            gemv_bf16_kernel<MT, U, 1, GEMV_WARPS, TO><<<tiles, GEMV_WARPS * 32, 0, stream>>>(x, W, out, M, N, K, epi, cap);
         return launched("gemv_bf16");
     }
     cudaLaunchConfig_t cfg = {};
@@ -181,7 +189,7 @@ static int launch_one(const bf16* x, const bf16* W, TO* out, int M, int N, int K
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<MT, U, CL, TO>, x, W, out, M, N, K, epi, cap);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<MT, U, CL, GEMV_WARPS, TO>, x, W, out, M, N, K, epi, cap);
     if (e != cudaSuccess) return fail("gemv_bf16: cluster launch failed: %s", cudaGetErrorString(e));
     return launched("gemv_bf16");
 }
@@ -209,16 +217,17 @@ JANIS_EXPORT int janis_gemv_bf16(const void* x, const void* W, void* out, int ou
     if ((epi == EPI_GATED_GELU || epi == EPI_GATED_SILU) && N % 16)
         return fail("gemv_bf16: a gated epilogue needs N to be a multiple of 16, found %d", N);
     if (epi < 0 || epi > 3) return fail("gemv_bf16: unknown epilogue %d", epi);
-    if (cluster < 0 || cluster > 4) return fail("gemv_bf16: cluster must be 0, 1, 2 or 4, found %d", cluster);
+    if (cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4)
+        return fail("gemv_bf16: cluster must be 0, 1, 2 or 4, found %d", cluster);
     if (((uintptr_t)x | (uintptr_t)W) & 15) return fail("gemv_bf16: operands must be 16-byte aligned");
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)W;
+    const int tiles = (N + 15) / 16, nblk = (K + 31) / 32;
     if (cluster == 0) {
         // enough CTAs to fill the GPU a few times over, as long as every warp keeps some blocks of K
-        const int tiles = (N + 15) / 16, nblk = (K + 31) / 32;
         cluster = 1;
         while (cluster < 4 && tiles * cluster < 600 && nblk >= GEMV_WARPS * cluster * 2 * 2) cluster *= 2;
     }
-    const bf16* xp = (const bf16*)x;
-    const bf16* wp = (const bf16*)W;
     if (M <= 8) return launch_gemv<1, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     if (M <= 16) return launch_gemv<2, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     if (M <= 32) return launch_gemv<4, 2>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);

@@ -76,6 +76,7 @@ def attention_lib(head_dim: int):
         lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P]
         lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
         lib.janis_attn_prefill_mma.argtypes = [P, P, P, P, I, I, P, I, I, I, I, I, F, F, I, P]
+        lib.janis_attn_prefill_tile.restype = I
         lib.janis_attn_set_decode_kernel.argtypes = [I]
         lib.janis_attn_set_decode_kernel.restype = None
         lib.janis_attn_wait_timeouts.restype = I
@@ -326,7 +327,8 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
     _t(seq_len, "seq_len", torch.int32, (n_seq,))
     _t(seq_first_row, "seq_first_row", torch.int32, (n_seq,))
     lib = attention_lib(hd)
-    tiles = (T + 63) // 64 + n_seq          # >= sum of ceil(len / 64)
+    bm = lib.janis_attn_prefill_tile()      # queries per CTA
+    tiles = (T + bm - 1) // bm + n_seq      # >= sum of ceil(len / bm)
     _check(lib, lib.janis_attn_prefill_mma(qkv.data_ptr(), kv_src.data_ptr(), seq_first_row.data_ptr(),
                                            seq_len.data_ptr(), n_seq, tiles, out.data_ptr(), nq, nkv,
                                            qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),

@@ -84,7 +84,7 @@ def test_rmsnorm(din, dout, Rn, H, eps):
 @pytest.mark.parametrize("dr", DTYPES)
 @pytest.mark.parametrize("post,nxt,n_part", [(True, True, 1), (True, False, 1), (False, True, 1), (True, True, 3),
                                              (False, False, 2)])
-@pytest.mark.parametrize("Rn,H", [(1, 96), (6, 2304), (4, 1000)])
+@pytest.mark.parametrize("Rn,H", [(1, 96), (6, 2304), (4, 1000), (3, 4608), (2, 9000)])
 def test_add_rmsnorm(dr, post, nxt, n_part, Rn, H):
     h0 = rnd((Rn, H), torch.float32, 5, std=2.0)
     res = rnd((n_part, Rn, H) if n_part > 1 else (Rn, H), dr, 6, std=0.5)
@@ -216,6 +216,19 @@ def test_gemv_bf16_clusters_share_k(cluster, M, N, K):
     want = torch.empty((M, N), dtype=torch.float64)
     R.gemv_bf16(x.cpu(), w.cpu(), want)
     close(out, want, 1e-4, f"gemv_bf16 cluster {cluster}")
+
+
+@pytest.mark.parametrize("M,N,K,epi", [(1, 18432, 2304, 1), (8, 17000, 264, 0), (16, 16400, 96, 2), (40, 16384, 40, 3)])
+def test_gemv_bf16_tall(M, N, K, epi):
+    """Tall products (the gated feed-forward, the head) run in CTAs of 4 warps."""
+    x = rnd((M, K), torch.bfloat16, 52)
+    w = rnd((N, K), torch.bfloat16, 53, std=0.1)
+    n_out = N // 2 if epi in (1, 3) else N
+    out = torch.empty((M, n_out), dtype=torch.float32, device=dev())
+    ops().gemv_bf16(x, w, out, epi, 7.0)
+    want = torch.empty((M, n_out), dtype=torch.float64)
+    R.gemv_bf16(x.cpu(), w.cpu(), want, epi, 7.0)
+    close(out, want, 1e-4, "gemv_bf16, tall")
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 12, 40, 64])
