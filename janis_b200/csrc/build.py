@@ -31,7 +31,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # no fast-math: expf, tanhf and sincosf keep their accurate forms
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
-CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemv_bf16.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemv_bf16.cu", "gemm_tc05.cu", "sampling.cu"]
 ATTENTION_SOURCES = ["attention.cu", "attention_prefill_mma.cu", "attention_no_alloc.cu"]
 HEADERS = ["common.cuh", "attention_no_alloc.h"]
 

@@ -56,6 +56,8 @@ def core():
         lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
         lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
         lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
+        lib.janis_gemm_tc05.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
+        lib.janis_tc05_timeouts.restype = I
         lib.janis_argmax.argtypes = [P, P, I, I, P]
         lib.janis_sample.argtypes = [P, P, P, I, I, F, F, c_ulonglong, P, P, P]
         lib.janis_repeat_penalty.argtypes = [P, P, I, I, I, F, P]
@@ -249,6 +251,25 @@ def softcap(x, cap: float):
     lib = core()
     _check(lib, lib.janis_softcap(_t(x, "x", torch.float32), x.numel(), float(cap), _stream()))
     return x
+
+
+def gemm_tc05(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0, split: int = 0):
+    """out = x[M<=64, K] w[N, K]^T on the tcgen05 tensor cores (operands swapped: rows of w fill the 128 TMEM
+    lanes, the batch rows are the narrow side), TMA-fed, K split over a cluster when N is small.  Same
+    epilogues and output shapes as gemv_bf16.  split: CTAs that share K (1, 2, 4, 8; 0 = chosen from N, K)."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if epilogue in (EPI_GATED_GELU, EPI_GATED_SILU) else N
+    lib = core()
+    _check(lib, lib.janis_gemm_tc05(_t(x, "x", torch.bfloat16, (M, K)), _t(w, "w", torch.bfloat16, (N, K)),
+                                    _t(out, "out", _FLOATS, (M, n_out)), _DT[out.dtype], M, N, K, epilogue,
+                                    float(cap), int(split), _stream()))
+    return out
+
+
+def tc05_timeouts() -> int:
+    """How often a CTA of gemm_tc05 gave up waiting on a barrier (0 in a healthy run); synchronises."""
+    return int(core().janis_tc05_timeouts())
 
 
 def linear_bf16(x, w, out):
