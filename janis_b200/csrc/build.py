@@ -167,7 +167,9 @@ def _load(name: str, sources, defines=()) -> ctypes.CDLL:
 
 
 def core_library() -> ctypes.CDLL:
-    return _load("janis_core", CORE_SOURCES)
+    extra = [d for d in os.environ.get("JANIS_CORE_DEFINES", "").split(",") if d]      # tuning experiments
+    tag = "_" + "_".join(d.replace("=", "") for d in extra) if extra else ""
+    return _load(f"janis_core{tag}", CORE_SOURCES, extra)
 
 
 def attention_library(head_dim: int) -> ctypes.CDLL:

@@ -31,7 +31,10 @@ namespace tc {
 
 constexpr int BLOCK_N = 128;          // rows of W per CTA (TMEM lanes)
 constexpr int BLOCK_K = 64;           // bf16 elements per stage along K: one 128-byte swizzle row
-constexpr int STAGES = 6;
+#ifndef JANIS_TC05_STAGES
+#define JANIS_TC05_STAGES 3      // 73 KB a CTA: two CTAs share an SM, one's epilogue under the other's loads
+#endif
+constexpr int STAGES = JANIS_TC05_STAGES;
 constexpr int MAX_M = 64;
 constexpr int THREADS = 128;
 constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;                    // 16 KB
@@ -51,10 +54,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, int bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int it = 0; it < (1 << 18); ++it) {        // each try blocks for a while by itself: seconds in all
+    // test_wait polls without suspending the thread (try_wait may park it for a while, which costs a stage's
+    // worth of latency at every hand-over); about a second's worth of polls, then give up
+    for (int it = 0; it < (1 << 26); ++it) {
         uint32_t done;
         asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
             : "=r"(done)
             : "r"(bar), "r"(parity)
             : "memory");

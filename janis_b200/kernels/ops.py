@@ -21,6 +21,7 @@ from ..csrc import build
 PAGE = 64                      # tokens per cache page (JANIS_PAGE in the CUDA sources)
 GEMV_MAX_ROWS = 64             # what the skinny kernel accepts
 GEMV_FAST_ROWS = 16            # up to here it beats the library product (above, each warp re-reads too much of x)
+TC05_MAX_ROWS = 64             # rows the tcgen05 skinny product takes
 EPI_NONE, EPI_GATED_GELU, EPI_SOFTCAP, EPI_GATED_SILU = 0, 1, 2, 3
 GATE_GROUP = 8                 # fused gate/up rows alternate in groups of 8
 ACT_GELU_TANH, ACT_SILU = 0, 1

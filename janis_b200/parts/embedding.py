@@ -57,6 +57,8 @@ class LMHead(Part):
             return ops.gemm_f32(y, self.table, out, self.softcap)
         if R <= ops.GEMV_FAST_ROWS:
             return ops.gemv_bf16(y, self.table, out, ops.EPI_SOFTCAP, self.softcap)
+        if R <= ops.TC05_MAX_ROWS:
+            return ops.gemm_tc05(y, self.table, out, ops.EPI_SOFTCAP, self.softcap)   # float32 logits straight from tensor memory
         # many rows: the library's product with float32 output, then the cap
         ops.matmul_bf16_to_f32(y, self.table, out)
         if self.softcap > 0:

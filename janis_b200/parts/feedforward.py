@@ -61,9 +61,12 @@ class GatedMLP(FeedForward):
         rt, ws, ops = ctx.rt, ctx.ws, ctx.rt.ops
         T, I = ctx.n_tok, self.intermediate
         a = ws.buf("ffn.act", (T, I), rt.dtype)
+        epi = ops.EPI_GATED_GELU if self.act == 0 else ops.EPI_GATED_SILU
         if rt.dtype == torch.bfloat16 and T <= ops.GEMV_FAST_ROWS:
-            ops.gemv_bf16(x, self.w_gu, a, ops.EPI_GATED_GELU if self.act == 0 else ops.EPI_GATED_SILU)
+            ops.gemv_bf16(x, self.w_gu, a, epi)
         else:
+            # (ops.gemm_tc05 computes this product with the activation fused for 17..64 rows, but at these
+            # shapes the library product plus the activation kernel is still the faster pair)
             gu = ws.buf("ffn.gu", (T, 2 * I), rt.dtype)
             rt.linear(x, self.w_gu, gu)
             ops.gated_act(gu, a, self.act, self.GROUP)

@@ -121,6 +121,13 @@ def softcap(x, cap):
     return x
 
 
+TC05_MAX_ROWS = 64
+
+
+def gemm_tc05(x, w, out, epilogue=EPI_NONE, cap=0.0, split=0):
+    return gemv_bf16(x, w, out, epilogue, cap)
+
+
 def linear_bf16(x, w, out):
     return gemv_bf16(x, w, out)
 
