@@ -264,8 +264,9 @@ def run(steps: int = 64, warmup: int = 8, batch: int = 8, context: int = 8192, c
         raw = dict(raw, num_hidden_layers=int(layers))
     pk, pk_kind = peaks()
     max_batch = max([batch, *points])
-    eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=max_batch * context, max_batch=max_batch,
-                                 max_context=context)
+    room = max(context, prefill_tokens)                 # the prefill measurement needs its own length to fit
+    eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=max_batch * room, max_batch=max_batch,
+                                 max_context=room)
     main = measure_decode(eng, batch, context, steps, warmup, sample_clocks=True)
     pts = {}
     for b in points:

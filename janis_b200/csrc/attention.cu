@@ -146,6 +146,8 @@ attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ kv_src, con
     typedef Geo<T> G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * ATTN_WARPS + warp;
+    grid_dependents_launch();
+    grid_dependency_wait();
     if (t >= n_tok) return;
     const int rep = nq / nkv;
     const int groups = (rep + G::RG - 1) / G::RG;
@@ -249,6 +251,8 @@ attn_decode_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool, const
     typedef Geo<T> G;
     __shared__ float sm[ATTN_WARPS][G::RG][HD + 2];
     const int s = blockIdx.z;
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int slot = seq_slot[s];
     if (slot < 0) return;
     const int len = seq_len[s];
@@ -368,6 +372,8 @@ attn_decode_staged_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool
     extern __shared__ __align__(128) unsigned char stage_mem[];
     __shared__ __align__(8) unsigned long long full[S::STAGES];
     const int s = blockIdx.z;
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int slot = seq_slot[s];
     if (slot < 0) return;
     const int len = seq_len[s];
@@ -486,12 +492,16 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
     extern __shared__ __align__(128) unsigned char stage_mem[];
     __shared__ __align__(8) unsigned long long full[S::STAGES];
     const int s = blockIdx.z;
+    grid_dependents_launch();
+    // The step's tables (slots, lengths, pages) are written before the step's first kernel, and every
+    // key but the newest was stored by an earlier step: the first tiles are asked for before this
+    // kernel waits for the one that stores the newest key and rotates the queries.
     const int slot = seq_slot[s];
-    if (slot < 0) return;
+    if (slot < 0) { grid_dependency_wait(); return; }
     const int len = seq_len[s];
     int lo, first_chunk, n_chunks;
     chunk_range(len, window, chunk, lo, first_chunk, n_chunks);
-    if ((int)blockIdx.x >= n_chunks) return;
+    if ((int)blockIdx.x >= n_chunks) { grid_dependency_wait(); return; }
     const int c = first_chunk + blockIdx.x;
     const int k_begin = max(lo, c * chunk), k_end = min(len, (c + 1) * chunk);
 
@@ -525,8 +535,20 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
         bulk_load(dst, kpool + off, S::TILE_BYTES, bar);
         bulk_load(dst + S::TILE_BYTES, vpool + off, S::TILE_BYTES, bar);
     };
+    // a tile may be read early unless it holds the place the newest key goes to (position len - 1, which
+    // in a ring is also the place of position len - 1 - ring_len)
+    auto early = [&](int i) {
+        const int p0 = t_first + i * S::TILE;
+        const int newest = len - 1, shadow = len - 1 - ring_len;
+        return !(newest >= p0 && newest < p0 + S::TILE) && !(ring_len > 0 && shadow >= p0 && shadow < p0 + S::TILE);
+    };
     if (threadIdx.x == 0)
-        for (int i = 0; i < S::STAGES && i < n_tiles; ++i) issue(i);
+        for (int i = 0; i < S::STAGES && i < n_tiles; ++i)
+            if (early(i)) issue(i);
+    grid_dependency_wait();
+    if (threadIdx.x == 0)
+        for (int i = 0; i < S::STAGES && i < n_tiles; ++i)
+            if (!early(i)) issue(i);
 
     // query fragments: row g of the 16-row operand is head h0 + g (zero beyond nh_here); a thread keeps, for
     // each block of 32 features, the 8 features t*8 .. t*8+7 as the pairs that two k-steps want
@@ -700,6 +722,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const int* 
     extern __shared__ float wgt[];            // max_chunks weights
     __shared__ float red[32];
     const int s = blockIdx.x, h = blockIdx.y;
+    grid_dependents_launch();
+    grid_dependency_wait();
     T* o = out + ((size_t)s * nq + h) * HD;
     if (seq_slot[s] < 0) {
         for (int d = threadIdx.x; d < HD; d += blockDim.x) o[d] = from_float<T>(0.f);
@@ -748,6 +772,9 @@ using namespace janis;
 
 JANIS_EXPORT int janis_attn_head_dim() { return HD; }
 
+// 0: launch every kernel of this library plainly; 1 (default): let a kernel's CTAs arrive while the one before it runs
+JANIS_EXPORT void janis_attn_set_overlap(int on) { overlap_launches() = on ? 1 : 0; }
+
 // floats of scratch that a decode call with these sizes needs
 JANIS_EXPORT long long janis_attn_decode_scratch(int n_seq, int nq, int max_chunks) {
     return (long long)n_seq * nq * max_chunks * (HD + 2);
@@ -767,18 +794,17 @@ JANIS_EXPORT int janis_attn_prefill(const void* qkv, const void* kv_src, int dty
     dim3 grid((n_tok + ATTN_WARPS - 1) / ATTN_WARPS, 1, 1);
     if (dtype == JANIS_F32) {
         grid.y = nkv * ((rep + Geo<float>::RG - 1) / Geo<float>::RG);
-        attn_prefill_kernel<float><<<grid, ATTN_WARPS * 32, 0, stream>>>(
-            (const float*)qkv, (const float*)kv_src, tok_pos, tok_seq, seq_first_row, (float*)out, n_tok, nq, nkv,
-            q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window);
-    } else if (dtype == JANIS_BF16) {
-        grid.y = nkv * ((rep + Geo<bf16>::RG - 1) / Geo<bf16>::RG);
-        attn_prefill_kernel<bf16><<<grid, ATTN_WARPS * 32, 0, stream>>>(
-            (const bf16*)qkv, (const bf16*)kv_src, tok_pos, tok_seq, seq_first_row, (bf16*)out, n_tok, nq, nkv,
-            q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window);
-    } else {
-        return fail("attn_prefill: unknown dtype %d", dtype);
+        return launch_kernel("attn_prefill", attn_prefill_kernel<float>, grid, dim3(ATTN_WARPS * 32), 0, stream, 1,
+                             (const float*)qkv, (const float*)kv_src, tok_pos, tok_seq, seq_first_row, (float*)out, n_tok, nq,
+                             nkv, q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window);
     }
-    return launched("attn_prefill");
+    if (dtype == JANIS_BF16) {
+        grid.y = nkv * ((rep + Geo<bf16>::RG - 1) / Geo<bf16>::RG);
+        return launch_kernel("attn_prefill", attn_prefill_kernel<bf16>, grid, dim3(ATTN_WARPS * 32), 0, stream, 1,
+                             (const bf16*)qkv, (const bf16*)kv_src, tok_pos, tok_seq, seq_first_row, (bf16*)out, n_tok, nq,
+                             nkv, q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window);
+    }
+    return fail("attn_prefill: unknown dtype %d", dtype);
 }
 
 static int g_decode_kernel = 2;     // 2: staged, scores on the tensor cores (bfloat16, head sizes <= 256);
@@ -810,10 +836,9 @@ static int launch_decode_mma_rb(const bf16* qkv, const bf16* kpool, const bf16* 
     }
     const int rep = nq / nkv;
     dim3 grid(max_chunks, nkv * ((rep + RB - 1) / RB), n_seq);
-    attn_decode_mma_kernel<RB><<<grid, MmaDecode::WARPS * 32, MmaDecode::SMEM_BYTES, stream>>>(
-        qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv, q_row_heads, scale, cap, window,
-        ring_len, chunk);
-    return launched("attn_decode");
+    return launch_kernel("attn_decode", attn_decode_mma_kernel<RB>, grid, dim3(MmaDecode::WARPS * 32), MmaDecode::SMEM_BYTES,
+                         stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv,
+                         q_row_heads, scale, cap, window, ring_len, chunk);
 }
 
 static int launch_decode_mma(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table, int table_stride,
@@ -853,21 +878,21 @@ static int launch_decode(const T* qkv, const T* kpool, const T* vpool, const int
                                               cudaGetErrorString(e));
             configured = true;
         }
-        attn_decode_staged_kernel<T><<<grid, Staged<T>::WARPS * 32, Staged<T>::SMEM_BYTES, stream>>>(
-            qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv, q_row_heads, scale, cap,
-            window, ring_len, chunk);
+        if (launch_kernel("attn_decode", attn_decode_staged_kernel<T>, grid, dim3(Staged<T>::WARPS * 32), Staged<T>::SMEM_BYTES,
+                          stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv,
+                          q_row_heads, scale, cap, window, ring_len, chunk))
+            return 1;
     } else {
         dim3 grid(max_chunks, nkv * ((rep + Geo<T>::RG - 1) / Geo<T>::RG), n_seq);
-        attn_decode_kernel<T><<<grid, ATTN_WARPS * 32, 0, stream>>>(qkv, kpool, vpool, page_table, table_stride, seq_slot,
-                                                                   seq_len, partial, nq, nkv, q_row_heads, scale, cap,
-                                                                   window, ring_len, chunk);
+        if (launch_kernel("attn_decode", attn_decode_kernel<T>, grid, dim3(ATTN_WARPS * 32), 0, stream, 1, qkv, kpool, vpool,
+                          page_table, table_stride, seq_slot, seq_len, partial, nq, nkv, q_row_heads, scale, cap, window,
+                          ring_len, chunk))
+            return 1;
     }
-    if (!(g_decode_kernel == 2 && sizeof(T) == 2 && MmaDecode::OK) && launched("attn_decode")) return 1;
     dim3 mgrid(n_seq, nq);
     const int mthreads = HD < 256 ? (HD < 32 ? 32 : HD) : 256;
-    attn_merge_kernel<T><<<mgrid, mthreads, max_chunks * sizeof(float), stream>>>(partial, seq_slot, seq_len, out, nq,
-                                                                                   max_chunks, window, chunk);
-    return launched("attn_merge");
+    return launch_kernel("attn_merge", attn_merge_kernel<T>, mgrid, dim3(mthreads), max_chunks * sizeof(float), stream, 1,
+                         (const float*)partial, seq_slot, seq_len, out, nq, max_chunks, window, chunk);
 }
 
 JANIS_EXPORT int janis_attn_decode(const void* qkv, const void* kpool, const void* vpool, int dtype,

@@ -43,6 +43,70 @@ inline int launched(const char* what) {
     return 0;
 }
 
+// Programmatic dependent launch.  Every kernel of this library is launched so that
+// its CTAs may become resident while the kernel before it in the stream is still
+// running: it calls grid_dependents_launch() at its top and grid_dependency_wait()
+// before it touches anything an earlier kernel wrote or still reads; one of the two
+// (see JANIS_RUN_AHEAD) tells the hardware that the next kernel may start arriving.  What comes before the wait may only read constants of the
+// model (weights).  The wait returns when the whole preceding grid has finished and
+// its writes are visible, so the order of the stream is kept link by link.  Without
+// the launch attribute both instructions do nothing.
+//
+// JANIS_RUN_AHEAD = 0 (default): the next kernel may arrive only once this one has passed its own
+// wait, so at most two kernels share the GPU (one running, one with its weights on the way).
+// JANIS_RUN_AHEAD = 1: the next kernel may arrive as soon as this one is resident, and so on down
+// the stream; kernels that only wait then hold registers and shared memory of several layers.
+#ifndef JANIS_RUN_AHEAD
+#define JANIS_RUN_AHEAD 0
+#endif
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#if !JANIS_RUN_AHEAD
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void grid_dependents_launch() {
+#if JANIS_RUN_AHEAD
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+// one switch per library (the wrapper sets it in each): 0 launches plainly
+inline int& overlap_launches() {
+    static int on = 1;
+    return on;
+}
+
+// Launch with the attribute above, and as thread-block clusters of `cluster` CTAs when cluster > 1.
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, int cluster, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (overlap_launches()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return fail("%s: launch failed: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
 

@@ -14,6 +14,8 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ out, int H, int V, float scale) {
     const int t = blockIdx.x;
+    grid_dependents_launch();
+    grid_dependency_wait();                 // the tokens may come from the sampling kernel of the step before
     int tok = tokens[t];
     if (tok < 0 || tok >= V) tok = 0;   // the host has checked the ids; padding rows carry 0
     const T* row = table + (size_t)tok * H;
@@ -29,6 +31,8 @@ __global__ void rmsnorm_kernel(const TI* __restrict__ x, const float* __restrict
                                const int* __restrict__ rows, TO* __restrict__ y, int H, float eps) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int src = rows ? rows[r] : r;
     const TI* xr = x + (size_t)src * H;
     float ss = 0.f;
@@ -57,6 +61,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TR* __restrict__
     const int r = blockIdx.x;
     const TR* rr = res + (size_t)r * H;
     float* hr = h + (size_t)r * H;
+    grid_dependents_launch();
+    grid_dependency_wait();
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = to_float(rr[i]);
@@ -91,7 +97,15 @@ add_rmsnorm_reg_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_
     const int r = blockIdx.x;
     const TR* rr = res + (size_t)r * H;
     float* hr = h + (size_t)r * H;
-    float v[EPT], hv[EPT];
+    float v[EPT], hv[EPT], wp[EPT], wn[EPT];
+    grid_dependents_launch();
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {         // the norms' weights are constants: read them while the producer still runs
+        const int i = threadIdx.x + k * 256;
+        wp[k] = (w_post && i < H) ? w_post[i] : 0.f;
+        wn[k] = (w_next && i < H) ? w_next[i] : 0.f;
+    }
+    grid_dependency_wait();
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
@@ -112,7 +126,7 @@ add_rmsnorm_reg_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_
     for (int k = 0; k < EPT; ++k) {
         const int i = threadIdx.x + k * 256;
         if (i < H) {
-            hv[k] = hv[k] + (w_post ? v[k] * inv * w_post[i] : v[k]);
+            hv[k] = hv[k] + (w_post ? v[k] * inv * wp[k] : v[k]);
             hr[i] = hv[k];
             ss2 = fmaf(hv[k], hv[k], ss2);
         }
@@ -124,7 +138,7 @@ add_rmsnorm_reg_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_
 #pragma unroll
     for (int k = 0; k < EPT; ++k) {
         const int i = threadIdx.x + k * 256;
-        if (i < H) yr[i] = from_float<TO>(hv[k] * inv2 * w_next[i]);
+        if (i < H) yr[i] = from_float<TO>(hv[k] * inv2 * wn[k]);
     }
 }
 
@@ -136,6 +150,8 @@ add_rmsnorm_reg_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int rows, int I, int group,
                                  int act) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     const size_t n = (size_t)rows * I;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -149,6 +165,8 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
 
 // the same for bfloat16 and groups of 8: a thread takes 8 gates and their 8 ups as two 16-byte loads
 __global__ void gated_act8_bf16_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, size_t n_groups, int act) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_groups; q += (size_t)gridDim.x * blockDim.x) {
         float g[8], u[8], o[8];
         Vec16<bf16>::load(gu + q * 16, g);
@@ -164,6 +182,8 @@ __global__ void gated_act8_bf16_kernel(const bf16* __restrict__ gu, bf16* __rest
 // ---------------------------------------------------------------------------
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
     const float inv = 1.0f / cap;
+    grid_dependents_launch();
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         x[i] = cap * tanhf(x[i] * inv);
 }
@@ -183,48 +203,61 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
                                   const int* __restrict__ seq_end, const float* __restrict__ inv_freq,
                                   int rot, int nq, int nkv, int hd, int row_heads, T* __restrict__ kpool,
                                   T* __restrict__ vpool, const int* __restrict__ page_table,
-                                  int table_stride, int ring_len, int store_q_only) {
-    extern __shared__ float cs[];          // cos[rot/2], sin[rot/2]
+                                  int table_stride, int ring_len, int n_heads, int heads_per_cta) {
+    // A CTA takes heads [blockIdx.y * heads_per_cta, ...) of token blockIdx.x: heads 0..nq-1 are queries,
+    // then nkv key heads, then nkv value heads (n_heads = nq when only queries are rotated).  Few tokens
+    // (decoding) spread their heads over CTAs; many tokens take all heads of a token in one CTA.
     const int t = blockIdx.x;
-    const int pos = tok_pos[t];
     const int half = rot >> 1;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const float theta = (float)pos * inv_freq[i];
-        float s, c;
-        sincosf(theta, &s, &c);
-        cs[i] = c;
-        cs[half + i] = s;
+    grid_dependents_launch();
+    // The step's tables (positions, slots, ends, pages) are written before the step's first kernel and
+    // inv_freq is a constant of the model: the place in the cache and the angle are found before the wait.
+    const int pos = tok_pos[t];
+    long long place = -1;                    // element offset of this token's row of head 0 in a pool
+    if (kpool != nullptr && n_heads > nq) {
+        const int seq = tok_seq[t];
+        const int slot = seq_slot[seq];
+        int idx = pos;
+        bool keep = slot >= 0;
+        if (keep && ring_len > 0) {
+            keep = pos >= seq_end[seq] - ring_len;
+            idx = pos % ring_len;
+        }
+        if (keep) {
+            const int page = page_table[(size_t)slot * table_stride + idx / JANIS_PAGE];
+            place = ((long long)page * nkv * JANIS_PAGE + idx % JANIS_PAGE) * hd;
+        }
     }
-    __syncthreads();
-    T* row = qkv + (size_t)t * row_heads * hd;
-    const int n_rot_heads = store_q_only ? nq : nq + nkv;
-    for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
-        const int head = idx / half, i = idx % half;
-        T* p = row + (size_t)head * hd;
-        const float a = to_float(p[i]), b = to_float(p[i + half]);
-        const float c = cs[i], s = cs[half + i];
-        p[i] = from_float<T>(a * c - b * s);
-        p[i + half] = from_float<T>(a * s + b * c);
-    }
-    if (store_q_only || kpool == nullptr) return;
-    const int seq = tok_seq[t];
-    const int slot = seq_slot[seq];
-    if (slot < 0) return;
-    int idx = pos;
-    if (ring_len > 0) {
-        if (pos < seq_end[seq] - ring_len) return;
-        idx = pos % ring_len;
-    }
-    const int page = page_table[(size_t)slot * table_stride + idx / JANIS_PAGE];
-    const int off = idx % JANIS_PAGE;
-    __syncthreads();                        // the rotated k of this row is complete
-    const T* ksrc = row + (size_t)nq * hd;
-    const T* vsrc = row + (size_t)(nq + nkv) * hd;
-    for (int e = threadIdx.x; e < nkv * hd; e += blockDim.x) {
-        const int kvh = e / hd, d = e % hd;
-        const size_t dst = (((size_t)page * nkv + kvh) * JANIS_PAGE + off) * hd + d;
-        kpool[dst] = ksrc[e];
-        vpool[dst] = vsrc[e];
+    // thread i owns the pair (i, i + half) below half and the single feature i from rot on
+    const int i0 = threadIdx.x;
+    float s0 = 0.f, c0 = 1.f;
+    if (i0 < half) sincosf((float)pos * inv_freq[i0], &s0, &c0);
+    grid_dependency_wait();
+    const int h_end = min(n_heads, ((int)blockIdx.y + 1) * heads_per_cta);
+    for (int head = blockIdx.y * heads_per_cta; head < h_end; ++head) {
+        const bool is_k = head >= nq && head < nq + nkv, is_v = head >= nq + nkv;
+        T* p = qkv + ((size_t)t * row_heads + head) * hd;
+        T* dst = nullptr;                    // this head's row in the cache, if it is stored
+        if (place >= 0 && (is_k || is_v))
+            dst = (is_k ? kpool : vpool) + place + (size_t)(is_k ? head - nq : head - nq - nkv) * JANIS_PAGE * hd;
+        if (is_v) {
+            if (dst)
+                for (int d = i0; d < hd; d += blockDim.x) dst[d] = p[d];
+            continue;
+        }
+        for (int i = i0; i < hd; i += blockDim.x) {
+            if (i < half) {
+                float s = s0, c = c0;
+                if (i != i0) sincosf((float)pos * inv_freq[i], &s, &c);
+                const float a = to_float(p[i]), b = to_float(p[i + half]);
+                const T lo = from_float<T>(a * c - b * s), hi = from_float<T>(a * s + b * c);
+                p[i] = lo;
+                p[i + half] = hi;
+                if (dst) { dst[i] = lo; dst[i + half] = hi; }
+            } else if (i >= rot) {
+                if (dst) dst[i] = p[i];
+            }
+        }
     }
 }
 
@@ -234,30 +267,50 @@ using namespace janis;
 
 static inline int row_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
 
+// 0: launch every kernel of this library plainly; 1 (default): let a kernel's CTAs arrive while the one before it runs
+JANIS_EXPORT void janis_set_overlap(int on) { overlap_launches() = on ? 1 : 0; }
+
 JANIS_EXPORT int janis_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H,
                              int V, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
+    const dim3 grid(T), block(row_threads(H));
     if (table_dtype == JANIS_F32)
-        embed_kernel<float><<<T, row_threads(H), 0, stream>>>(tokens, (const float*)table, out, H, V, scale);
-    else if (table_dtype == JANIS_BF16)
-        embed_kernel<bf16><<<T, row_threads(H), 0, stream>>>(tokens, (const bf16*)table, out, H, V, scale);
-    else
-        return fail("embed: unknown table dtype %d", table_dtype);
-    return launched("embed");
+        return launch_kernel("embed", embed_kernel<float>, grid, block, 0, stream, 1, tokens, (const float*)table, out, H, V,
+                             scale);
+    if (table_dtype == JANIS_BF16)
+        return launch_kernel("embed", embed_kernel<bf16>, grid, block, 0, stream, 1, tokens, (const bf16*)table, out, H, V,
+                             scale);
+    return fail("embed: unknown table dtype %d", table_dtype);
 }
 
 JANIS_EXPORT int janis_rmsnorm(const void* x, int x_dtype, const float* w, const int* rows, void* y, int y_dtype,
                                int R, int H, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
-    const int nt = row_threads(H);
-#define JANIS_CASE(TI, TO) rmsnorm_kernel<TI, TO><<<R, nt, 0, stream>>>((const TI*)x, w, rows, (TO*)y, H, eps)
+    const dim3 grid(R), block(row_threads(H));
+#define JANIS_CASE(TI, TO) \
+    return launch_kernel("rmsnorm", rmsnorm_kernel<TI, TO>, grid, block, 0, stream, 1, (const TI*)x, w, rows, (TO*)y, H, eps)
     if (x_dtype == JANIS_F32 && y_dtype == JANIS_F32) JANIS_CASE(float, float);
-    else if (x_dtype == JANIS_F32 && y_dtype == JANIS_BF16) JANIS_CASE(float, bf16);
-    else if (x_dtype == JANIS_BF16 && y_dtype == JANIS_F32) JANIS_CASE(bf16, float);
-    else if (x_dtype == JANIS_BF16 && y_dtype == JANIS_BF16) JANIS_CASE(bf16, bf16);
-    else return fail("rmsnorm: unknown dtypes %d -> %d", x_dtype, y_dtype);
+    if (x_dtype == JANIS_F32 && y_dtype == JANIS_BF16) JANIS_CASE(float, bf16);
+    if (x_dtype == JANIS_BF16 && y_dtype == JANIS_F32) JANIS_CASE(bf16, float);
+    if (x_dtype == JANIS_BF16 && y_dtype == JANIS_BF16) JANIS_CASE(bf16, bf16);
 #undef JANIS_CASE
-    return launched("rmsnorm");
+    return fail("rmsnorm: unknown dtypes %d -> %d", x_dtype, y_dtype);
+}
+
+template <typename TR, typename TO>
+static int launch_add_rmsnorm(float* h, const TR* res, int n_part, size_t part_stride, const float* w_post, float eps_post,
+                              const float* w_next, float eps_next, TO* y, int R, int H, cudaStream_t stream) {
+    // rows up to 8192 wide stay in registers (each input read once); wider rows take three passes
+#define JANIS_REG(EPT)                                                                                             \
+    return launch_kernel("add_rmsnorm", add_rmsnorm_reg_kernel<TR, TO, EPT>, dim3(R), dim3(256), 0, stream, 1, h, res, \
+                         n_part, part_stride, w_post, eps_post, w_next, eps_next, y, H)
+    if (H <= 1024) JANIS_REG(4);
+    if (H <= 2048) JANIS_REG(8);
+    if (H <= 4096) JANIS_REG(16);
+    if (H <= 8192) JANIS_REG(32);
+#undef JANIS_REG
+    return launch_kernel("add_rmsnorm", add_rmsnorm_kernel<TR, TO>, dim3(R), dim3(row_threads(H)), 0, stream, 1, h, res,
+                         n_part, part_stride, w_post, eps_post, w_next, eps_next, y, H);
 }
 
 JANIS_EXPORT int janis_add_rmsnorm(float* h, const void* res, int res_dtype, int n_part, long long part_stride,
@@ -266,28 +319,15 @@ JANIS_EXPORT int janis_add_rmsnorm(float* h, const void* res, int res_dtype, int
     if (R <= 0) return 0;
     if (n_part < 1) return fail("add_rmsnorm: n_part must be >= 1");
     if (w_next != nullptr && y == nullptr) return fail("add_rmsnorm: a next norm needs an output");
-    const int nt = row_threads(H);
-    // rows up to 8192 wide stay in registers (each input read once); wider rows take three passes
-#define JANIS_REG(TR, TO, EPT)                                                                                  \
-    add_rmsnorm_reg_kernel<TR, TO, EPT><<<R, 256, 0, stream>>>(h, (const TR*)res, n_part, (size_t)part_stride,   \
-                                                               w_post, eps_post, w_next, eps_next, (TO*)y, H)
-#define JANIS_CASE(TR, TO)                                                                                      \
-    do {                                                                                                        \
-        if (H <= 1024) JANIS_REG(TR, TO, 4);                                                                    \
-        else if (H <= 2048) JANIS_REG(TR, TO, 8);                                                               \
-        else if (H <= 4096) JANIS_REG(TR, TO, 16);                                                              \
-        else if (H <= 8192) JANIS_REG(TR, TO, 32);                                                              \
-        else add_rmsnorm_kernel<TR, TO><<<R, nt, 0, stream>>>(h, (const TR*)res, n_part, (size_t)part_stride,    \
-                                                              w_post, eps_post, w_next, eps_next, (TO*)y, H);   \
-    } while (0)
+#define JANIS_CASE(TR, TO)                                                                                        \
+    return launch_add_rmsnorm<TR, TO>(h, (const TR*)res, n_part, (size_t)part_stride, w_post, eps_post, w_next,    \
+                                      eps_next, (TO*)y, R, H, stream)
     if (res_dtype == JANIS_F32 && y_dtype == JANIS_F32) JANIS_CASE(float, float);
-    else if (res_dtype == JANIS_F32 && y_dtype == JANIS_BF16) JANIS_CASE(float, bf16);
-    else if (res_dtype == JANIS_BF16 && y_dtype == JANIS_F32) JANIS_CASE(bf16, float);
-    else if (res_dtype == JANIS_BF16 && y_dtype == JANIS_BF16) JANIS_CASE(bf16, bf16);
-    else return fail("add_rmsnorm: unknown dtypes %d -> %d", res_dtype, y_dtype);
+    if (res_dtype == JANIS_F32 && y_dtype == JANIS_BF16) JANIS_CASE(float, bf16);
+    if (res_dtype == JANIS_BF16 && y_dtype == JANIS_F32) JANIS_CASE(bf16, float);
+    if (res_dtype == JANIS_BF16 && y_dtype == JANIS_BF16) JANIS_CASE(bf16, bf16);
 #undef JANIS_CASE
-#undef JANIS_REG
-    return launched("add_rmsnorm");
+    return fail("add_rmsnorm: unknown dtypes %d -> %d", res_dtype, y_dtype);
 }
 
 JANIS_EXPORT int janis_gated_act(const void* gu, void* out, int dtype, int rows, int I, int group, int act,
@@ -298,25 +338,26 @@ JANIS_EXPORT int janis_gated_act(const void* gu, void* out, int dtype, int rows,
     const int nt = 256;
     const int nb = (int)((n + nt - 1) / nt < 148 * 16 ? (n + nt - 1) / nt : 148 * 16);
     if (dtype == JANIS_F32)
-        gated_act_kernel<float><<<nb, nt, 0, stream>>>((const float*)gu, (float*)out, rows, I, group, act);
-    else if (dtype == JANIS_BF16 && group == 8 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+        return launch_kernel("gated_act", gated_act_kernel<float>, dim3(nb), dim3(nt), 0, stream, 1, (const float*)gu,
+                             (float*)out, rows, I, group, act);
+    if (dtype == JANIS_BF16 && group == 8 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
         const size_t n_groups = n / 8;        // rows * I / 8: group q of a row-major [rows, 2I] starts at 16 q
         const size_t want = (n_groups + nt - 1) / nt;
-        gated_act8_bf16_kernel<<<(int)(want < 148 * 32 ? want : 148 * 32), nt, 0, stream>>>((const bf16*)gu, (bf16*)out,
-                                                                                             n_groups, act);
-    } else if (dtype == JANIS_BF16)
-        gated_act_kernel<bf16><<<nb, nt, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I, group, act);
-    else
-        return fail("gated_act: unknown dtype %d", dtype);
-    return launched("gated_act");
+        return launch_kernel("gated_act", gated_act8_bf16_kernel, dim3((int)(want < 148 * 32 ? want : 148 * 32)), dim3(nt),
+                             0, stream, 1, (const bf16*)gu, (bf16*)out, n_groups, act);
+    }
+    if (dtype == JANIS_BF16)
+        return launch_kernel("gated_act", gated_act_kernel<bf16>, dim3(nb), dim3(nt), 0, stream, 1, (const bf16*)gu,
+                             (bf16*)out, rows, I, group, act);
+    return fail("gated_act: unknown dtype %d", dtype);
 }
 
 JANIS_EXPORT int janis_softcap(float* x, long long n, float cap, cudaStream_t stream) {
     if (n <= 0 || !(cap > 0.f)) return 0;
     const int nt = 256;
     const long long want = (n + nt - 1) / nt;
-    softcap_kernel<<<(int)(want < 148 * 32 ? want : 148 * 32), nt, 0, stream>>>(x, (size_t)n, cap);
-    return launched("softcap");
+    return launch_kernel("softcap", softcap_kernel, dim3((int)(want < 148 * 32 ? want : 148 * 32)), dim3(nt), 0, stream, 1,
+                         x, (size_t)n, cap);
 }
 
 JANIS_EXPORT int janis_rope_store(void* qkv, int dtype, const int* tok_pos, const int* tok_seq,
@@ -328,21 +369,22 @@ JANIS_EXPORT int janis_rope_store(void* qkv, int dtype, const int* tok_pos, cons
     if (rot < 0 || rot > hd || (rot & 1)) return fail("rope_store: rotary width %d does not fit head size %d", rot, hd);
     if (row_heads < (store_q_only ? nq : nq + 2 * nkv)) return fail("rope_store: rows of %d heads are too short", row_heads);
     if (ring_len % JANIS_PAGE) return fail("rope_store: ring length %d is not a multiple of the page", ring_len);
-    const size_t smem = (size_t)rot * sizeof(float);
-    if (smem > 48 * 1024) return fail("rope_store: rotary width %d too large", rot);
-    const int nt = 256;
+    const int heads = store_q_only ? nq : nq + 2 * nkv;
+    // few tokens: a CTA per head; many: up to 4 heads per CTA, which share the angles
+    int per = (int)(((long long)T * heads) / 2048);
+    per = per < 1 ? 1 : (per > 4 ? 4 : per);
+    const int want = rot < hd ? hd : hd / 2;                 // threads that have an element of their own
+    const int nt = want >= 256 ? 256 : ((want + 31) / 32) * 32;
+    const dim3 grid(T, (heads + per - 1) / per), block(nt < 32 ? 32 : nt);
     if (dtype == JANIS_F32)
-        rope_store_kernel<float><<<T, nt, smem, stream>>>((float*)qkv, tok_pos, tok_seq, seq_slot, seq_end,
-                                                          inv_freq, rot, nq, nkv, hd, row_heads, (float*)kpool,
-                                                          (float*)vpool, page_table, table_stride, ring_len,
-                                                          store_q_only);
-    else if (dtype == JANIS_BF16)
-        rope_store_kernel<bf16><<<T, nt, smem, stream>>>((bf16*)qkv, tok_pos, tok_seq, seq_slot, seq_end,
-                                                         inv_freq, rot, nq, nkv, hd, row_heads, (bf16*)kpool, (bf16*)vpool,
-                                                         page_table, table_stride, ring_len, store_q_only);
-    else
-        return fail("rope_store: unknown dtype %d", dtype);
-    return launched("rope_store");
+        return launch_kernel("rope_store", rope_store_kernel<float>, grid, block, 0, stream, 1, (float*)qkv, tok_pos, tok_seq,
+                             seq_slot, seq_end, inv_freq, rot, nq, nkv, hd, row_heads, (float*)kpool, (float*)vpool,
+                             page_table, table_stride, ring_len, heads, per);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("rope_store", rope_store_kernel<bf16>, grid, block, 0, stream, 1, (bf16*)qkv, tok_pos, tok_seq,
+                             seq_slot, seq_end, inv_freq, rot, nq, nkv, hd, row_heads, (bf16*)kpool, (bf16*)vpool,
+                             page_table, table_stride, ring_len, heads, per);
+    return fail("rope_store: unknown dtype %d", dtype);
 }
 
 JANIS_EXPORT const char* janis_last_error() { return error_buffer(); }

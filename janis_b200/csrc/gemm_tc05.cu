@@ -138,9 +138,19 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int nk = rank < nk_all ? (nk_all - rank + split - 1) / split : 0;
     const int b_bytes = Mpad * BLOCK_K * 2;
 
+    grid_dependents_launch();
     if (warp == 0 && lane == 0) {
-        // ---- producer: TMA loads into the ring
-        for (int i = 0; i < nk; ++i) {
+        // ---- producer: TMA loads into the ring.  The weights are constants of the model: the first
+        // tiles of W are on their way before this kernel waits for the one that produces x.
+        const int pre = nk < STAGES ? nk : STAGES;
+        for (int i = 0; i < pre; ++i) {
+            mbar_expect_tx(bar_full + 8 * i, A_BYTES + b_bytes);
+            tma_load_2d(stage0 + i * STAGE_BYTES, &map_w, (rank + i * split) * BLOCK_K, n0, bar_full + 8 * i);
+        }
+        grid_dependency_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(stage0 + i * STAGE_BYTES + A_BYTES, &map_x, (rank + i * split) * BLOCK_K, 0, bar_full + 8 * i);
+        for (int i = pre; i < nk; ++i) {
             const int s = i % STAGES;
             if (i >= STAGES && !mbar_wait(bar_empty + 8 * s, ((i / STAGES) - 1) & 1)) { atomicExch(&failed, 1); break; }
             const uint32_t a = stage0 + s * STAGE_BYTES, b = a + A_BYTES;
@@ -151,6 +161,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
     } else if (warp == 1 && lane == 0) {
         // ---- the thread that issues the products
+        grid_dependency_wait();
         const uint32_t idesc = instr_desc(BLOCK_N, Mpad);
         for (int i = 0; i < nk; ++i) {
             const int s = i % STAGES;
@@ -164,6 +175,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
         umma_commit(bar_done);                                        // all products of this CTA have finished
     }
+    else grid_dependency_wait();
     __syncwarp();
     // ---- everyone: wait for the accumulator
     bool ok = nk == 0 ? true : mbar_wait(bar_done, 0);
@@ -340,13 +352,18 @@ JANIS_EXPORT int janis_gemm_tc05(const void* x, const void* W, void* out, int ou
     cfg.blockDim = dim3(tc::THREADS);
     cfg.dynamicSmemBytes = tc::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = split;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (overlap_launches()) {            // the kernel may arrive while the one before it runs (see common.cuh)
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
     cudaError_t e;
     if (oi == 0)
         e = cudaLaunchKernelEx(&cfg, tc::gemm_tc05_kernel<bf16>, *mw, *mx, (bf16*)out, M, Mpad, N, K, split, epi, cap);

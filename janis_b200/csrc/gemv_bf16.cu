@@ -24,6 +24,10 @@ namespace cg = cooperative_groups;
 
 namespace janis {
 
+#ifndef JANIS_GEMV_AHEAD
+#define JANIS_GEMV_AHEAD 1            // rounds of weights asked for before the wait (0: none; a tuning switch)
+#endif
+
 constexpr int GEMV_WARPS = 8;        // warps of a CTA that split K (4 when N alone gives CTAs enough)
 
 enum { EPI_NONE = 0, EPI_GATED_GELU = 1, EPI_SOFTCAP = 2, EPI_GATED_SILU = 3 };
@@ -76,14 +80,38 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
 
     constexpr int SPLIT = NW * CL;             // warps that share the K of a tile
     const int nblk = (K + 31) / 32;
-    for (int kb = rank * NW + warp; kb < nblk; kb += SPLIT * U) {
-        uint4 a_lo[U], a_hi[U], b[U][MT];
+    // Weights are constants of the model: the first round of them is asked for (into L2) before
+    // this kernel waits for the one that produces x.
+    uint4 a_lo[U], a_hi[U];
+    auto load_w = [&](int kb0) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int k0 = (kb + u * SPLIT) * 32;
+            const int k0 = (kb0 + u * SPLIT) * 32;
             const bool in = k0 + t * 8 < K;          // K % 8 == 0: a 16-byte piece is all in or all out
             a_lo[u] = in ? ldg_stream(wlo + k0) : make_uint4(0, 0, 0, 0);
             a_hi[u] = in ? ldg_stream(whi + k0) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    int kb = rank * NW + warp;
+    grid_dependents_launch();
+#if JANIS_GEMV_AHEAD
+    // hints only: a load into registers would have to land before the wait below lets the thread go on
+    for (int pk = kb, n = 0; pk < nblk && n < JANIS_GEMV_AHEAD * U; pk += SPLIT, ++n) {
+        const int k0 = pk * 32;
+        if (k0 + t * 8 < K) {
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wlo + k0));
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(whi + k0));
+        }
+    }
+#endif
+    grid_dependency_wait();
+    for (; kb < nblk; kb += SPLIT * U) {
+        uint4 b[U][MT];
+        load_w(kb);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k0 = (kb + u * SPLIT) * 32;
+            const bool in = k0 + t * 8 < K;
 #pragma unroll
             for (int i = 0; i < MT; ++i)
                 b[u][i] = (in && xok[i]) ? *reinterpret_cast<const uint4*>(xr[i] + k0) : make_uint4(0, 0, 0, 0);
@@ -172,26 +200,13 @@ static int launch_one(const bf16* x, const bf16* W, TO* out, int M, int N, int K
     if (CL == 1) {
         // many tiles: CTAs of 4 warps, so that more of them are resident and the last wave is short
         if (tiles >= 1024 && g_gemv_small_ctas)
-            gemv_bf16_kernel<MT, U, 1, 4, TO><<<tiles, 4 * 32, 0, stream>>>(x, W, out, M, N, K, epi, cap);
-        else
-            gemv_bf16_kernel<MT, U, 1, GEMV_WARPS, TO><<<tiles, GEMV_WARPS * 32, 0, stream>>>(x, W, out, M, N, K, epi, cap);
-        return launched("gemv_bf16");
+            return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, 4, TO>, dim3(tiles), dim3(4 * 32), 0, stream, 1, x, W,
+                                 out, M, N, K, epi, cap);
+        return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, GEMV_WARPS, TO>, dim3(tiles), dim3(GEMV_WARPS * 32), 0,
+                             stream, 1, x, W, out, M, N, K, epi, cap);
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles * CL);
-    cfg.blockDim = dim3(GEMV_WARPS * 32);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CL;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<MT, U, CL, GEMV_WARPS, TO>, x, W, out, M, N, K, epi, cap);
-    if (e != cudaSuccess) return fail("gemv_bf16: cluster launch failed: %s", cudaGetErrorString(e));
-    return launched("gemv_bf16");
+    return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, CL, GEMV_WARPS, TO>, dim3(tiles * CL), dim3(GEMV_WARPS * 32), 0,
+                         stream, CL, x, W, out, M, N, K, epi, cap);
 }
 
 template <int MT, int U>

@@ -57,6 +57,8 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.x * V;
+    grid_dependents_launch();
+    grid_dependency_wait();
     float v = -INFINITY;
     int i = 0x7fffffff;
     // four independent loads per round keep the memory pipe busy (one dependent load per round is
@@ -138,6 +140,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, float* __
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ int chosen;
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * V;
     const int per = (V + blockDim.x - 1) / blockDim.x;
@@ -250,6 +254,8 @@ __global__ void repeat_penalty_kernel(float* __restrict__ logits, const int* __r
                                       int V, float penalty) {
     // recent: [R, n_recent], -1 where empty.  A token that occurs twice is changed once.
     const int r = blockIdx.x;
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int* rec = recent + (size_t)r * n_recent;
     for (int i = threadIdx.x; i < n_recent; i += blockDim.x) {
         const int tok = rec[i];
@@ -267,6 +273,8 @@ __global__ void repeat_penalty_kernel(float* __restrict__ logits, const int* __r
 __global__ void mask_tokens_kernel(float* __restrict__ logits, const int* __restrict__ ids, int n_ids, int R,
                                    int V) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    grid_dependents_launch();
+    grid_dependency_wait();
     if (idx >= R * n_ids) return;
     const int r = idx / n_ids, tok = ids[idx % n_ids];
     if (tok >= 0 && tok < V) logits[(size_t)r * V + tok] = -INFINITY;
@@ -279,8 +287,7 @@ using namespace janis;
 JANIS_EXPORT int janis_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return fail("argmax: empty vocabulary");
-    argmax_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, out, V);
-    return launched("argmax");
+    return launch_kernel("argmax", argmax_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 1, logits, out, V);
 }
 
 JANIS_EXPORT int janis_sample(const float* logits, int* out, float* u_out, int R, int V, float temp, float top_p,
@@ -289,21 +296,20 @@ JANIS_EXPORT int janis_sample(const float* logits, int* out, float* u_out, int R
     if (R <= 0) return 0;
     if (V <= 0) return fail("sample: empty vocabulary");
     if (!(temp > 0.f)) return fail("sample: temperature must be positive (greedy is argmax), found %g", temp);
-    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, out, u_out, V, temp, top_p, seed, request_ids,
-                                                     token_index);
-    return launched("sample");
+    return launch_kernel("sample", sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 1, logits, out, u_out, V, temp,
+                         top_p, seed, request_ids, token_index);
 }
 
 JANIS_EXPORT int janis_repeat_penalty(float* logits, const int* recent, int n_recent, int R, int V, float penalty,
                                       cudaStream_t stream) {
     if (R <= 0 || n_recent <= 0 || !(penalty > 1.f)) return 0;
-    repeat_penalty_kernel<<<R, 64, 0, stream>>>(logits, recent, n_recent, V, penalty);
-    return launched("repeat_penalty");
+    return launch_kernel("repeat_penalty", repeat_penalty_kernel, dim3(R), dim3(64), 0, stream, 1, logits, recent, n_recent,
+                         V, penalty);
 }
 
 JANIS_EXPORT int janis_mask_tokens(float* logits, const int* ids, int n_ids, int R, int V, cudaStream_t stream) {
     if (R <= 0 || n_ids <= 0) return 0;
     const int n = R * n_ids;
-    mask_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, ids, n_ids, R, V);
-    return launched("mask_tokens");
+    return launch_kernel("mask_tokens", mask_tokens_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, 1, logits, ids,
+                         n_ids, R, V);
 }

@@ -12,6 +12,7 @@ for its products (`engine/backend.go:265-267`, `mlxc/mlxc.go:655`).
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
@@ -63,6 +64,9 @@ def core():
         lib.janis_sample.argtypes = [P, P, P, I, I, F, F, c_ulonglong, P, P, P]
         lib.janis_repeat_penalty.argtypes = [P, P, I, I, I, F, P]
         lib.janis_mask_tokens.argtypes = [P, P, I, I, I, P]
+        lib.janis_set_overlap.argtypes = [I]
+        lib.janis_set_overlap.restype = None
+        lib.janis_set_overlap(1 if _overlap else 0)
         _core = lib
     return _core
 
@@ -83,10 +87,28 @@ def attention_lib(head_dim: int):
         lib.janis_attn_set_decode_kernel.argtypes = [I]
         lib.janis_attn_set_decode_kernel.restype = None
         lib.janis_attn_wait_timeouts.restype = I
+        lib.janis_attn_set_overlap.argtypes = [I]
+        lib.janis_attn_set_overlap.restype = None
+        lib.janis_attn_set_overlap(1 if _overlap else 0)
         if lib.janis_attn_head_dim() != head_dim:
             raise KernelError(f"attention library for head size {head_dim} reports {lib.janis_attn_head_dim()}")
         _attn[head_dim] = lib
     return lib
+
+
+_overlap = os.environ.get("JANIS_OVERLAP", "1") != "0"
+
+
+def set_overlap(on: bool) -> None:
+    """Whether a kernel's CTAs may arrive while the kernel before it in the stream still runs
+    (programmatic dependent launch; every kernel waits for its predecessor before it touches
+    anything but weights and the step's tables).  Results are the same either way."""
+    global _overlap
+    _overlap = bool(on)
+    if _core is not None:
+        _core.janis_set_overlap(1 if _overlap else 0)
+    for lib in _attn.values():
+        lib.janis_attn_set_overlap(1 if _overlap else 0)
 
 
 def _stream() -> int:

@@ -136,3 +136,28 @@ def test_graphs_and_plain_launches_agree(dtype, model_dirs, plain_models):
         eng.close()
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_overlapped_and_plain_launches_agree(dtype, graphs, model_dirs):
+    """Kernels whose CTAs arrive while their predecessor still runs give the bits of serial launches: a
+    kernel that read its input before the wait, or wrote before its predecessor had read, would differ."""
+    from janis_b200.kernels import ops
+    key = "B_hot"
+    reqs = [random_tokens(vocab_of(key), n, 170 + n) for n in (41, 9, 77, 130)]
+    outs = []
+    try:
+        for overlap in (True, False):
+            ops.set_overlap(overlap)
+            eng = make_engine(model_dirs[key], dtype, "cuda", max_tokens=2048, use_graphs=graphs)
+            for _ in range(3):                      # several rounds: slots, graphs and buffers are used again
+                outs.append(run_requests(eng, reqs, [24, 1, 40, 64]))
+            eng.close()
+    finally:
+        ops.set_overlap(True)
+    half = len(outs) // 2
+    for with_overlap, without in zip(outs[:half], outs[half:]):
+        for a, b in zip(with_overlap, without):
+            assert torch.equal(a, b)
