@@ -87,48 +87,73 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TR* __restrict__
     for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_float<TO>(hr[i] * inv2 * w_next[i]);
 }
 
-// The same with the row held in registers (H <= 256 * EPT): every input is read once.
-template <typename TR, typename TO, int EPT>
-__global__ void __launch_bounds__(256)
-add_rmsnorm_reg_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_part, size_t part_stride,
+// 8 consecutive elements as floats (p aligned to 16 bytes)
+__device__ __forceinline__ void load8(const bf16* p, float* o) { Vec16<bf16>::load(p, o); }
+__device__ __forceinline__ void load8(const float* p, float* o) {
+    Vec16<float>::load(p, o);
+    Vec16<float>::load(p + 4, o + 4);
+}
+__device__ __forceinline__ void store8(bf16* p, const float* v) { Vec16<bf16>::store(p, v); }
+__device__ __forceinline__ void store8(float* p, const float* v) {
+    Vec16<float>::store(p, v);
+    Vec16<float>::store(p + 4, v + 4);
+}
+
+// The same with the row held in registers: 128 threads take the row as vectors of 8 elements
+// (H a multiple of 8, H <= 1024 * VPT), every input is read once with 16-byte loads, and the small
+// CTAs leave room for many rows per SM.
+template <typename TR, typename TO, int VPT>
+__global__ void __launch_bounds__(128)
+add_rmsnorm_vec_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_part, size_t part_stride,
                        const float* __restrict__ w_post, float eps_post, const float* __restrict__ w_next,
                        float eps_next, TO* __restrict__ y, int H) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
+    const int nvec = H >> 3;
     const TR* rr = res + (size_t)r * H;
     float* hr = h + (size_t)r * H;
-    float v[EPT], hv[EPT], wp[EPT], wn[EPT];
+    float v[VPT][8], hv[VPT][8];
     grid_dependents_launch();
-#pragma unroll
-    for (int k = 0; k < EPT; ++k) {         // the norms' weights are constants: read them while the producer still runs
-        const int i = threadIdx.x + k * 256;
-        wp[k] = (w_post && i < H) ? w_post[i] : 0.f;
-        wn[k] = (w_next && i < H) ? w_next[i] : 0.f;
-    }
     grid_dependency_wait();
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < EPT; ++k) {
-        const int i = threadIdx.x + k * 256;
-        v[k] = 0.f;
-        if (i < H) {
-            float a = to_float(rr[i]);
-            for (int p = 1; p < n_part; ++p) a += to_float(rr[p * part_stride + i]);
-            v[k] = a;
-            hv[k] = hr[i];
+    for (int k = 0; k < VPT; ++k) {
+        const int j = threadIdx.x + k * 128;
+        if (j < nvec) {
+            load8(rr + j * 8, v[k]);
+            for (int p = 1; p < n_part; ++p) {
+                float more[8];
+                load8(rr + p * part_stride + j * 8, more);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[k][e] += more[e];
+            }
+            load8(hr + j * 8, hv[k]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[k][e] = 0.f;
         }
-        ss = fmaf(v[k], v[k], ss);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(v[k][e], v[k][e], ss);
     }
     ss = block_sum(ss, scratch);
     const float inv = w_post ? 1.0f / sqrtf(ss / (float)H + eps_post) : 1.0f;
     float ss2 = 0.f;
 #pragma unroll
-    for (int k = 0; k < EPT; ++k) {
-        const int i = threadIdx.x + k * 256;
-        if (i < H) {
-            hv[k] = hv[k] + (w_post ? v[k] * inv * wp[k] : v[k]);
-            hr[i] = hv[k];
-            ss2 = fmaf(hv[k], hv[k], ss2);
+    for (int k = 0; k < VPT; ++k) {
+        const int j = threadIdx.x + k * 128;
+        if (j < nvec) {
+            if (w_post) {
+                float w[8];
+                load8(w_post + j * 8, w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) hv[k][e] += v[k][e] * inv * w[e];
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) hv[k][e] += v[k][e];
+            }
+            store8(hr + j * 8, hv[k]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss2 = fmaf(hv[k][e], hv[k][e], ss2);
         }
     }
     if (w_next == nullptr) return;
@@ -136,9 +161,15 @@ add_rmsnorm_reg_kernel(float* __restrict__ h, const TR* __restrict__ res, int n_
     const float inv2 = 1.0f / sqrtf(ss2 / (float)H + eps_next);
     TO* yr = y + (size_t)r * H;
 #pragma unroll
-    for (int k = 0; k < EPT; ++k) {
-        const int i = threadIdx.x + k * 256;
-        if (i < H) yr[i] = from_float<TO>(hv[k] * inv2 * wn[k]);
+    for (int k = 0; k < VPT; ++k) {
+        const int j = threadIdx.x + k * 128;
+        if (j < nvec) {
+            float w[8], o[8];
+            load8(w_next + j * 8, w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = hv[k][e] * inv2 * w[e];
+            store8(yr + j * 8, o);
+        }
     }
 }
 
@@ -261,6 +292,75 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
     }
 }
 
+// The same for rot == hd with 16-byte accesses: a thread takes 8 neighbouring pairs (i, i + hd/2) of one
+// token and walks over `heads_per_thread` heads with the same 8 angles.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                      const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
+                      const float* __restrict__ inv_freq, int n_tok, int nq, int nkv, int hd, int row_heads,
+                      T* __restrict__ kpool, T* __restrict__ vpool, const int* __restrict__ page_table,
+                      int table_stride, int ring_len, int n_heads, int heads_per_thread) {
+    const int half = hd >> 1, vph = half >> 3;               // vectors of 8 pairs per head
+    const int groups = (n_heads + heads_per_thread - 1) / heads_per_thread;
+    const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = u < (long long)n_tok * groups * vph;
+    grid_dependents_launch();
+    // tables of the step and constants of the model only, before the wait
+    int t = 0, hg = 0, vi = 0, pos = 0;
+    long long place = -1;
+    float sn[8], cs[8];
+    if (live) {
+        vi = (int)(u % vph);
+        hg = (int)((u / vph) % groups);
+        t = (int)(u / ((long long)vph * groups));
+        pos = tok_pos[t];
+        if (kpool != nullptr && n_heads > nq) {
+            const int seq = tok_seq[t];
+            const int slot = seq_slot[seq];
+            int idx = pos;
+            bool keep = slot >= 0;
+            if (keep && ring_len > 0) {
+                keep = pos >= seq_end[seq] - ring_len;
+                idx = pos % ring_len;
+            }
+            if (keep) {
+                const int page = page_table[(size_t)slot * table_stride + idx / JANIS_PAGE];
+                place = ((long long)page * nkv * JANIS_PAGE + idx % JANIS_PAGE) * hd;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sincosf((float)pos * inv_freq[vi * 8 + e], &sn[e], &cs[e]);
+    }
+    grid_dependency_wait();
+    if (!live) return;
+    const int h_end = min(n_heads, (hg + 1) * heads_per_thread);
+    for (int head = hg * heads_per_thread; head < h_end; ++head) {
+        const bool is_k = head >= nq && head < nq + nkv, is_v = head >= nq + nkv;
+        T* p = qkv + ((size_t)t * row_heads + head) * hd + vi * 8;
+        T* dst = nullptr;
+        if (place >= 0 && (is_k || is_v))
+            dst = (is_k ? kpool : vpool) + place + (size_t)(is_k ? head - nq : head - nq - nkv) * JANIS_PAGE * hd + vi * 8;
+        float lo[8], hi[8];
+        load8(p, lo);
+        load8(p + half, hi);
+        if (!is_v) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float a = lo[e], b = hi[e];
+                lo[e] = a * cs[e] - b * sn[e];
+                hi[e] = a * sn[e] + b * cs[e];
+            }
+            store8(p, lo);
+            store8(p + half, hi);
+        }
+        if (dst) {
+            store8(dst, lo);                                  // rounds as the store into the row did
+            store8(dst + half, hi);
+        }
+    }
+}
+
 }  // namespace janis
 
 using namespace janis;
@@ -300,15 +400,23 @@ JANIS_EXPORT int janis_rmsnorm(const void* x, int x_dtype, const float* w, const
 template <typename TR, typename TO>
 static int launch_add_rmsnorm(float* h, const TR* res, int n_part, size_t part_stride, const float* w_post, float eps_post,
                               const float* w_next, float eps_next, TO* y, int R, int H, cudaStream_t stream) {
-    // rows up to 8192 wide stay in registers (each input read once); wider rows take three passes
-#define JANIS_REG(EPT)                                                                                             \
-    return launch_kernel("add_rmsnorm", add_rmsnorm_reg_kernel<TR, TO, EPT>, dim3(R), dim3(256), 0, stream, 1, h, res, \
+    // rows of up to 8192 elements, a multiple of 8, stay in registers (each input read once, 16-byte
+    // accesses); other rows take three passes
+    const uintptr_t all = (uintptr_t)h | (uintptr_t)res | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)y |
+                          (uintptr_t)(part_stride * sizeof(TR));
+    if (H % 8 == 0 && H <= 8192 && (all & 15) == 0) {
+        const int need = (H / 8 + 127) / 128;
+#define JANIS_VEC(VPT)                                                                                             \
+    return launch_kernel("add_rmsnorm", add_rmsnorm_vec_kernel<TR, TO, VPT>, dim3(R), dim3(128), 0, stream, 1, h, res, \
                          n_part, part_stride, w_post, eps_post, w_next, eps_next, y, H)
-    if (H <= 1024) JANIS_REG(4);
-    if (H <= 2048) JANIS_REG(8);
-    if (H <= 4096) JANIS_REG(16);
-    if (H <= 8192) JANIS_REG(32);
-#undef JANIS_REG
+        if (need <= 1) JANIS_VEC(1);
+        if (need <= 2) JANIS_VEC(2);
+        if (need <= 3) JANIS_VEC(3);
+        if (need <= 4) JANIS_VEC(4);
+        if (need <= 6) JANIS_VEC(6);
+        JANIS_VEC(8);
+#undef JANIS_VEC
+    }
     return launch_kernel("add_rmsnorm", add_rmsnorm_kernel<TR, TO>, dim3(R), dim3(row_threads(H)), 0, stream, 1, h, res,
                          n_part, part_stride, w_post, eps_post, w_next, eps_next, y, H);
 }
@@ -370,7 +478,23 @@ JANIS_EXPORT int janis_rope_store(void* qkv, int dtype, const int* tok_pos, cons
     if (row_heads < (store_q_only ? nq : nq + 2 * nkv)) return fail("rope_store: rows of %d heads are too short", row_heads);
     if (ring_len % JANIS_PAGE) return fail("rope_store: ring length %d is not a multiple of the page", ring_len);
     const int heads = store_q_only ? nq : nq + 2 * nkv;
-    // few tokens: a CTA per head; many: up to 4 heads per CTA, which share the angles
+    const uintptr_t all = (uintptr_t)qkv | (uintptr_t)kpool | (uintptr_t)vpool;
+    if (rot == hd && hd % 16 == 0 && (all & 15) == 0) {
+        // 16-byte accesses; few tokens: a thread per head, many: 4 heads per thread, which share the angles
+        const int per = (long long)T * heads >= 4096 ? 4 : 1;
+        const long long units = (long long)T * ((heads + per - 1) / per) * (hd / 16);
+        const dim3 grid((unsigned)((units + 127) / 128)), block(128);
+        if (dtype == JANIS_F32)
+            return launch_kernel("rope_store", rope_store_vec_kernel<float>, grid, block, 0, stream, 1, (float*)qkv, tok_pos,
+                                 tok_seq, seq_slot, seq_end, inv_freq, T, nq, nkv, hd, row_heads, (float*)kpool,
+                                 (float*)vpool, page_table, table_stride, ring_len, heads, per);
+        if (dtype == JANIS_BF16)
+            return launch_kernel("rope_store", rope_store_vec_kernel<bf16>, grid, block, 0, stream, 1, (bf16*)qkv, tok_pos,
+                                 tok_seq, seq_slot, seq_end, inv_freq, T, nq, nkv, hd, row_heads, (bf16*)kpool, (bf16*)vpool,
+                                 page_table, table_stride, ring_len, heads, per);
+        return fail("rope_store: unknown dtype %d", dtype);
+    }
+    // partial rotary widths and odd sizes: element by element; few tokens: a CTA per head, many: up to 4 heads per CTA
     int per = (int)(((long long)T * heads) / 2048);
     per = per < 1 ? 1 : (per > 4 ? 4 : per);
     const int want = rot < hd ? hd : hd / 2;                 // threads that have an element of their own

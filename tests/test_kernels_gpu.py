@@ -153,6 +153,34 @@ def test_rope_store(dtype, nq, nkv, hd, rot, ring):
     close(q, q_ref, tol_of(dtype), "rotated q alone")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,rot,ring", [(8, 4, 256, 256, 0), (5, 1, 32, 32, 128), (3, 2, 48, 24, 0)])
+def test_rope_store_many_tokens(dtype, nq, nkv, hd, rot, ring):
+    """Enough tokens that a thread (or CTA) walks over several heads, with a head count that its groups do not divide."""
+    lens = [300, 3, 450]
+    slots = [1, -1, 0]
+    T = sum(lens)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(3), torch.tensor(lens)).int()
+    seq_slot = torch.tensor(slots).int()
+    seq_end = torch.tensor(lens).int()
+    inv = torch.tensor([10000.0 ** (-2.0 * i / max(rot, 1)) for i in range(rot // 2)], dtype=torch.float32)
+    width = 8
+    n_pages = 2 * width + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(5))[:2 * width].int()
+    table = perm.view(2, width).contiguous()
+    qkv = rnd((T, nq + 2 * nkv, hd), dtype, 20)
+    k, v = _paged(n_pages, nkv, hd, dtype, 21)
+    qkv_ref, k_ref, v_ref = qkv.cpu().clone(), k.cpu().clone(), v.cpu().clone()
+    d = dev()
+    ops().rope_store(qkv, tok_pos.to(d), tok_seq.to(d), seq_slot.to(d), seq_end.to(d), inv.to(d), rot, nq, nkv, hd,
+                     k, v, table.to(d), ring, True)
+    R.rope_store(qkv_ref, tok_pos, tok_seq, seq_slot, seq_end, inv, rot, nq, nkv, hd, k_ref, v_ref, table, ring, True)
+    close(qkv, qkv_ref, tol_of(dtype), "rotated q/k")
+    close(k, k_ref, tol_of(dtype), "cached k")
+    close(v, v_ref, tol_of(dtype), "cached v")
+
+
 def test_rope_angles_at_large_positions():
     """theta = float32(pos) * inv_freq with accurate sin/cos, also thousands of radians out."""
     nq, nkv, hd = 1, 1, 64
