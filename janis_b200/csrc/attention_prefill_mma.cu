@@ -16,6 +16,11 @@
 // expf, which had made the softmax, not the products, the kernel's main cost.  The
 // float32 path of the library does not use this kernel.
 // Shared-memory rows are XOR-swizzled in 16-byte pieces against ldmatrix bank conflicts.
+//
+// A prompt step with few tiles of queries (a short prompt, few heads) leaves SMs idle, and its last tile
+// walks all the keys while the first walks one tile of them.  Such a step runs with `parts` = 2: a tile
+// of queries with at least SPLIT_MIN key tiles is shared by two CTAs, each walks half of the keys and
+// writes its maximum, sum and unnormalised output to scratch, and a second kernel adds the halves.
 #include "common.cuh"
 
 #ifndef JANIS_HEAD_DIM
@@ -36,6 +41,8 @@ constexpr int ROW_BYTES = HD * 2;
 constexpr int Q_BYTES = BM * ROW_BYTES;
 constexpr int KV_BYTES = BN * ROW_BYTES;              // one of K or V, one stage
 constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES;    // Q, then two stages of (K, V)
+constexpr int SPLIT_MIN = 4;                          // key tiles from which a tile of queries is shared
+constexpr int PART_ROW = HD + 2;                      // floats of a partial row: maximum, sum, output
 static_assert(SMEM_BYTES <= 227 * 1024, "tiles do not fit shared memory");
 
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
@@ -95,23 +102,39 @@ __device__ __forceinline__ void load_tile(uint32_t smem, const bf16* src, size_t
     }
 }
 
+// The sequence and the tile of BM queries that item `tile` of the step stands for (false: none).
+__device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ seq_len, int n_seq, int& seq, int& q0, int& len) {
+    for (int s = 0; s < n_seq; ++s) {
+        const int n = seq_len[s];
+        const int nt = (n + BM - 1) / BM;
+        if (tile < nt) { seq = s; q0 = tile * BM; len = n; return true; }
+        tile -= nt;
+    }
+    return false;
+}
+
+// Key tiles [k_first / BN, ...) that a tile of queries walks: n_tiles of them from key k_first.
+__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_first, int& n_tiles) {
+    const int q_last = min(q0 + BM, len) - 1;
+    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
+    k_first = (j_first / BN) * BN;
+    n_tiles = (q_last - k_first) / BN + 1;
+}
+
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__ kv_src,
                         const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
                         bf16* __restrict__ out, int nq, int nkv, int q_row_heads, int kv_row_heads,
-                        int kv_k_head0, float scale, float cap, int window) {
+                        int kv_k_head0, float scale, float cap, int window, int parts, float* __restrict__ partial) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    // Which sequence and which tile of BM queries is this CTA's.  Tiles are handed out from the end of
-    // the list: the last tiles of a sequence see the most keys and should start first.
-    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, seq = -1, q0 = 0, len = 0;
-    for (int s = 0; s < n_seq; ++s) {
-        const int n = seq_len[s];
-        const int nt = (n + BM - 1) / BM;
-        if (tile < nt) { seq = s; q0 = tile * BM; len = n; break; }
-        tile -= nt;
-    }
-    if (seq < 0) return;
-    const int head = blockIdx.y;
+    // Which sequence, which tile of BM queries and which part of its keys is this CTA's.  Items are handed
+    // out from the end of the list: the last tiles of a sequence see the most keys and should start first.
+    // (heads vary fastest in the grid, so the long items of all heads come before anyone's short ones).
+    const int item = (int)gridDim.y - 1 - (int)blockIdx.y;
+    const int gtile = item / parts, part = item % parts;
+    int seq = -1, q0 = 0, len = 0;
+    if (!find_tile(gtile, seq_len, n_seq, seq, q0, len)) return;
+    const int head = blockIdx.x;
     const int kvh = head / (nq / nkv);
     const int first = seq_first_row[seq];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -121,10 +144,15 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     const uint32_t sKV = sQ + Q_BYTES;                // stage s: K at sKV + s * 2 KV_BYTES, V right after
 
     const size_t q_stride = (size_t)q_row_heads * HD, kv_stride = (size_t)kv_row_heads * HD;
-    const int q_last = min(q0 + BM, len) - 1;
-    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
-    const int k_first = (j_first / BN) * BN;
-    const int n_tiles = (q_last - k_first) / BN + 1;
+    int k_first, n_tiles;
+    key_tiles(q0, len, window, k_first, n_tiles);
+    const bool shared_tile = parts > 1 && n_tiles >= SPLIT_MIN;     // the merge kernel decides the same way
+    if (!shared_tile && part > 0) return;
+    if (shared_tile) {                                               // this part's share of the key tiles
+        const int t0 = (int)((long long)n_tiles * part / parts), t1 = (int)((long long)n_tiles * (part + 1) / parts);
+        k_first += t0 * BN;
+        n_tiles = t1 - t0;
+    }
     const bf16* kbase = kv_src + (size_t)first * kv_stride + (size_t)(kv_k_head0 + kvh) * HD;
     const bf16* vbase = kbase + (size_t)nkv * HD;
     auto load_kv = [&](int it) {
@@ -249,6 +277,22 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
+    if (shared_tile) {
+        // maximum (in units of log2 e), sum and unnormalised output of this part; a row that saw no key: -inf, 0, 0
+        float* base = partial + ((((size_t)gtile * nq + head) * parts + part) * BM) * PART_ROW;
+        float* p_lo = base + (size_t)(warp * 16 + g) * PART_ROW;
+        float* p_hi = p_lo + 8 * PART_ROW;
+        if (t == 0) {
+            p_lo[0] = m_run[0]; p_lo[1] = l_run[0];
+            p_hi[0] = m_run[1]; p_hi[1] = l_run[1];
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            *reinterpret_cast<float2*>(p_lo + 2 + i * 8 + t * 2) = make_float2(o[i][0], o[i][1]);
+            *reinterpret_cast<float2*>(p_hi + 2 + i * 8 + t * 2) = make_float2(o[i][2], o[i][3]);
+        }
+        return;
+    }
     const float inv_lo = 1.0f / l_run[0], inv_hi = 1.0f / l_run[1];
     bf16* out_lo = out + (size_t)(first + row_lo) * nq * HD + (size_t)head * HD + t * 2;
     bf16* out_hi = out + (size_t)(first + row_hi) * nq * HD + (size_t)head * HD + t * 2;
@@ -259,6 +303,45 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     }
 }
 
+// Adds the parts of the shared tiles: out = sum_p o_p 2^(m_p - m) / sum_p l_p 2^(m_p - m), parts in index order.
+__global__ void __launch_bounds__(256)
+attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restrict__ seq_first_row,
+                          const int* __restrict__ seq_len, int n_seq, bf16* __restrict__ out, int nq, int window,
+                          int parts) {
+    const int gtile = blockIdx.x, head = blockIdx.y;
+    constexpr int ROWS = 16;                          // rows of the tile per CTA
+    const int r_begin = blockIdx.z * ROWS;
+    grid_dependents_launch();
+    grid_dependency_wait();
+    int seq = -1, q0 = 0, len = 0;
+    if (!find_tile(gtile, seq_len, n_seq, seq, q0, len)) return;
+    int k_first, n_tiles;
+    key_tiles(q0, len, window, k_first, n_tiles);
+    if (n_tiles < SPLIT_MIN) return;
+    const int rows = min(ROWS, len - q0 - r_begin);
+    const int first = seq_first_row[seq];
+    const float* base = partial + (((size_t)gtile * nq + head) * parts * BM) * PART_ROW;
+    constexpr int VEC = HD / 4;                       // float4 pieces of an output row
+    for (int idx = threadIdx.x; idx < rows * VEC; idx += blockDim.x) {
+        const int r = r_begin + idx / VEC, c = (idx % VEC) * 4;
+        float m = -INFINITY;
+        for (int p = 0; p < parts; ++p) m = fmaxf(m, base[((size_t)p * BM + r) * PART_ROW]);
+        float l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < parts; ++p) {
+            const float* row = base + ((size_t)p * BM + r) * PART_ROW;
+            const float mp = row[0];
+            if (mp == -INFINITY) continue;            // this part saw no key of the row
+            const float w = ex2(mp - m);
+            l += row[1] * w;
+            const float2 a = *reinterpret_cast<const float2*>(row + 2 + c), b = *reinterpret_cast<const float2*>(row + 4 + c);
+            acc[0] += a.x * w; acc[1] += a.y * w; acc[2] += b.x * w; acc[3] += b.y * w;
+        }
+        const float inv = 1.0f / l;
+        bf16* o = out + (size_t)(first + q0 + r) * nq * HD + (size_t)head * HD + c;
+        *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
+    }
+}
+
 }  // namespace pf
 }  // namespace janis
 
@@ -266,17 +349,39 @@ using namespace janis;
 
 JANIS_EXPORT int janis_attn_prefill_tile() { return pf::BM; }
 
+static int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+// CTAs that share a tile of queries in a step of n_tiles_bound tiles and nq heads (1 or 2), and the
+// floats of scratch such a step needs (0 when nothing is shared).
+JANIS_EXPORT int janis_attn_prefill_parts(int n_tiles_bound, int nq) {
+    return (long long)n_tiles_bound * nq < 2LL * sm_count() ? 2 : 1;
+}
+JANIS_EXPORT long long janis_attn_prefill_scratch(int n_tiles_bound, int nq) {
+    const int parts = janis_attn_prefill_parts(n_tiles_bound, nq);
+    return parts > 1 ? (long long)n_tiles_bound * nq * parts * pf::BM * pf::PART_ROW : 0;
+}
+
 // q_src: [T, q_row_heads, hd] with the queries in its first nq heads; keys and values of position j of
 // sequence s are read from row seq_first_row[s] + j of kv_src [T, kv_row_heads, hd], key heads starting at
 // head kv_k_head0, value heads nkv later.  n_tiles_bound >= sum over sequences of ceil(len / tile), tile =
-// janis_attn_prefill_tile().
+// janis_attn_prefill_tile().  partial: janis_attn_prefill_scratch(n_tiles_bound, nq) floats, or null (or
+// fewer floats), in which case no tile is shared.
 JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, const int* seq_first_row,
                                         const int* seq_len, int n_seq, int n_tiles_bound, void* out, int nq,
                                         int nkv, int q_row_heads, int kv_row_heads, int kv_k_head0, float scale,
-                                        float cap, int window, cudaStream_t stream) {
+                                        float cap, int window, float* partial, long long partial_floats,
+                                        cudaStream_t stream) {
     if (n_seq <= 0 || n_tiles_bound <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attn_prefill_mma: %d query heads do not divide over %d key heads", nq, nkv);
-    if (((uintptr_t)q_src | (uintptr_t)kv_src | (uintptr_t)out) & 15)
+    if (((uintptr_t)q_src | (uintptr_t)kv_src | (uintptr_t)out | (uintptr_t)partial) & 15)
         return fail("attn_prefill_mma: operands must be 16-byte aligned");
     static bool configured = false;
     if (!configured) {
@@ -286,9 +391,15 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, c
                                           cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(n_tiles_bound, nq);
+    int parts = janis_attn_prefill_parts(n_tiles_bound, nq);
+    if (partial == nullptr || partial_floats < janis_attn_prefill_scratch(n_tiles_bound, nq)) parts = 1;
+    if ((long long)n_tiles_bound * parts > 65535) return fail("attn_prefill_mma: %d tiles of queries exceed the grid", n_tiles_bound);
+    dim3 grid(nq, n_tiles_bound * parts);
     pf::attn_prefill_mma_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
         (const bf16*)q_src, (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
-        kv_row_heads, kv_k_head0, scale, cap, window);
-    return launched("attn_prefill_mma");
+        kv_row_heads, kv_k_head0, scale, cap, window, parts, partial);
+    if (launched("attn_prefill_mma")) return 1;
+    if (parts == 1) return 0;
+    return launch_kernel("attn_prefill_merge", pf::attn_prefill_merge_kernel, dim3(n_tiles_bound, nq, pf::BM / 16), dim3(256), 0, stream, 1,
+                         (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts);
 }

@@ -82,7 +82,9 @@ def attention_lib(head_dim: int):
         lib.janis_attn_decode_scratch.restype = c_longlong
         lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P]
         lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
-        lib.janis_attn_prefill_mma.argtypes = [P, P, P, P, I, I, P, I, I, I, I, I, F, F, I, P]
+        lib.janis_attn_prefill_mma.argtypes = [P, P, P, P, I, I, P, I, I, I, I, I, F, F, I, P, c_longlong, P]
+        lib.janis_attn_prefill_scratch.argtypes = [I, I]
+        lib.janis_attn_prefill_scratch.restype = c_longlong
         lib.janis_attn_prefill_tile.restype = I
         lib.janis_attn_set_decode_kernel.argtypes = [I]
         lib.janis_attn_set_decode_kernel.restype = None
@@ -321,8 +323,20 @@ def matmul_bf16_to_f32(x, w, out):
 # attention
 # ---------------------------------------------------------------------------
 
+def attn_prefill_scratch_floats(n_tok: int, n_seq: int, nq: int, hd: int, dtype=torch.bfloat16) -> int:
+    """Floats of scratch that attn_prefill wants for a step of n_tok tokens in n_seq sequences: a bfloat16
+    step with few tiles of queries shares each long tile between two CTAs, which meet through the scratch
+    (0: nothing is shared).  Without the scratch the step runs unshared."""
+    if dtype != torch.bfloat16:
+        return 0
+    lib = attention_lib(hd)
+    bm = lib.janis_attn_prefill_tile()
+    return int(lib.janis_attn_prefill_scratch((n_tok + bm - 1) // bm + n_seq, nq))
+
+
 def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, hd: int, scale: float, cap: float,
-                 window: int, kv_src=None, kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True):
+                 window: int, kv_src=None, kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True,
+                 scratch=None):
     """Causal (and windowed when window > 0) attention over packed sequences that start at position 0.
     qkv: [T, nq + 2 nkv, hd], or [T, nq, hd] when keys and values come from `kv_src`, another layer's
     [T, kv_row_heads, hd] rows whose key heads start at head kv_k_head0 (values nkv heads later).
@@ -331,7 +345,7 @@ def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, h
     T = qkv.shape[0]
     if qkv.dtype == torch.bfloat16 and seq_len is not None and tensor_cores:
         return _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src,
-                                 kv_row_heads, kv_k_head0)
+                                 kv_row_heads, kv_k_head0, scratch)
     if kv_src is None:
         _t(qkv, "qkv", _FLOATS, (T, nq + 2 * nkv, hd))
         kv_src, kv_row_heads, kv_k_head0 = qkv, nq + 2 * nkv, nq
@@ -354,7 +368,7 @@ def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, h
 
 
 def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src, kv_row_heads,
-                      kv_k_head0):
+                      kv_k_head0, scratch=None):
     T = qkv.shape[0]
     if kv_src is None:
         _t(qkv, "qkv", torch.bfloat16, (T, nq + 2 * nkv, hd))
@@ -373,10 +387,15 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
     lib = attention_lib(hd)
     bm = lib.janis_attn_prefill_tile()      # queries per CTA
     tiles = (T + bm - 1) // bm + n_seq      # >= sum of ceil(len / bm)
+    need = int(lib.janis_attn_prefill_scratch(tiles, nq))
+    if scratch is not None and (need == 0 or scratch.numel() < need):
+        scratch = None
     _check(lib, lib.janis_attn_prefill_mma(qkv.data_ptr(), kv_src.data_ptr(), seq_first_row.data_ptr(),
                                            seq_len.data_ptr(), n_seq, tiles, out.data_ptr(), nq, nkv,
                                            qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),
-                                           int(window), _stream()))
+                                           int(window), _t(scratch, "scratch", torch.float32) if scratch is not None else None,
+                                           scratch.numel() if scratch is not None else 0, _stream()),
+           2 if scratch is not None else 1)
     return out
 
 

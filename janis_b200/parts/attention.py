@@ -104,16 +104,18 @@ class SoftmaxAttention(Mixer):
         self.position.encode_and_store(qkv, ctx, nq, nkv, hd, kv)
         att = ws.buf("attn.ctx", (T, nq * hd), rt.dtype)
         if ctx.mode == "prefill":
+            n_scratch = ops.attn_prefill_scratch_floats(T, ctx.n_seq, nq, hd, rt.dtype)
+            scratch = ws.buf("attn.prefill_partial", (n_scratch,), torch.float32) if n_scratch else None
             if own:
                 if line.has_readers:
                     ctx.shared[("kv", line.index)] = (qkv, heads, nq)
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
-                                 self.softcap, self.window, seq_len=ctx.seq_end)
+                                 self.softcap, self.window, seq_len=ctx.seq_end, scratch=scratch)
             else:
                 src, src_heads, k0 = ctx.shared[("kv", line.index)]
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
                                  self.softcap, self.window, kv_src=src, kv_row_heads=src_heads, kv_k_head0=k0,
-                                 seq_len=ctx.seq_end)
+                                 seq_len=ctx.seq_end, scratch=scratch)
         else:
             chunk, max_chunks = self._decode_geometry(ctx, rt.sm_count)
             scratch = ws.buf("attn.partial", (ops.attn_decode_scratch_floats(ctx.n_seq, nq, hd, max_chunks),),

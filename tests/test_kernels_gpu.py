@@ -355,6 +355,36 @@ def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap):
     close(out, want, 2 * BF16_TOL, "attn_prefill on tensor cores")
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 2, 64), (3, 1, 80), (2, 2, 128)])
+@pytest.mark.parametrize("window,cap", [(0, 0.0), (100, 30.0), (300, 50.0)])
+def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap):
+    """Few tiles of queries: the long ones are shared by two CTAs that meet through scratch.  Sequences long
+    enough for tiles with many key tiles, a window that leaves some tiles unshared, a far key that must win,
+    and the same call without scratch."""
+    lens = [700, 129, 300, 1]
+    T = sum(lens)
+    first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).int()
+    seq_len = torch.tensor(lens, dtype=torch.int32)
+    qkv = rnd((T, nq + 2 * nkv, hd), torch.bfloat16, 41)
+    qkv[0, nq] = qkv[699, 0] * 3.0                # position 0 of the long sequence answers its last query
+    d = dev()
+    n = ops().attn_prefill_scratch_floats(T, len(lens), nq, hd)
+    assert n > 0
+    scratch = torch.full((n,), float("nan"), dtype=torch.float32, device=d)
+    outs = []
+    for sc in (scratch, None):
+        out = torch.full((T, nq * hd), 9.0, dtype=torch.bfloat16, device=d)
+        ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, 1.0 / math.sqrt(hd), cap,
+                           window, seq_len=seq_len.to(d), scratch=sc)
+        outs.append(out)
+    want = torch.empty((T, nq * hd), dtype=torch.float64)
+    R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 1.0 / math.sqrt(hd), cap, window)
+    close(outs[0], want, 2 * BF16_TOL, "attn_prefill with shared tiles")
+    close(outs[1], want, 2 * BF16_TOL, "attn_prefill without scratch")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attn_prefill_reads_another_layers_keys(dtype):
     nq, nkv, hd = 4, 2, 32
