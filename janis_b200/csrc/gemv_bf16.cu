@@ -24,6 +24,9 @@ namespace cg = cooperative_groups;
 
 namespace janis {
 
+#ifndef JANIS_GEMV_BULK_AHEAD
+#define JANIS_GEMV_BULK_AHEAD 0       // 1: one bulk prefetch of the CTA's whole share of the tile instead (a tuning switch)
+#endif
 #ifndef JANIS_GEMV_AHEAD
 #define JANIS_GEMV_AHEAD 1            // rounds of weights asked for before the wait (0: none; a tuning switch)
 #endif
@@ -94,7 +97,22 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
     };
     int kb = rank * NW + warp;
     grid_dependents_launch();
-#if JANIS_GEMV_AHEAD
+#if JANIS_GEMV_BULK_AHEAD
+    // The 16 rows of a tile lie one after another in memory: one bulk prefetch per CTA asks for this CTA's
+    // share of them (into L2) while the kernel before this one still runs.
+    if (threadIdx.x == 0) {
+        const int rows_here = min(16, N - r0);
+        const size_t bytes = (size_t)rows_here * K * sizeof(bf16);
+        size_t piece = ((bytes / CL) + 15) & ~(size_t)15;
+        const size_t off = piece * rank;
+        if (off < bytes) {
+            if (off + piece > bytes) piece = (bytes - off) & ~(size_t)15;
+            if (piece > 0)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(reinterpret_cast<const char*>(W + (size_t)r0 * K) + off),
+                             "r"((uint32_t)piece) : "memory");
+        }
+    }
+#elif JANIS_GEMV_AHEAD
     // hints only: a load into registers would have to land before the wait below lets the thread go on
     for (int pk = kb, n = 0; pk < nblk && n < JANIS_GEMV_AHEAD * U; pk += SPLIT, ++n) {
         const int k0 = pk * 32;
