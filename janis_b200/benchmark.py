@@ -166,8 +166,11 @@ def fill(engine, batch: int, length: int, seed: int = 0) -> list[int]:
     return slots
 
 
-def measure_decode(engine, batch: int, context: int, steps: int, warmup: int, sample_clocks: bool = False) -> dict:
-    """Decode tokens a second at `batch` sequences whose cache grows to `context` tokens by the last step."""
+def measure_decode(engine, batch: int, context: int, steps: int, warmup: int, sample_clocks: bool = False,
+                   profile: bool = False) -> dict:
+    """Decode tokens a second at `batch` sequences whose cache grows to `context` tokens by the last step.
+    `profile` opens the CUDA profiler range around the first two timed steps (for a profiler that was
+    started with its capture off); the timing of such a run means nothing."""
     from .engine.step import StepEntry
     ops = engine.rt.ops
     start_len = context - steps - warmup
@@ -195,7 +198,12 @@ def measure_decode(engine, batch: int, context: int, steps: int, warmup: int, sa
         clocks.__enter__()
     e0.record()
     for i in range(steps):
+        if profile and i == 0:
+            torch.cuda.profiler.start()
         one(warmup + i)
+        if profile and i == 1:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
     e1.record()
     torch.cuda.synchronize()
     if clocks:
@@ -235,18 +243,23 @@ def measure_e2e(engine, batch: int, context: int, steps: int) -> dict:
             "d2h_bytes_per_step": 4 * batch}
 
 
-def measure_prefill(engine, n_tokens: int, repeats: int = 5, warmup: int = 3) -> dict:
+def measure_prefill(engine, n_tokens: int, repeats: int = 5, warmup: int = 3, profile: bool = False) -> dict:
     from .engine.step import StepEntry
     times = []
     for r in range(warmup + repeats):
         slot = engine.alloc_slot()
         toks = _tokens(engine.model.vocab, n_tokens, 500 + r)
         torch.cuda.synchronize()
+        last = profile and r == warmup + repeats - 1
+        if last:
+            torch.cuda.profiler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         engine.stepper.step([StepEntry(slot, toks, (n_tokens - 1,))])
         e1.record()
         torch.cuda.synchronize()
+        if last:
+            torch.cuda.profiler.stop()
         if r >= warmup:
             times.append(e0.elapsed_time(e1))
         engine.free_slot(slot)
@@ -255,7 +268,8 @@ def measure_prefill(engine, n_tokens: int, repeats: int = 5, warmup: int = 3) ->
 
 
 def run(steps: int = 64, warmup: int = 8, batch: int = 8, context: int = 8192, config: str = "gemma2-2b",
-        layers: int | None = None, points=(1, 64), prefill_tokens: int = 2048, e2e: bool = True) -> dict:
+        layers: int | None = None, points=(1, 64), prefill_tokens: int = 2048, e2e: bool = True,
+        profile: str = "") -> dict:
     """The whole benchmark; returns the record that bench.py prints as one JSON line."""
     import janis_b200
     raw = load_config(config)
@@ -267,12 +281,12 @@ def run(steps: int = 64, warmup: int = 8, batch: int = 8, context: int = 8192, c
     room = max(context, prefill_tokens)                 # the prefill measurement needs its own length to fit
     eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=max_batch * room, max_batch=max_batch,
                                  max_context=room)
-    main = measure_decode(eng, batch, context, steps, warmup, sample_clocks=True)
+    main = measure_decode(eng, batch, context, steps, warmup, sample_clocks=True, profile=profile == "decode")
     pts = {}
     for b in points:
         pts[f"decode_b{b}"] = round(measure_decode(eng, b, context, max(16, steps // 2), warmup)["tok_s"], 1)
-    pre = measure_prefill(eng, prefill_tokens)
-    end = measure_e2e(eng, batch, context, steps) if e2e else None
+    pre = measure_prefill(eng, prefill_tokens, profile=profile == "prefill")
+    end = measure_e2e(eng, batch, context, steps) if e2e and not profile else None
     cfg = eng.config
     rec = {
         "metric": "decode tok/s at batch %d (Gemma2-2B sizes, context %d)" % (batch, context),
@@ -310,6 +324,8 @@ def main(argv=None) -> int:
     ap.add_argument("--config", default="gemma2-2b")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--profile", choices=["decode", "prefill"], default="",
+                    help="open the CUDA profiler range around two timed decode steps, or the last prompt step")
     a = ap.parse_args(argv)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go module (no Go toolchain here, "
@@ -319,6 +335,6 @@ def main(argv=None) -> int:
         print(f"janis_b200 is a one-GPU library: --gpus {a.gpus} is not supported")
         return 2
     rec = run(a.steps, max(3, a.warmup), a.batch, a.context, a.config, a.layers or None,
-              points=() if a.no_points else (1, 64))
+              points=() if (a.no_points or a.profile) else (1, 64), profile=a.profile)
     print(json.dumps(rec))
     return 0
