@@ -466,6 +466,16 @@ attn_decode_staged_kernel(const T* __restrict__ qkv, const T* __restrict__ kpool
 // Staging (bulk copies, mbarriers, bounded waits), chunking and the merge are those of the
 // staged kernel.  Needs a tile of 32 or 64 keys: head sizes up to 256.
 // ---------------------------------------------------------------------------
+// out[s, heads of head group `y`, :] = v   (a padding row: 0; a sequence the launch was not sized for: NaN)
+__device__ __forceinline__ void fill_heads(bf16* out, int s, int nq, int nkv, int y, int rb, float v) {
+    const int rep = nq / nkv;
+    const int groups = (rep + rb - 1) / rb;
+    const int kvh = y / groups, hg = y % groups;
+    const int h0 = kvh * rep + hg * rb, nh = min(rb, rep - hg * rb);
+    for (int idx = threadIdx.x; idx < nh * HD; idx += blockDim.x)
+        out[((size_t)s * nq + h0 + idx / HD) * HD + idx % HD] = __float2bfloat16_rn(v);
+}
+
 struct MmaDecode {
     static constexpr int WARPS = 4;
     static constexpr int STAGES = JANIS_STAGES;
@@ -482,12 +492,14 @@ struct MmaDecode {
     static constexpr bool OK = HD <= 256;
 };
 
-template <int RB>
+// DIRECT: the launch has one chunk per sequence and the kernel writes the result itself (`out`); otherwise it
+// leaves a partial per chunk for the merge kernel.
+template <int RB, bool DIRECT>
 __global__ void __launch_bounds__(MmaDecode::WARPS * 32)
 attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
                        const int* __restrict__ page_table, int table_stride, const int* __restrict__ seq_slot,
                        const int* __restrict__ seq_len, float* __restrict__ partial, int nq, int nkv, int q_row_heads,
-                       float scale, float cap, int window, int ring_len, int chunk) {
+                       float scale, float cap, int window, int ring_len, int chunk, bf16* __restrict__ out) {
     typedef MmaDecode S;
     extern __shared__ __align__(128) unsigned char stage_mem[];
     __shared__ __align__(8) unsigned long long full[S::STAGES];
@@ -497,10 +509,20 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
     // key but the newest was stored by an earlier step: the first tiles are asked for before this
     // kernel waits for the one that stores the newest key and rotates the queries.
     const int slot = seq_slot[s];
-    if (slot < 0) { grid_dependency_wait(); return; }
+    if (slot < 0) {
+        grid_dependency_wait();
+        if (DIRECT) fill_heads(out, s, nq, nkv, blockIdx.y, RB, 0.f);   // a padding row
+        return;
+    }
     const int len = seq_len[s];
     int lo, first_chunk, n_chunks;
     chunk_range(len, window, chunk, lo, first_chunk, n_chunks);
+    if (DIRECT && n_chunks > 1) {
+        // the launch was sized for shorter sequences: make it visible, as the merge kernel does
+        grid_dependency_wait();
+        fill_heads(out, s, nq, nkv, blockIdx.y, RB, __int_as_float(0x7fc00000));
+        return;
+    }
     if ((int)blockIdx.x >= n_chunks) { grid_dependency_wait(); return; }
     const int c = first_chunk + blockIdx.x;
     const int k_begin = max(lo, c * chunk), k_end = min(len, (c + 1) * chunk);
@@ -694,6 +716,28 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
     }
     __syncthreads();
     const int max_chunks = gridDim.x;
+    // the warps' states in warp order
+    if (DIRECT) {
+        // one chunk per sequence: the result itself
+        for (int idx = threadIdx.x; idx < nh_here * HD; idx += blockDim.x) {
+            const int r = idx / HD, d = idx % HD;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < S::WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
+            float v = 0.f, l = 0.f;
+#pragma unroll
+            for (int w = 0; w < S::WARPS; ++w) {
+                const float mw = sm[w][r][0];
+                if (mw != -INFINITY) {
+                    const float e = expf(mw - mx);
+                    v += sm[w][r][2 + d] * e;
+                    l += sm[w][r][1] * e;
+                }
+            }
+            out[((size_t)s * nq + h0 + r) * HD + d] = __float2bfloat16_rn(v / l);
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < nh_here * (HD + 2); idx += blockDim.x) {
         const int r = idx / (HD + 2), d = idx % (HD + 2);
         float mx = -INFINITY;
@@ -825,30 +869,37 @@ template <int RB>
 static int launch_decode_mma_rb(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table,
                                 int table_stride, const int* seq_slot, const int* seq_len, float* partial, int n_seq, int nq,
                                 int nkv, int q_row_heads, float scale, float cap, int window, int ring_len, int chunk,
-                                int max_chunks, cudaStream_t stream) {
+                                int max_chunks, bf16* out, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              MmaDecode::SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     MmaDecode::SMEM_BYTES);
         if (e != cudaSuccess) return fail("attn_decode: shared memory of %d bytes refused: %s", MmaDecode::SMEM_BYTES,
                                           cudaGetErrorString(e));
         configured = true;
     }
     const int rep = nq / nkv;
     dim3 grid(max_chunks, nkv * ((rep + RB - 1) / RB), n_seq);
-    return launch_kernel("attn_decode", attn_decode_mma_kernel<RB>, grid, dim3(MmaDecode::WARPS * 32), MmaDecode::SMEM_BYTES,
-                         stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, nq, nkv,
-                         q_row_heads, scale, cap, window, ring_len, chunk);
+    if (out != nullptr)
+        return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, true>, grid, dim3(MmaDecode::WARPS * 32),
+                             MmaDecode::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
+                             partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, out);
+    return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, false>, grid, dim3(MmaDecode::WARPS * 32),
+                         MmaDecode::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
+                         partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, out);
 }
 
 static int launch_decode_mma(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table, int table_stride,
                              const int* seq_slot, const int* seq_len, float* partial, int n_seq, int nq, int nkv,
                              int q_row_heads, float scale, float cap, int window, int ring_len, int chunk, int max_chunks,
-                             cudaStream_t stream) {
+                             bf16* out, cudaStream_t stream) {
     const int rep = nq / nkv;
 #define JANIS_RB(RB)                                                                                                   \
     return launch_decode_mma_rb<RB>(qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, n_seq, nq, nkv, \
-                                    q_row_heads, scale, cap, window, ring_len, chunk, max_chunks, stream)
+                                    q_row_heads, scale, cap, window, ring_len, chunk, max_chunks, out, stream)
     if (rep == 1) JANIS_RB(1);
     if (rep == 2) JANIS_RB(2);
     if (rep <= 4) JANIS_RB(4);
@@ -863,10 +914,13 @@ static int launch_decode(const T* qkv, const T* kpool, const T* vpool, const int
                          cudaStream_t stream) {
     const int rep = nq / nkv;
     if (g_decode_kernel == 2 && sizeof(T) == 2 && MmaDecode::OK) {
+        // a launch of one chunk per sequence writes the result itself: no partials, no merge
+        bf16* direct = max_chunks == 1 ? (bf16*)out : nullptr;
         if (launch_decode_mma((const bf16*)qkv, (const bf16*)kpool, (const bf16*)vpool, page_table, table_stride, seq_slot,
                               seq_len, partial, n_seq, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, max_chunks,
-                              stream))
+                              direct, stream))
             return 1;
+        if (direct != nullptr) return 0;
     } else if (g_decode_kernel >= 1) {
         typedef Geo<T, Staged<T>::LMAX, Staged<T>::BUDGET> GS;
         dim3 grid(max_chunks, nkv * ((rep + GS::RG - 1) / GS::RG), n_seq);

@@ -404,6 +404,7 @@ def attn_set_decode_kernel(hd: int, which: int = 2) -> None:
     tensor cores (bfloat16 and head sizes <= 256; the default), 1 = staged, CUDA cores (also what float32
     runs), 0 = straight from global memory into registers."""
     attention_lib(hd).janis_attn_set_decode_kernel(int(which))
+    _decode_kernel[hd] = int(which)
 
 
 def attn_wait_timeouts(hd: int) -> int:
@@ -415,10 +416,15 @@ def attn_decode_scratch_floats(n_seq: int, nq: int, hd: int, max_chunks: int) ->
     return n_seq * nq * max_chunks * (hd + 2)
 
 
+_decode_kernel: dict[int, int] = {}      # head size -> kernel chosen for tests (default 2)
+
+
 def attn_decode(qkv, kpool, vpool, page_table, seq_slot, seq_len, scratch, out, nq: int, nkv: int, hd: int,
                 scale: float, cap: float, window: int, ring_len: int, chunk: int, max_chunks: int):
     """One query per sequence over the paged cache.  qkv: [n_seq, heads >= nq, hd] with q first;
-    seq_len counts the new token; scratch is float32."""
+    seq_len counts the new token; scratch is float32.  The chunks of a sequence are merged by a second
+    kernel; a launch of one chunk per sequence (max_chunks == 1) on the bfloat16 tensor-core kernel
+    writes the result itself."""
     n_seq = qkv.shape[0]
     _t(qkv, "qkv", _FLOATS, (n_seq, None, hd))
     if qkv.shape[1] < nq:
@@ -432,12 +438,13 @@ def attn_decode(qkv, kpool, vpool, page_table, seq_slot, seq_len, scratch, out, 
     if seq_slot.numel() < n_seq or seq_len.numel() < n_seq:
         raise KernelError("attn_decode: sequence tables shorter than the batch")
     lib = attention_lib(hd)
+    direct = max_chunks == 1 and qkv.dtype == torch.bfloat16 and hd <= 256 and _decode_kernel.get(hd, 2) == 2
     _check(lib, lib.janis_attn_decode(qkv.data_ptr(), kpool.data_ptr(), vpool.data_ptr(), _DT[qkv.dtype],
                                       page_table.data_ptr(), page_table.shape[1],
                                       _t(seq_slot, "seq_slot", torch.int32), _t(seq_len, "seq_len", torch.int32),
                                       scratch.data_ptr(), scratch.numel(), out.data_ptr(), n_seq, nq, nkv,
                                       qkv.shape[1], float(scale), float(cap), int(window), int(ring_len),
-                                      int(chunk), int(max_chunks), _stream()), kernels=2)
+                                      int(chunk), int(max_chunks), _stream()), kernels=1 if direct else 2)
     return out
 
 

@@ -408,7 +408,8 @@ def test_attn_prefill_reads_another_layers_keys(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES)
-@pytest.mark.parametrize("window,ring,chunk", [(0, 0, 64), (0, 0, 256), (16, 64, 64), (100, 128, 64), (128, 128, 128)])
+@pytest.mark.parametrize("window,ring,chunk", [(0, 0, 64), (0, 0, 256), (0, 0, 320), (16, 64, 64), (100, 128, 64), (128, 128, 128),
+                                               (128, 128, 384)])
 @pytest.mark.parametrize("kernel", [2, 1, 0])
 def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, kernel):
     # sequences of unequal lengths in scattered pages; one padding row; lengths at page and chunk edges
@@ -456,6 +457,11 @@ def test_attn_decode_marks_an_undersized_launch():
     ops().attn_decode(qkv, k, v, table, torch.tensor([0], dtype=torch.int32, device=d),
                       torch.tensor([200], dtype=torch.int32, device=d), scratch, out, nq, nkv, hd, 1.0, 0.0, 0, 0, 64, 1)
     assert torch.isnan(out).all()
+    # the same through the kernel that writes its result itself when a launch has one chunk per sequence
+    outb = torch.zeros((1, nq * hd), dtype=torch.bfloat16, device=d)
+    ops().attn_decode(qkv.bfloat16(), k.bfloat16(), v.bfloat16(), table, torch.tensor([0], dtype=torch.int32, device=d),
+                      torch.tensor([200], dtype=torch.int32, device=d), scratch, outb, nq, nkv, hd, 1.0, 0.0, 0, 0, 64, 1)
+    assert torch.isnan(outb.float()).all()
 
 
 @pytest.mark.parametrize("Rn,V", [(1, 7), (5, 384), (3, 256000), (64, 1000)])
