@@ -319,9 +319,11 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="janis_b200")
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--config", default="gemma2-2b")
+    ap.add_argument("--batch", default="8", help="sequences decoded together; a list (8,1,64) also times the others")
+    ap.add_argument("--context", "--ctx", dest="context", type=int, default=8192)
+    ap.add_argument("--prefill", type=int, default=2048, help="tokens of the timed prompt step")
+    ap.add_argument("--json", action="store_true", help="accepted for familiarity: the record is always one JSON line")
+    ap.add_argument("--config", default="gemma2-2b", help="2b, 9b, 27b, gemma2-2b ... or a config.json")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--profile", choices=["decode", "prefill"], default="",
@@ -334,7 +336,16 @@ def main(argv=None) -> int:
     if a.gpus != 1:
         print(f"janis_b200 is a one-GPU library: --gpus {a.gpus} is not supported")
         return 2
-    rec = run(a.steps, max(3, a.warmup), a.batch, a.context, a.config, a.layers or None,
-              points=() if (a.no_points or a.profile) else (1, 64), profile=a.profile)
+    try:
+        batches = [int(b) for b in str(a.batch).split(",") if b.strip()]
+    except ValueError:
+        batches = []
+    if not batches or min(batches) < 1:
+        print(f"--batch wants positive integers, found {a.batch!r}")
+        return 2
+    points = tuple(batches[1:]) if len(batches) > 1 else (1, 64)
+    config = a.config if (os.path.exists(a.config) or a.config.startswith("gemma2-")) else "gemma2-" + a.config
+    rec = run(a.steps, max(3, a.warmup), batches[0], a.context, config, a.layers or None,
+              points=() if (a.no_points or a.profile) else points, prefill_tokens=a.prefill, profile=a.profile)
     print(json.dumps(rec))
     return 0

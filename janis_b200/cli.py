@@ -53,12 +53,13 @@ def cmd_generate(argv) -> int:
     ap.add_argument("--weights-seed", type=int, default=0)
     ap.add_argument("--ids", action="append", default=[], help="a prompt as comma-separated token ids (repeatable)")
     ap.add_argument("--ids-file", help="one prompt per line, comma- or space-separated ids")
-    ap.add_argument("--temp", type=float, default=0.0)
+    ap.add_argument("--temp", "--temperature", dest="temp", type=float, default=0.0)
     ap.add_argument("--top-p", type=float, default=1.0)
-    ap.add_argument("--max-tokens", type=int, default=_env_int("JANIS_MAXTOK", 512))
+    ap.add_argument("--max-tokens", "--max-new-tokens", dest="max_tokens", type=int,
+                    default=_env_int("JANIS_MAXTOK", 512))
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--stop", default=None, help="stop token ids (default: the model's end-of-sequence ids)")
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     ap.add_argument("--max-cache-tokens", type=int, default=0)
     a = ap.parse_args(argv)
     prompts = [_ids(s) for s in a.ids]

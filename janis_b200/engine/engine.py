@@ -68,15 +68,20 @@ class Engine:
                  max_tokens: int = loop.DEFAULT_MAX_TOKENS, seed: int = 0, stop: Iterable[int] | None = None,
                  on_token: Callable[[int, int], None] | None = None, cancel: Callable[[], bool] | None = None,
                  repeat_penalty: float = 1.0, repeat_last_n: int = 64, mask_stop_on_first: bool = False,
-                 return_replies: bool = False):
+                 return_replies: bool = False, *, temperature: float | None = None,
+                 max_new_tokens: int | None = None, stop_tokens: Iterable[int] | None = None):
         """Replies (lists of token ids) to prompts (lists of token ids), in order.
 
         temp <= 0 is greedy; top_p outside (0, 1] means 1; max_tokens <= 0 means 512; `stop` defaults to
         the model's end-of-sequence ids and a stop token is not part of the reply; `on_token(request,
         token)` hears every token as it is produced; `cancel()` is asked before every decode step.
-        With return_replies=True the result is a list of `Reply` (tokens and finish_reason)."""
+        With return_replies=True the result is a list of `Reply` (tokens and finish_reason).
+        `temperature`, `max_new_tokens` and `stop_tokens` are other names of temp, max_tokens and stop."""
         if self._closed:
             raise RuntimeError("the engine is closed")
+        temp = temp if temperature is None else temperature
+        max_tokens = max_tokens if max_new_tokens is None else max_new_tokens
+        stop = stop if stop_tokens is None else stop_tokens
         params = SamplingParams(temp, top_p, seed, repeat_penalty, repeat_last_n).normalized()
         backend = _Backend(self, params)
         replies = loop.generate(backend, prompts, max_tokens, self.stop_tokens if stop is None else stop,

@@ -20,15 +20,19 @@ class Embedding(Part):
         self.scale = float(scale)
         self.init_std = init_std
         self.table = None
+        self.scale_used = self.scale
 
     def tensor_specs(self):
         return {self.table_name: TensorSpec((self.vocab, self.hidden), init_std=self.init_std)}
 
     def load(self, store, rt: Runtime):
         self.table = store.get(self.table_name, rt.dtype).contiguous()
+        # the reference casts the scalar to the activation dtype before the multiply (`mlxc/mlxc.go:587-601`):
+        # in bfloat16 sqrt(2304) = 48 stays exact, sqrt(3584) = 59.87 becomes 59.75
+        self.scale_used = float(torch.tensor(self.scale, dtype=torch.float32).to(rt.dtype))
 
     def forward(self, tokens, ctx: StepContext, out):
-        return ctx.rt.ops.embed(tokens, self.table, self.scale, out)
+        return ctx.rt.ops.embed(tokens, self.table, self.scale_used, out)
 
 
 class LMHead(Part):
