@@ -19,21 +19,14 @@
 //
 // A prompt step with few tiles of queries (a short prompt, few heads) leaves SMs idle, and its last tile
 // walks all the keys while the first walks one tile of them.  Such a step runs with `parts` = 2: a tile
-// of queries with at least SPLIT_MIN key tiles is shared by two CTAs, each walks half of the keys and
+// of queries with at least `split_min` key tiles is shared by two CTAs, each walks half of the keys and
 // writes its maximum, sum and unnormalised output to scratch, and a second kernel adds the halves.
-#include "common.cuh"
-
-#ifndef JANIS_HEAD_DIM
-#error "compile with -DJANIS_HEAD_DIM=<head size, a multiple of 16>"
-#endif
+#include "attention_prefill_tiles.cuh"
 
 namespace janis {
 namespace pf {
 
-constexpr int HD = JANIS_HEAD_DIM;
-constexpr int BN = HD <= 256 ? 64 : 32;               // keys per tile
-constexpr int WARPS = HD <= 256 ? 8 : 4;              // 16 query rows each
-constexpr int BM = WARPS * 16, THREADS = WARPS * 32;
+constexpr int THREADS = WARPS * 32;
 constexpr int CHUNKS = HD / 8;                        // 16-byte pieces per row
 constexpr int swz_pow2(int n) { return n % 8 == 0 ? 8 : (n % 4 == 0 ? 4 : (n % 2 == 0 ? 2 : 1)); }
 constexpr int SWZ_MASK = swz_pow2(CHUNKS) - 1;
@@ -41,8 +34,6 @@ constexpr int ROW_BYTES = HD * 2;
 constexpr int Q_BYTES = BM * ROW_BYTES;
 constexpr int KV_BYTES = BN * ROW_BYTES;              // one of K or V, one stage
 constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES;    // Q, then two stages of (K, V)
-constexpr int SPLIT_MIN = 4;                          // key tiles from which a tile of queries is shared
-constexpr int PART_ROW = HD + 2;                      // floats of a partial row: maximum, sum, output
 static_assert(SMEM_BYTES <= 227 * 1024, "tiles do not fit shared memory");
 
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
@@ -74,24 +65,6 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-
-__device__ __forceinline__ float ex2(float x) {        // 2^x; ex2(-inf) = 0
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ float fast_tanh(float x) {  // 1 - 2 / (e^2x + 1); exact limits at +-inf
-    const float e = ex2(x * 2.8853900817779268f);      // 2 log2(e)
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(e + 1.0f));
-    return 1.0f - 2.0f * r;
-}
-
 // `rows` rows x HD of bf16 from global rows (row stride `stride` elements) into a swizzled tile;
 // rows >= n_valid are filled with zeros.
 __device__ __forceinline__ void load_tile(uint32_t smem, const bf16* src, size_t stride, int rows, int n_valid) {
@@ -102,30 +75,12 @@ __device__ __forceinline__ void load_tile(uint32_t smem, const bf16* src, size_t
     }
 }
 
-// The sequence and the tile of BM queries that item `tile` of the step stands for (false: none).
-__device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ seq_len, int n_seq, int& seq, int& q0, int& len) {
-    for (int s = 0; s < n_seq; ++s) {
-        const int n = seq_len[s];
-        const int nt = (n + BM - 1) / BM;
-        if (tile < nt) { seq = s; q0 = tile * BM; len = n; return true; }
-        tile -= nt;
-    }
-    return false;
-}
-
-// Key tiles [k_first / BN, ...) that a tile of queries walks: n_tiles of them from key k_first.
-__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_first, int& n_tiles) {
-    const int q_last = min(q0 + BM, len) - 1;
-    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
-    k_first = (j_first / BN) * BN;
-    n_tiles = (q_last - k_first) / BN + 1;
-}
-
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__ kv_src,
                         const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
                         bf16* __restrict__ out, int nq, int nkv, int q_row_heads, int kv_row_heads,
-                        int kv_k_head0, float scale, float cap, int window, int parts, float* __restrict__ partial) {
+                        int kv_k_head0, float scale, float cap, int window, int parts, int split_min,
+                        float* __restrict__ partial) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // Which sequence, which tile of BM queries and which part of its keys is this CTA's.  Items are handed
     // out from the end of the list: the last tiles of a sequence see the most keys and should start first.
@@ -146,7 +101,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     const size_t q_stride = (size_t)q_row_heads * HD, kv_stride = (size_t)kv_row_heads * HD;
     int k_first, n_tiles;
     key_tiles(q0, len, window, k_first, n_tiles);
-    const bool shared_tile = parts > 1 && n_tiles >= SPLIT_MIN;     // the merge kernel decides the same way
+    const bool shared_tile = parts > 1 && n_tiles >= split_min;     // the merge kernel decides the same way
     if (!shared_tile && part > 0) return;
     if (shared_tile) {                                               // this part's share of the key tiles
         const int t0 = (int)((long long)n_tiles * part / parts), t1 = (int)((long long)n_tiles * (part + 1) / parts);
@@ -307,7 +262,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
 __global__ void __launch_bounds__(256)
 attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restrict__ seq_first_row,
                           const int* __restrict__ seq_len, int n_seq, bf16* __restrict__ out, int nq, int window,
-                          int parts) {
+                          int parts, int split_min) {
     const int gtile = blockIdx.x, head = blockIdx.y;
     constexpr int ROWS = 16;                          // rows of the tile per CTA
     const int r_begin = blockIdx.z * ROWS;
@@ -317,7 +272,7 @@ attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restri
     if (!find_tile(gtile, seq_len, n_seq, seq, q0, len)) return;
     int k_first, n_tiles;
     key_tiles(q0, len, window, k_first, n_tiles);
-    if (n_tiles < SPLIT_MIN) return;
+    if (n_tiles < split_min) return;
     const int rows = min(ROWS, len - q0 - r_begin);
     const int first = seq_first_row[seq];
     const float* base = partial + (((size_t)gtile * nq + head) * parts * BM) * PART_ROW;
@@ -369,12 +324,17 @@ JANIS_EXPORT long long janis_attn_prefill_scratch(int n_tiles_bound, int nq) {
     return parts > 1 ? (long long)n_tiles_bound * nq * parts * pf::BM * pf::PART_ROW : 0;
 }
 
-// q_src: [T, q_row_heads, hd] with the queries in its first nq heads; keys and values of position j of
-// sequence s are read from row seq_first_row[s] + j of kv_src [T, kv_row_heads, hd], key heads starting at
+static int g_prefill_kernel = 1;    // 1: tcgen05 where the head size allows it, else mma.sync; 0: mma.sync always
+
+// Which kernel janis_attn_prefill_mma launches (both give the same results up to rounding).
+JANIS_EXPORT void janis_attn_set_prefill_kernel(int which) { g_prefill_kernel = which ? 1 : 0; }
+
+// q_src: [n_tok, q_row_heads, hd] with the queries in its first nq heads; keys and values of position j of
+// sequence s are read from row seq_first_row[s] + j of kv_src [n_tok, kv_row_heads, hd], key heads starting at
 // head kv_k_head0, value heads nkv later.  n_tiles_bound >= sum over sequences of ceil(len / tile), tile =
 // janis_attn_prefill_tile().  partial: janis_attn_prefill_scratch(n_tiles_bound, nq) floats, or null (or
 // fewer floats), in which case no tile is shared.
-JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, const int* seq_first_row,
+JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, int n_tok, const int* seq_first_row,
                                         const int* seq_len, int n_seq, int n_tiles_bound, void* out, int nq,
                                         int nkv, int q_row_heads, int kv_row_heads, int kv_k_head0, float scale,
                                         float cap, int window, float* partial, long long partial_floats,
@@ -393,13 +353,25 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, c
     }
     int parts = janis_attn_prefill_parts(n_tiles_bound, nq);
     if (partial == nullptr || partial_floats < janis_attn_prefill_scratch(n_tiles_bound, nq)) parts = 1;
+    // Every tile of queries with at least 4 key tiles is shared.  (Sharing only the tiles longer than an SM's even
+    // share of the step was slower: items are handed out in tile order, and an unshared tile of 14 key tiles then
+    // starts after the halves of longer ones that are shorter than it.)
+    const int split_min = 4;
     if ((long long)n_tiles_bound * parts > 65535) return fail("attn_prefill_mma: %d tiles of queries exceed the grid", n_tiles_bound);
-    dim3 grid(nq, n_tiles_bound * parts);
-    pf::attn_prefill_mma_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
-        (const bf16*)q_src, (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
-        kv_row_heads, kv_k_head0, scale, cap, window, parts, partial);
-    if (launched("attn_prefill_mma")) return 1;
+    int done = -1;
+    if (g_prefill_kernel == 1)
+        done = launch_prefill_tc05(q_src, kv_src, n_tok, seq_first_row, seq_len, n_seq, n_tiles_bound, out, nq, nkv,
+                                   q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window, parts, split_min, partial,
+                                   stream);
+    if (done > 0) return 1;
+    if (done < 0) {
+        dim3 grid(nq, n_tiles_bound * parts);
+        pf::attn_prefill_mma_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
+            (const bf16*)q_src, (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
+            kv_row_heads, kv_k_head0, scale, cap, window, parts, split_min, partial);
+        if (launched("attn_prefill_mma")) return 1;
+    }
     if (parts == 1) return 0;
     return launch_kernel("attn_prefill_merge", pf::attn_prefill_merge_kernel, dim3(n_tiles_bound, nq, pf::BM / 16), dim3(256), 0, stream, 1,
-                         (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts);
+                         (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts, split_min);
 }

@@ -1,0 +1,514 @@
+// Prompt attention in bfloat16 on the 5th-generation tensor cores, for head sizes that are a multiple
+// of 64 up to 256; one head size per compiled library (JANIS_HEAD_DIM).
+//
+// A CTA owns 128 queries of one sequence and one query head and walks the tiles of 64 keys that the
+// causal mask and the window leave (the tiling, the sharing of long tiles between CTAs and the merge
+// are those of attention_prefill_mma.cu).  Three roles:
+//   * one thread brings Q once and then K and V tiles by TMA tensor maps (128-byte swizzle, slabs of 64
+//     features) into a ring of two stages;
+//   * one thread issues tcgen05.mma: S = Q K^T (K-major operands) into one of two [128 x 64] float
+//     buffers in tensor memory, and O += P V (V is the MN-major operand: its rows are keys) into a
+//     [128 x head size] float accumulator in tensor memory;
+//   * sixteen warps do the softmax, four threads per query row (tensor-memory lane = row; a thread takes
+//     16 of a tile's 64 keys): tcgen05.ld of the scores, scale, cap * tanh, masks on absolute positions,
+//     the row's maximum through shared memory, exponentials, P rounded to bfloat16 into shared memory
+//     for the second product.  Four softmax warps per scheduler hide each other's latencies; with one
+//     the kernel ran at a sixth of an instruction per cycle.
+// While the softmax works on tile i the tensor cores compute S of tile i + 1.  The accumulator is
+// rescaled only when a row's maximum has grown by more than 2^8 since the reference the exponentials
+// use (P stays below 256, far inside bfloat16 and float range), so most tiles leave it untouched.
+// Every wait is bounded: on a timeout the CTA records it (janis_attn_tc05_timeouts), frees its tensor
+// memory and returns.  No TMA load here uses cluster multicast.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "attention_prefill_tiles.cuh"
+
+namespace janis {
+namespace pt {
+
+using pf::BM;
+using pf::BN;
+using pf::HD;
+
+constexpr bool SUPPORTED = HD % 64 == 0 && HD <= 256;
+constexpr int SLABS = SUPPORTED ? HD / 64 : 1;        // slabs of 64 features: one 128-byte swizzle row each
+constexpr int Q_SLAB = BM * 128;                      // bytes
+constexpr int KV_SLAB = BN * 128;
+constexpr int Q_BYTES = SLABS * Q_SLAB;
+constexpr int KV_TILE = SLABS * KV_SLAB;              // one of K or V, one stage
+constexpr int STAGES = 2;
+constexpr int P_BYTES = BM * 128;                     // 64 keys of bfloat16 per query row
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + STAGES * 2 * KV_TILE + P_BYTES;
+constexpr int TMEM_COLS = HD + 128 <= 256 ? 256 : 512;        // O, then two buffers of S
+#ifndef JANIS_PT_SPLIT
+#define JANIS_PT_SPLIT 4
+#endif
+constexpr int SPLIT = JANIS_PT_SPLIT;                 // threads that share a query row in the softmax (each 64 / SPLIT keys)
+constexpr int CPT = 64 / SPLIT;                       // keys per softmax thread and tile: 16
+static_assert(SPLIT == 4, "the softmax works in pieces of 16 columns");
+constexpr int SOFTMAX_WARPS = 4 * SPLIT;              // warp w: rows 32 (w % 4) .., keys CPT (w / 4) .. of a tile
+constexpr int LOADER_WARP = SOFTMAX_WARPS, ISSUER_WARP = SOFTMAX_WARPS + 1;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+constexpr int OCOLS = HD / SPLIT;                     // accumulator columns a softmax thread looks after
+constexpr float RESCALE_STEP = 8.0f;                  // in units of log2: P stays below 2^8
+
+enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_DONE = 14, ROW_X = 15, N_BARS = 16 };
+
+__device__ int g_timeouts = 0;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+// try_wait parks the thread for a while instead of spinning (eighteen warps poll here, and spinning took the
+// issue slots of the ones that compute); a bounded number of tries, then give up.  `failed` lets the other
+// roles give up sooner.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* failed) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((it & 63) == 63 && *failed) return false;
+    }
+    return false;
+}
+// one arrival per warp: the lanes' writes are ordered before it by the warp barrier
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+// Shared-memory operand in rows of 128 bytes with the 128-byte swizzle, groups of 8 rows 1024 bytes apart.
+// K-major operands (Q, K, P) walk along a row; the MN-major operand (V) has its K index on the rows.  One
+// instruction never spans two slabs here, so both offset fields name the distance between groups of 8 rows.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address
+    d |= (uint64_t)(1024 >> 4) << 16;                   // leading byte offset
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
+    d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+// kind::f16, bfloat16 operands, float accumulator, shape M x N x 16; b_mn: the second operand is MN-major
+__device__ __forceinline__ uint32_t instr_desc(int M, int N, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                         const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
+                         bf16* __restrict__ out, int nq, int nkv, int kv_k_head0, float scale, float cap, int window,
+                         int parts, int split_min, float* __restrict__ partial) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[N_BARS];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+    __shared__ float row_max[2][SPLIT][BM];          // the threads of a row tell each other their maxima (two tiles' worth)
+    __shared__ float row_sum[SPLIT][BM];             // and, at the end, their sums
+    grid_dependents_launch();
+    grid_dependency_wait();
+    // which sequence, which tile of queries, which part of its keys (as in the mma.sync kernel)
+    const int item = (int)gridDim.y - 1 - (int)blockIdx.y;
+    const int gtile = item / parts, part = item % parts;
+    int seq = -1, q0 = 0, len = 0;
+    if (!pf::find_tile(gtile, seq_len, n_seq, seq, q0, len)) return;
+    const int head = blockIdx.x;
+    const int kvh = head / (nq / nkv);
+    const int first = seq_first_row[seq];
+    int k_first, n_tiles;
+    pf::key_tiles(q0, len, window, k_first, n_tiles);
+    const bool shared_tile = parts > 1 && n_tiles >= split_min;
+    if (!shared_tile && part > 0) return;
+    if (shared_tile) {
+        const int t0 = (int)((long long)n_tiles * part / parts), t1 = (int)((long long)n_tiles * (part + 1) / parts);
+        k_first += t0 * BN;
+        n_tiles = t1 - t0;
+    }
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sQ = (raw + 1023) & ~1023u;        // swizzle atoms want 1024-byte alignment
+    const uint32_t sKV = sQ + Q_BYTES;                // stage s: K at sKV + s * 2 KV_TILE, V right after
+    const uint32_t sP = sKV + STAGES * 2 * KV_TILE;
+    unsigned char* p_ptr = smem_raw + (sP - raw);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+    auto bar = [&](int i) { return bar0 + 8 * i; };
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(K_FULL + i), 1);
+            mbar_init(bar(K_EMPTY + i), 1);
+            mbar_init(bar(V_FULL + i), 1);
+            mbar_init(bar(V_EMPTY + i), 1);
+            mbar_init(bar(S_FULL + i), 1);
+            mbar_init(bar(S_EMPTY + i), SOFTMAX_WARPS);
+        }
+        mbar_init(bar(P_FULL), SOFTMAX_WARPS);
+        mbar_init(bar(O_DONE), 1);
+        mbar_init(bar(ROW_X), SOFTMAX_WARPS);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == LOADER_WARP) {                        // one warp allocates tensor memory
+        const uint32_t slot = (uint32_t)__cvta_generic_to_shared(&tmem_slot);
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t tO = tmem, tS = tmem + HD;          // S buffer b at tS + 64 b
+    const volatile int* fail_flag = &failed;
+
+    if (warp == LOADER_WARP && lane == 0) {
+        // ---- loader
+        mbar_expect_tx(bar(Q_FULL), Q_BYTES);
+        for (int sl = 0; sl < SLABS; ++sl) tma_load_2d(sQ + sl * Q_SLAB, &map_q, head * HD + sl * 64, first + q0, bar(Q_FULL));
+        // Keys are free again as soon as their scores are done, values only after P V: the loads follow the
+        // order in which the products finish (K0 K1 V0 V1, then K(i+2) after S(i), V(i+2) after O(i)).
+        bool ok = true;
+        auto load_k = [&](int i) {
+            const int s = i & 1;
+            if (i >= 2 && !mbar_wait(bar(K_EMPTY + s), ((i >> 1) - 1) & 1, fail_flag)) { ok = false; return; }
+            const uint32_t sK = sKV + s * 2 * KV_TILE;
+            mbar_expect_tx(bar(K_FULL + s), KV_TILE);
+            for (int sl = 0; sl < SLABS; ++sl)
+                tma_load_2d(sK + sl * KV_SLAB, &map_kv, (kv_k_head0 + kvh) * HD + sl * 64, first + k_first + i * BN, bar(K_FULL + s));
+        };
+        auto load_v = [&](int i) {
+            const int s = i & 1;
+            if (i >= 2 && !mbar_wait(bar(V_EMPTY + s), ((i >> 1) - 1) & 1, fail_flag)) { ok = false; return; }
+            const uint32_t sV = sKV + s * 2 * KV_TILE + KV_TILE;
+            mbar_expect_tx(bar(V_FULL + s), KV_TILE);
+            for (int sl = 0; sl < SLABS; ++sl)
+                tma_load_2d(sV + sl * KV_SLAB, &map_kv, (kv_k_head0 + nkv + kvh) * HD + sl * 64, first + k_first + i * BN,
+                            bar(V_FULL + s));
+        };
+        load_k(0);
+        if (n_tiles > 1) load_k(1);
+        load_v(0);
+        if (n_tiles > 1) load_v(1);
+        for (int i = 2; ok && i < n_tiles; ++i) {
+            load_k(i);
+            if (ok) load_v(i);
+        }
+        if (!ok) atomicExch(&failed, 1);
+    } else if (warp == ISSUER_WARP && lane == 0) {
+        // ---- the thread that issues the products
+        const uint32_t idesc_s = instr_desc(BM, BN, false), idesc_o = instr_desc(BM, 64, true);
+        auto scores = [&](int it) {                   // S[it & 1] = Q K(it)^T
+            const uint32_t sK = sKV + (it & 1) * 2 * KV_TILE;
+            for (int sl = 0; sl < SLABS; ++sl)
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma(tS + 64 * (it & 1), smem_desc(sQ + sl * Q_SLAB + kk * 32), smem_desc(sK + sl * KV_SLAB + kk * 32),
+                         idesc_s, (sl > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(bar(S_FULL + (it & 1)));      // the scores are there ...
+            umma_commit(bar(K_EMPTY + (it & 1)));     // ... and these keys are no longer needed
+        };
+        bool ok = mbar_wait(bar(Q_FULL), 0, fail_flag) && mbar_wait(bar(K_FULL), 0, fail_flag);
+        if (ok) {
+            fence_after();
+            scores(0);
+        }
+        for (int it = 0; ok && it < n_tiles; ++it) {
+            if (it + 1 < n_tiles) {                   // the next tile's scores run under this tile's softmax
+                const int nx = it + 1, b = nx & 1;
+                ok = mbar_wait(bar(K_FULL + b), (nx >> 1) & 1, fail_flag) &&
+                     (nx < 2 || mbar_wait(bar(S_EMPTY + b), ((nx >> 1) - 1) & 1, fail_flag));
+                if (!ok) break;
+                fence_after();
+                scores(nx);
+            }
+            ok = mbar_wait(bar(P_FULL), it & 1, fail_flag) && mbar_wait(bar(V_FULL + (it & 1)), (it >> 1) & 1, fail_flag);
+            if (!ok) break;
+            fence_after();
+            const uint32_t sV = sKV + (it & 1) * 2 * KV_TILE + KV_TILE;
+            for (int sl = 0; sl < SLABS; ++sl)          // O[:, 64 sl ..] += P V[:, 64 sl ..]; 16 keys per instruction
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma(tO + sl * 64, smem_desc(sP + kk * 32), smem_desc(sV + sl * KV_SLAB + kk * 2048), idesc_o,
+                         (it > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(bar(V_EMPTY + (it & 1)));      // the values are free once these have read them
+            umma_commit(bar(O_DONE));                  // and the accumulator holds tile `it`
+        }
+        if (!ok) atomicExch(&failed, 1);
+    } else if (warp < SOFTMAX_WARPS) {
+        // ---- softmax: SPLIT threads share query row q0 + r (tensor-memory lane r); this one has keys CPT h .. of
+        // each tile and columns OCOLS h .. of the accumulator
+        const int quarter = warp & 3, h = warp >> 2;
+        const int r = quarter * 32 + lane, row_pos = q0 + r;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const float LOG2E = 1.4426950408889634f;
+        const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+        const float cap2 = cap * LOG2E, scale2 = scale * LOG2E, scale_c = scale * inv_cap;
+        float m_ref = -INFINITY, l_run = 0.f;         // reference of the exponentials (log2 units); sum over this thread's keys
+        bool ok = true;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int b = it & 1, k0 = k_first + it * BN;
+            ok = mbar_wait(bar(S_FULL + b), (it >> 1) & 1, fail_flag);
+            if (!ok) break;
+            fence_after();
+            uint32_t sv[CPT];
+            tmem_ld16(tS + 64 * b + CPT * h + lane_base, sv);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            fence_before();
+            warp_arrive(bar(S_EMPTY + b), lane);      // the scores are in registers
+            // scale, cap, masks; scores end up in units of log2(e)
+            const bool inner = k0 + BN - 1 <= q0 && k0 + BN <= len && (window <= 0 || k0 > q0 + BM - 1 - window);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) {
+                const float s = __uint_as_float(sv[j]);
+                float v = cap > 0.f ? cap2 * pf::fast_tanh(s * scale_c) : s * scale2;
+                if (!inner) {
+                    const int key = k0 + CPT * h + j;
+                    const bool seen = key <= row_pos && key < len && (window <= 0 || key > row_pos - window);
+                    v = seen ? v : -INFINITY;
+                }
+                sv[j] = __float_as_uint(v);
+                mx = fmaxf(mx, v);
+            }
+            // (an mbarrier, not bar.sync: a thread that has given up a wait must not leave the others stuck)
+            row_max[b][h][r] = mx;
+            warp_arrive(bar(ROW_X), lane);
+            ok = mbar_wait(bar(ROW_X), it & 1, fail_flag);
+            if (!ok) break;
+#pragma unroll
+            for (int hh = 0; hh < SPLIT; ++hh) mx = fmaxf(mx, row_max[b][hh][r]);
+            // the reference moves only when the maximum has outgrown it by more than RESCALE_STEP
+            // (every thread of the row sees the same maximum and decides the same)
+            float factor = 1.0f;
+            const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx != -INFINITY);
+            if (grow) {
+                factor = pf::ex2(m_ref - mx);          // 2^(-inf) = 0 the first time
+                m_ref = mx;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            l_run *= factor;
+            uint32_t pk[CPT / 2];
+#pragma unroll
+            for (int j = 0; j < CPT; j += 2) {
+                const float p0 = pf::ex2(__uint_as_float(sv[j]) - m_use), p1 = pf::ex2(__uint_as_float(sv[j + 1]) - m_use);
+                l_run += p0 + p1;
+                pk[j / 2] = pf::pack_bf16(p0, p1);
+            }
+            // P's buffer and the accumulator are free once the products of the tile before have finished
+            if (it > 0) {
+                ok = mbar_wait(bar(O_DONE), (it - 1) & 1, fail_flag);
+                if (!ok) break;
+                fence_after();
+                if (__any_sync(0xffffffffu, grow)) {  // tensor-memory accesses are warp-wide: rows that keep their reference use 1
+#pragma unroll 1
+                    for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
+                        uint32_t o[16];
+                        tmem_ld16(tO + c + lane_base, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+                        tmem_st16(tO + c + lane_base, o);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                }
+            }
+            // this thread's CPT keys of row r of P: pieces of 16 bytes, swizzled like the TMA tiles
+#pragma unroll
+            for (int c = 0; c < CPT / 8; ++c) {
+                const int piece = (CPT / 8) * h + c;
+                *reinterpret_cast<uint4*>(p_ptr + r * 128 + ((piece ^ (r & 7)) << 4)) =
+                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            fence_before();
+            warp_arrive(bar(P_FULL), lane);
+        }
+        if (ok) ok = mbar_wait(bar(O_DONE), (n_tiles - 1) & 1, fail_flag);
+        if (!ok) atomicExch(&failed, 1);
+        // the row's sum, in the order of the threads' keys
+        if (ok) {
+            row_sum[h][r] = l_run;
+            warp_arrive(bar(ROW_X), lane);
+            ok = mbar_wait(bar(ROW_X), n_tiles & 1, fail_flag);
+            if (!ok) atomicExch(&failed, 1);
+        }
+        if (ok) {
+            fence_after();
+            float l_row = 0.f;
+#pragma unroll
+            for (int hh = 0; hh < SPLIT; ++hh) l_row += row_sum[hh][r];
+            if (shared_tile) {
+                float* prow = partial + ((((size_t)gtile * nq + head) * parts + part) * BM + r) * pf::PART_ROW;
+                if (h == 0) {
+                    prow[0] = m_ref;
+                    prow[1] = l_row;
+                }
+#pragma unroll 1
+                for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
+                    uint32_t o[16];
+                    tmem_ld16(tO + c + lane_base, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2)
+                        *reinterpret_cast<float2*>(prow + 2 + c + j) = make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1]));
+                }
+            } else {
+                const float inv = 1.0f / l_row;
+                bf16* orow = out + (size_t)(first + row_pos) * nq * HD + (size_t)head * HD;
+#pragma unroll 1
+                for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
+                    uint32_t o[16];
+                    tmem_ld16(tO + c + lane_base, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    if (row_pos < len) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 8) {
+                            uint4 w;
+                            w.x = pf::pack_bf16(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+                            w.y = pf::pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+                            w.z = pf::pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+                            w.w = pf::pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c + j) = w;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    fence_before();
+    __syncthreads();
+    if (warp == LOADER_WARP)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (failed && threadIdx.x == 0) atomicAdd(&g_timeouts, 1);
+}
+
+// ---- host side: tensor maps over the packed rows
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    });
+    return fn;
+}
+
+// a [rows, cols] bfloat16 matrix, cols contiguous, in boxes of 64 x box_rows with the 128-byte swizzle
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace pt
+
+int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const int* seq_first_row, const int* seq_len,
+                        int n_seq, int n_tiles_bound, void* out, int nq, int nkv, int q_row_heads, int kv_row_heads,
+                        int kv_k_head0, float scale, float cap, int window, int parts, int split_min, float* partial,
+                        cudaStream_t stream) {
+    if (!pt::SUPPORTED) return -1;
+    CUtensorMap mq, mkv;
+    if (!pt::make_map(&mq, q_src, n_tok, q_row_heads * pt::HD, pt::BM) ||
+        !pt::make_map(&mkv, kv_src, n_tok, kv_row_heads * pt::HD, pt::BN))
+        return -1;                                    // no encoder, or operands it refuses: the other kernel runs
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(pt::attn_prefill_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             pt::SMEM_BYTES);
+        if (e != cudaSuccess) return fail("attn_prefill_tc05: shared memory of %d bytes refused: %s", pt::SMEM_BYTES,
+                                          cudaGetErrorString(e));
+        configured = true;
+    }
+    return launch_kernel("attn_prefill_tc05", pt::attn_prefill_tc05_kernel, dim3(nq, n_tiles_bound * parts), dim3(pt::THREADS),
+                         pt::SMEM_BYTES, stream, 1, mq, mkv, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, kv_k_head0,
+                         scale, cap, window, parts, split_min, partial);
+}
+
+}  // namespace janis
+
+// How often a CTA of the tcgen05 prompt kernel has given up a wait since the library was loaded (0 unless
+// something is badly wrong).  Synchronises the device.
+JANIS_EXPORT int janis_attn_tc05_timeouts() {
+    int n = -1;
+    if (cudaMemcpyFromSymbol(&n, janis::pt::g_timeouts, sizeof(int)) != cudaSuccess) return -1;
+    return n;
+}

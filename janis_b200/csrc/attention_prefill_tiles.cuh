@@ -1,0 +1,67 @@
+// What the two prompt-attention kernels of a head size share: the tile sizes, how a CTA finds its tile of
+// queries and the key tiles it walks, the layout of the partial results of shared tiles, and the fast
+// exponential and tanh.
+#pragma once
+
+#include "common.cuh"
+
+#ifndef JANIS_HEAD_DIM
+#error "compile with -DJANIS_HEAD_DIM=<head size, a multiple of 16>"
+#endif
+
+namespace janis {
+namespace pf {
+
+constexpr int HD = JANIS_HEAD_DIM;
+constexpr int BN = HD <= 256 ? 64 : 32;               // keys per tile
+constexpr int WARPS = HD <= 256 ? 8 : 4;              // 16 query rows each (mma.sync kernel)
+constexpr int BM = WARPS * 16;                        // queries per tile
+constexpr int PART_ROW = HD + 2;                      // floats of a partial row: maximum, sum, output
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float ex2(float x) {        // 2^x; ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float fast_tanh(float x) {  // 1 - 2 / (e^2x + 1); exact limits at +-inf
+    const float e = ex2(x * 2.8853900817779268f);      // 2 log2(e)
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(e + 1.0f));
+    return 1.0f - 2.0f * r;
+}
+
+// The sequence and the tile of BM queries that item `tile` of the step stands for (false: none).
+__device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ seq_len, int n_seq, int& seq, int& q0, int& len) {
+    for (int s = 0; s < n_seq; ++s) {
+        const int n = seq_len[s];
+        const int nt = (n + BM - 1) / BM;
+        if (tile < nt) { seq = s; q0 = tile * BM; len = n; return true; }
+        tile -= nt;
+    }
+    return false;
+}
+
+// Key tiles [k_first / BN, ...) that a tile of queries walks: n_tiles of them from key k_first.
+__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_first, int& n_tiles) {
+    const int q_last = min(q0 + BM, len) - 1;
+    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
+    k_first = (j_first / BN) * BN;
+    n_tiles = (q_last - k_first) / BN + 1;
+}
+
+}  // namespace pf
+
+// The tcgen05 kernel of the same step (attention_prefill_tc05.cu): 0 launched, 1 failed (message set),
+// -1 this head size or these operands are not for it.
+int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const int* seq_first_row, const int* seq_len,
+                        int n_seq, int n_tiles_bound, void* out, int nq, int nkv, int q_row_heads, int kv_row_heads,
+                        int kv_k_head0, float scale, float cap, int window, int parts, int split_min, float* partial,
+                        cudaStream_t stream);
+
+}  // namespace janis

@@ -32,8 +32,8 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemv_bf16.cu", "gemm_tc05.cu", "sampling.cu"]
-ATTENTION_SOURCES = ["attention.cu", "attention_prefill_mma.cu", "attention_no_alloc.cu"]
-HEADERS = ["common.cuh", "attention_no_alloc.h"]
+ATTENTION_SOURCES = ["attention.cu", "attention_prefill_mma.cu", "attention_prefill_tc05.cu", "attention_no_alloc.cu"]
+HEADERS = ["common.cuh", "attention_no_alloc.h", "attention_prefill_tiles.cuh"]
 
 
 class BuildError(RuntimeError):

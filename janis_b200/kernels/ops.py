@@ -82,7 +82,10 @@ def attention_lib(head_dim: int):
         lib.janis_attn_decode_scratch.restype = c_longlong
         lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P]
         lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
-        lib.janis_attn_prefill_mma.argtypes = [P, P, P, P, I, I, P, I, I, I, I, I, F, F, I, P, c_longlong, P]
+        lib.janis_attn_prefill_mma.argtypes = [P, P, I, P, P, I, I, P, I, I, I, I, I, F, F, I, P, c_longlong, P]
+        lib.janis_attn_set_prefill_kernel.argtypes = [I]
+        lib.janis_attn_set_prefill_kernel.restype = None
+        lib.janis_attn_tc05_timeouts.restype = I
         lib.janis_attn_prefill_scratch.argtypes = [I, I]
         lib.janis_attn_prefill_scratch.restype = c_longlong
         lib.janis_attn_prefill_tile.restype = I
@@ -390,13 +393,24 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
     need = int(lib.janis_attn_prefill_scratch(tiles, nq))
     if scratch is not None and (need == 0 or scratch.numel() < need):
         scratch = None
-    _check(lib, lib.janis_attn_prefill_mma(qkv.data_ptr(), kv_src.data_ptr(), seq_first_row.data_ptr(),
+    _check(lib, lib.janis_attn_prefill_mma(qkv.data_ptr(), kv_src.data_ptr(), T, seq_first_row.data_ptr(),
                                            seq_len.data_ptr(), n_seq, tiles, out.data_ptr(), nq, nkv,
                                            qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),
                                            int(window), _t(scratch, "scratch", torch.float32) if scratch is not None else None,
                                            scratch.numel() if scratch is not None else 0, _stream()),
            2 if scratch is not None else 1)
     return out
+
+
+def attn_set_prefill_kernel(hd: int, which: int = 1) -> None:
+    """Choose the bfloat16 prompt kernel of the head size's library: 1 = tcgen05 with the accumulators in
+    tensor memory where the head size allows it (a multiple of 64 up to 256; the default), 0 = mma.sync."""
+    attention_lib(hd).janis_attn_set_prefill_kernel(int(which))
+
+
+def attn_tc05_timeouts(hd: int) -> int:
+    """How often a CTA of the tcgen05 prompt kernel has given up a wait (0 unless something is badly wrong)."""
+    return int(attention_lib(hd).janis_attn_tc05_timeouts())
 
 
 def attn_set_decode_kernel(hd: int, which: int = 2) -> None:

@@ -32,7 +32,14 @@ TINY_B = dict(
     rope_theta=50000.0, sliding_window=16, query_pre_attn_scalar=24, attn_logit_softcapping=20.0,
     final_logit_softcapping=15.0, rms_norm_eps=1e-5, max_position_embeddings=640, eos_token_id=[1, 7])
 
-TINY = {"A": TINY_A, "B": TINY_B}
+# a head size that the tcgen05 prompt kernel takes (a multiple of 64), a window that cuts inside a tile of keys
+TINY_C = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2", hidden_size=80, num_hidden_layers=2,
+    num_attention_heads=3, num_key_value_heads=1, head_dim=64, intermediate_size=136, vocab_size=300,
+    rope_theta=20000.0, sliding_window=40, query_pre_attn_scalar=48, attn_logit_softcapping=30.0,
+    final_logit_softcapping=20.0, rms_norm_eps=1e-6, max_position_embeddings=768, eos_token_id=2)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
 
 HOT_QK, HOT_EMBED = 20.0, 40.0
 
@@ -73,7 +80,7 @@ def write_tiny(model_dir: str, raw_config: dict, seed: int, hot: bool = False, n
 
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
-    """{'A', 'B', 'A_hot', 'B_hot'} -> folder with config.json and model.safetensors."""
+    """{'A', 'B', 'C', 'A_hot', 'B_hot', 'C_hot'} -> folder with config.json and model.safetensors."""
     out = {}
     seed = 11
     for name, cfg in TINY.items():

@@ -161,3 +161,19 @@ def test_overlapped_and_plain_launches_agree(dtype, graphs, model_dirs):
     for with_overlap, without in zip(outs[:half], outs[half:]):
         for a, b in zip(with_overlap, without):
             assert torch.equal(a, b)
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_of_several_tiles_at_head_size_64(dtype, engines, plain_models):
+    """A head size that the tcgen05 prompt kernel takes: prompts of several tiles of queries (some shared between
+    CTAs), alone and in an unequal batch, then tokens one by one over the same cache."""
+    key = "C_hot"
+    eng = engines(key, dtype, "cuda", max_tokens=2048)
+    reqs = [random_tokens(vocab_of(key), n, 300 + n) for n in (330, 129, 64, 200)]
+    got = run_requests(eng, reqs, [300, 129, 1, 180])
+    for g, r in zip(got, reqs):
+        assert_logits(g, plain_logits(plain_models, key, r), dtype, f"{key} n={len(r)}")
+    alone = run_requests(eng, [reqs[0]], [330])[0]
+    assert_logits(alone, plain_logits(plain_models, key, reqs[0]), dtype, f"{key} alone")
+    assert eng.cache.live_slots() == []

@@ -330,11 +330,22 @@ def test_attn_prefill(dtype, nq, nkv, hd, window, cap):
     close(out, want, tol_of(dtype), "attn_prefill")
 
 
+@pytest.fixture(params=[1, 0], ids=["tcgen05", "mma_sync"])
+def prefill_kernel(request):
+    """Both bfloat16 prompt kernels (head sizes the tcgen05 kernel does not take run mma.sync either way)."""
+    yield request.param
+    for hd in {shape[2] for shape in ATTN_SHAPES} | {96, 112, 80}:
+        ops().attn_set_prefill_kernel(hd, 1)
+
+
 @pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES + [(2, 1, 96), (2, 2, 112)])
 @pytest.mark.parametrize("window,cap", [(0, 0.0), (7, 20.0), (64, 50.0), (100, 30.0)])
-def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap):
-    """The bfloat16 tensor-core kernel: tiles of 64 queries and keys, so lengths around 64 and 128,
+def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap, prefill_kernel):
+    """The bfloat16 tensor-core kernels: tiles of 128 queries and 64 keys, so lengths around 64 and 128,
     a window that cuts inside and across tiles, and a far key that must win."""
+    if prefill_kernel == 1 and (hd % 64 or hd > 256):
+        pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
+    ops().attn_set_prefill_kernel(hd, prefill_kernel)
     lens = [1, 63, 64, 65, 200, 129]
     T = sum(lens)
     first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
@@ -353,14 +364,18 @@ def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap):
     R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, scale, cap, window)
     # P is rounded to bfloat16 before P V: one more rounding step than the CUDA-core kernel
     close(out, want, 2 * BF16_TOL, "attn_prefill on tensor cores")
+    assert ops().attn_tc05_timeouts(hd) == 0
 
 
 @pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 2, 64), (3, 1, 80), (2, 2, 128)])
 @pytest.mark.parametrize("window,cap", [(0, 0.0), (100, 30.0), (300, 50.0)])
-def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap):
+def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, prefill_kernel):
     """Few tiles of queries: the long ones are shared by two CTAs that meet through scratch.  Sequences long
     enough for tiles with many key tiles, a window that leaves some tiles unshared, a far key that must win,
     and the same call without scratch."""
+    if prefill_kernel == 1 and (hd % 64 or hd > 256):
+        pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
+    ops().attn_set_prefill_kernel(hd, prefill_kernel)
     lens = [700, 129, 300, 1]
     T = sum(lens)
     first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
@@ -383,6 +398,7 @@ def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap):
     R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 1.0 / math.sqrt(hd), cap, window)
     close(outs[0], want, 2 * BF16_TOL, "attn_prefill with shared tiles")
     close(outs[1], want, 2 * BF16_TOL, "attn_prefill without scratch")
+    assert ops().attn_tc05_timeouts(hd) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
