@@ -96,13 +96,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
-// Shared-memory operand in rows of 128 bytes with the 128-byte swizzle, groups of 8 rows 1024 bytes apart.
-// K-major operands (Q, K, P) walk along a row; the MN-major operand (V) has its K index on the rows.  One
-// instruction never spans two slabs here, so both offset fields name the distance between groups of 8 rows.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+// Shared-memory operand in rows of 128 bytes with the 128-byte swizzle, groups of 8 rows 1024 bytes apart
+// (the stride byte offset).  K-major operands (Q, K, P) walk along a row and never leave their slab within
+// an instruction; the MN-major operand (V) has its K index on the rows and its N index runs on into the next
+// slabs of 64 features, `lbo` bytes apart (the leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo = 1024) {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address
-    d |= (uint64_t)(1024 >> 4) << 16;                   // leading byte offset
+    d |= (uint64_t)(lbo >> 4) << 16;                    // leading byte offset
     d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
     d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
     d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
@@ -261,7 +262,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (!ok) atomicExch(&failed, 1);
     } else if (warp == ISSUER_WARP && lane == 0) {
         // ---- the thread that issues the products
-        const uint32_t idesc_s = instr_desc(BM, BN, false), idesc_o = instr_desc(BM, 64, true);
+        const uint32_t idesc_s = instr_desc(BM, BN, false), idesc_o = instr_desc(BM, HD, true);
         auto scores = [&](int it) {                   // S[it & 1] = Q K(it)^T
             const uint32_t sK = sKV + (it & 1) * 2 * KV_TILE;
             for (int sl = 0; sl < SLABS; ++sl)
@@ -290,11 +291,9 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!ok) break;
             fence_after();
             const uint32_t sV = sKV + (it & 1) * 2 * KV_TILE + KV_TILE;
-            for (int sl = 0; sl < SLABS; ++sl)          // O[:, 64 sl ..] += P V[:, 64 sl ..]; 16 keys per instruction
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                    umma(tO + sl * 64, smem_desc(sP + kk * 32), smem_desc(sV + sl * KV_SLAB + kk * 2048), idesc_o,
-                         (it > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < 4; ++kk)              // O += P[:, 16 kk ..] V[16 kk .., :]: all features in one instruction
+                umma(tO, smem_desc(sP + kk * 32), smem_desc(sV + kk * 2048, KV_SLAB), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
             umma_commit(bar(V_EMPTY + (it & 1)));      // the values are free once these have read them
             umma_commit(bar(O_DONE));                  // and the accumulator holds tile `it`
         }
