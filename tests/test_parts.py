@@ -17,7 +17,7 @@ from janis_b200.cache.cache import KVNeed, ModelCache, StateNeed
 from janis_b200.engine.engine import Engine
 from janis_b200.engine.model import DecoderModel, LayerCall
 from janis_b200.parts import registry as parts
-from janis_b200.parts.base import Mixer, Runtime, StepContext, WeightStore, Workspace
+from janis_b200.parts.base import FeedForward, Mixer, PositionEncoding, Runtime, StepContext, WeightStore, Workspace
 from janis_b200.parts.embedding import Embedding, LMHead
 from janis_b200.weights.loader import TensorSpec, random_tensors
 from tests import kernel_refs
@@ -339,6 +339,173 @@ def test_a_toy_architecture_with_a_stateful_mixer(on, dtype, toy_registered):
         assert err <= (1e-4 if dtype == torch.float32 else 3e-2) * scale, f"toy request {i}: {err:.3e} / {scale:.3e}"
     out = eng.generate([[1, 2, 3], [4]], max_tokens=5, stop=())
     assert [len(o) for o in out] == [5, 5]
+    eng.close()
+
+
+# ---------------------------------------------------------------------------
+# a feed-forward with routing and another position encoding, defined here and registered
+# ---------------------------------------------------------------------------
+
+class Top1Experts(FeedForward):
+    """A router picks one of several gated feed-forwards per token (router logits in float32, lowest id on a tie)."""
+
+    def __init__(self, hidden, intermediate, n_experts, prefix):
+        self.router_name = prefix + "router.weight"
+        self.hidden, self.n_experts = hidden, n_experts
+        self.experts = [parts.make("feed_forward", "gated_mlp", hidden=hidden, intermediate=intermediate, act="silu",
+                                   names={k: f"{prefix}e{e}.{k}.weight" for k in ("gate", "up", "down")})
+                        for e in range(n_experts)]
+
+    def sub_parts(self):
+        return list(self.experts)
+
+    def tensor_specs(self):
+        return {self.router_name: TensorSpec((self.n_experts, self.hidden), init_std=1.0)}
+
+    def load(self, store, rt):
+        self.router = store.get(self.router_name).float()
+
+    def forward(self, x, ctx):
+        choice = (x.float() @ self.router.T).argmax(-1)
+        out = None
+        for e, expert in enumerate(self.experts):
+            y = expert.forward(x, ctx)                              # the experts share workspace buffers: take a copy
+            y = torch.where((choice == e)[:, None], y, torch.zeros_like(y))
+            out = y if out is None else out + y
+        return out
+
+
+class TablePosition(PositionEncoding):
+    """A learned row per position added to queries and keys; nothing rotates."""
+
+    def __init__(self, head_dim, max_pos, name):
+        self.head_dim, self.max_pos, self.name = head_dim, max_pos, name
+        self.store_only = parts.make("position", "none", head_dim=head_dim)
+
+    def sub_parts(self):
+        return [self.store_only]
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.max_pos, self.head_dim), init_std=0.5)}
+
+    def load(self, store, rt):
+        self.table = store.get(self.name, rt.dtype)
+
+    def encode_and_store(self, qkv, ctx, nq, nkv, hd, kv_line):
+        add = self.table[ctx.tok_pos[:ctx.n_tok].long()]            # [T, hd]
+        n = nq + nkv if (kv_line is not None and kv_line.write) else nq
+        qkv[:, :n] += add[:, None, :]
+        return self.store_only.encode_and_store(qkv, ctx, nq, nkv, hd, kv_line)
+
+
+@dataclass(frozen=True)
+class Toy2Config:
+    hidden: int
+    vocab: int
+    layers: int
+    heads: int = 3
+    head_dim: int = 16
+    intermediate: int = 40
+    experts: int = 3
+
+    @classmethod
+    def from_dict(cls, raw, where="config.json"):
+        return cls(raw["hidden"], raw["vocab"], raw["layers"])
+
+    def to_dict(self):
+        return {"architectures": ["Toy2ForCausalLM"], "hidden": self.hidden, "vocab": self.vocab, "layers": self.layers}
+
+
+def build_toy2(cfg: Toy2Config) -> DecoderModel:
+    H = cfg.hidden
+    blocks = []
+    for i in range(cfg.layers):
+        mixer = parts.make("mixer", "softmax_attention", hidden=H, n_heads=cfg.heads, n_kv_heads=1, head_dim=cfg.head_dim,
+                           scale=cfg.head_dim ** -0.5,
+                           position=parts.make("position", "test_table", head_dim=cfg.head_dim, max_pos=256,
+                                               name=f"l{i}.pos.weight"),
+                           names={k: f"l{i}.{k}.weight" for k in "qkvo"})
+        ff = parts.make("feed_forward", "test_top1", hidden=H, intermediate=cfg.intermediate, n_experts=cfg.experts,
+                        prefix=f"l{i}.")
+        blocks.append(parts.make("block", "pre_norm", mixer=mixer, feed_forward=ff,
+                                 input_norm=parts.make("norm", "rms_norm", width=H, eps=1e-5, weight_name=f"l{i}.n1.weight"),
+                                 pre_ff_norm=parts.make("norm", "rms_norm", width=H, eps=1e-5, weight_name=f"l{i}.n2.weight")))
+    return DecoderModel(cfg, Embedding(cfg.vocab, H, "emb.weight", init_std=1.0), blocks,
+                        parts.make("norm", "rms_norm", width=H, eps=1e-5, weight_name="final.weight"),
+                        LMHead(cfg.vocab, H, "head.weight", init_std=0.3), max_context=256)
+
+
+def toy2_plain(cfg: Toy2Config, w, ids):
+    def norm(x, name):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * w[name]
+
+    n = len(ids)
+    h = w["emb.weight"][ids]
+    margin = float("inf")                        # the smallest gap between the two best router logits
+    for i in range(cfg.layers):
+        p = f"l{i}."
+        x = norm(h, p + "n1.weight")
+        t = w[p + "pos.weight"][:n]
+        q = (x @ w[p + "q.weight"].T).view(n, cfg.heads, cfg.head_dim) + t[:, None, :]
+        k = (x @ w[p + "k.weight"].T).view(n, 1, cfg.head_dim) + t[:, None, :]
+        v = (x @ w[p + "v.weight"].T).view(n, 1, cfg.head_dim)
+        s = (q.transpose(0, 1) @ k.transpose(0, 1).transpose(1, 2)) * cfg.head_dim ** -0.5
+        s = s.masked_fill(~P.visible(n, None), float("-inf"))
+        h = h + (torch.softmax(s, -1) @ v.transpose(0, 1)).transpose(0, 1).reshape(n, -1) @ w[p + "o.weight"].T
+        x = norm(h, p + "n2.weight")
+        logits = x @ w[p + "router.weight"].T
+        top = logits.topk(2, dim=-1).values
+        margin = min(margin, float((top[:, 0] - top[:, 1]).min()))
+        choice = logits.argmax(-1)
+        r = torch.zeros_like(h)
+        for e in range(cfg.experts):
+            g = x @ w[f"{p}e{e}.gate.weight"].T
+            y = ((g / (1 + torch.exp(-g))) * (x @ w[f"{p}e{e}.up.weight"].T)) @ w[f"{p}e{e}.down.weight"].T
+            r = r + torch.where((choice == e)[:, None], y, torch.zeros_like(y))
+        h = h + r
+    return norm(h, "final.weight") @ w["head.weight"].T, margin
+
+
+@pytest.fixture
+def toy2_registered():
+    parts.register("feed_forward", "test_top1", Top1Experts, replace=True)
+    parts.register("position", "test_table", TablePosition, replace=True)
+    janis_b200.register_architecture("Toy2ForCausalLM", Toy2Config, build_toy2, replace=True)
+    yield
+    parts.unregister("feed_forward", "test_top1")
+    parts.unregister("position", "test_table")
+    janis_b200.unregister_architecture("Toy2ForCausalLM")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_a_toy_architecture_with_routing_and_a_position_table(on, dtype, toy2_registered):
+    """Routing is a discrete choice: the comparison with the plain model is made in 32-bit, where a router
+    logit cannot fall the other way (requests whose closest call is within 1e-3 are left out); in bfloat16
+    the model is only run, cached against whole."""
+    rt = runtime(on, dtype)
+    arch, cfg, model = janis_b200.build_model(dict(architectures=["Toy2ForCausalLM"], hidden=24, vocab=40, layers=2))
+    host = random_tensors(model.tensor_specs(), 33, "cpu")
+    assert any(k.endswith("router.weight") for k in host) and any(k.endswith("e2.down.weight") for k in host)
+    model.load(WeightStore({k: v.to(rt.device) for k, v in host.items()}), rt)
+    eng = Engine(model, rt, max_tokens=8 * 64, max_batch=3)
+    w = {k: v.double() for k, v in host.items()}
+    reqs = [random_tokens(40, n, 60 + n) for n in (9, 1, 33, 70, 12)]
+    got = run_requests(eng, reqs, [4, 1, 33, 50, 2], max_live=3)
+    checked = 0
+    for i, (g, r) in enumerate(zip(got, reqs)):
+        assert torch.isfinite(g).all()
+        if dtype != torch.float32:
+            continue
+        want, margin = toy2_plain(cfg, w, r)
+        if margin < 1e-3:
+            continue
+        checked += 1
+        scale = want.abs().max().item()
+        err = (g.double() - want).abs().max().item()
+        assert err <= 1e-4 * scale, f"toy2 request {i}: {err:.3e} / {scale:.3e}"
+    assert dtype != torch.float32 or checked >= 3
+    out = eng.generate([[1, 2, 3], [4]], max_tokens=4, stop=())
+    assert [len(o) for o in out] == [4, 4]
     eng.close()
 
 
