@@ -348,8 +348,8 @@ __device__ __forceinline__ void mma_rows8(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
 }
 // true when the phase with this parity has completed; false after a bounded number of tries
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int it = 0; it < (1 << 22); ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int tries = 1 << 22) {
+    for (int it = 0; it < tries; ++it) {
         uint32_t done;
         asm volatile(
             "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
@@ -359,6 +359,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (done) return true;
     }
     return false;
+}
+
+// The bounded wait on its own: a barrier that nothing completes, waited for with `tries` tries.  The wait gives
+// up, the kernel says so (status 1, and the counter of timeouts goes up) and returns; the context stays usable.
+__global__ void wait_probe_kernel(int tries, int* __restrict__ status) {
+    __shared__ __align__(8) unsigned long long never;
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&never);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+    const bool done = mbar_wait(bar, 0, tries);
+    if (threadIdx.x == 0) {
+        *status = done ? 0 : 1;
+        if (!done) atomicAdd(&g_wait_timeouts, 1);
+    }
 }
 
 template <typename T>
@@ -863,6 +880,13 @@ JANIS_EXPORT int janis_attn_wait_timeouts() {
     int n = -1;
     if (cudaMemcpyFromSymbol(&n, g_wait_timeouts, sizeof(int)) != cudaSuccess) return -1;
     return n;
+}
+
+// Runs the bounded wait against a barrier nothing completes (at most 4096 tries): *status becomes 1.
+JANIS_EXPORT int janis_attn_wait_probe(int tries, int* status, cudaStream_t stream) {
+    if (tries < 1 || tries > 4096) return fail("wait_probe: between 1 and 4096 tries, found %d", tries);
+    wait_probe_kernel<<<1, 32, 0, stream>>>(tries, status);
+    return launched("wait_probe");
 }
 
 template <int RB>

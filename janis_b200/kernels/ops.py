@@ -92,6 +92,7 @@ def attention_lib(head_dim: int):
         lib.janis_attn_set_decode_kernel.argtypes = [I]
         lib.janis_attn_set_decode_kernel.restype = None
         lib.janis_attn_wait_timeouts.restype = I
+        lib.janis_attn_wait_probe.argtypes = [I, P, P]
         lib.janis_attn_set_overlap.argtypes = [I]
         lib.janis_attn_set_overlap.restype = None
         lib.janis_attn_set_overlap(1 if _overlap else 0)
@@ -424,6 +425,15 @@ def attn_set_decode_kernel(hd: int, which: int = 2) -> None:
 def attn_wait_timeouts(hd: int) -> int:
     """How often a decode CTA gave up waiting for its bulk copies (0 in a healthy run); synchronises."""
     return int(attention_lib(hd).janis_attn_wait_timeouts())
+
+
+def attn_wait_probe(hd: int, tries: int = 64) -> int:
+    """Runs the kernels' bounded wait on a barrier that nothing completes: returns 1 when the wait gave up
+    (as it must) and the kernel returned.  Raises the library's counter of timeouts by one."""
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib = attention_lib(hd)
+    _check(lib, lib.janis_attn_wait_probe(int(tries), status.data_ptr(), _stream()))
+    return int(status.item())
 
 
 def attn_decode_scratch_floats(n_seq: int, nq: int, hd: int, max_chunks: int) -> int:

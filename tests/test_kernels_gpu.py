@@ -462,6 +462,19 @@ def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, kernel):
     close(out, want, tol_of(dtype), "attn_decode")
 
 
+def test_a_wait_that_nothing_ends_gives_up_and_returns():
+    """The kernels' waits are bounded: a barrier nobody completes makes the wait return a status, the host
+    reads it, and the device goes on working."""
+    hd = 96                                    # a library whose counter no other test expects to be zero
+    before = ops().attn_wait_timeouts(hd)
+    assert ops().attn_wait_probe(hd, tries=32) == 1
+    assert ops().attn_wait_timeouts(hd) == before + 1
+    x = rnd((3, 64), torch.float32, 90)
+    out = torch.empty_like(x)
+    ops().rmsnorm(x, torch.ones(64, device=dev()), 1e-6, out)
+    assert torch.isfinite(out).all()
+
+
 def test_attn_decode_marks_an_undersized_launch():
     nq, nkv, hd = 2, 1, 32
     d = dev()
