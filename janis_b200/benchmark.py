@@ -267,6 +267,11 @@ def measure_prefill(engine, n_tokens: int, repeats: int = 5, warmup: int = 3, pr
     return {"tok_s": n_tokens / (ms / 1e3), "ms": ms, "flops": prefill_flops(engine.model, n_tokens)}
 
 
+def _pretty(config: str) -> str:
+    name = os.path.splitext(os.path.basename(config))[0]
+    return "Gemma2-" + name[len("gemma2-"):].upper() if name.startswith("gemma2-") else name
+
+
 def run(steps: int = 64, warmup: int = 8, batch: int = 8, context: int = 8192, config: str = "gemma2-2b",
         layers: int | None = None, points=(1, 64), prefill_tokens: int = 2048, e2e: bool = True,
         profile: str = "") -> dict:
@@ -289,7 +294,7 @@ def run(steps: int = 64, warmup: int = 8, batch: int = 8, context: int = 8192, c
     end = measure_e2e(eng, batch, context, steps) if e2e and not profile else None
     cfg = eng.config
     rec = {
-        "metric": "decode tok/s at batch %d (Gemma2-2B sizes, context %d)" % (batch, context),
+        "metric": "decode tok/s at batch %d (%s sizes, context %d)" % (batch, _pretty(config), context),
         "value": round(main["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
