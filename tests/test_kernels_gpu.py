@@ -367,6 +367,28 @@ def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap, prefill_kernel):
     assert ops().attn_tc05_timeouts(hd) == 0
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 2, 64), (2, 1, 128), (3, 1, 48)])
+@pytest.mark.parametrize("lens", [[1], [5], [3, 2], [64], [127, 1]])
+def test_attn_prefill_of_a_few_tokens(nq, nkv, hd, lens, prefill_kernel):
+    """Steps much shorter than a tile of queries or keys (the TMA boxes reach past the end of the rows)."""
+    if prefill_kernel == 1 and (hd % 64 or hd > 256):
+        pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
+    ops().attn_set_prefill_kernel(hd, prefill_kernel)
+    T = sum(lens)
+    first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).int()
+    qkv = rnd((T, nq + 2 * nkv, hd), torch.bfloat16, 43)
+    d = dev()
+    out = torch.full((T, nq * hd), 9.0, dtype=torch.bfloat16, device=d)
+    ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, 1.0 / math.sqrt(hd), 25.0, 0,
+                       seq_len=torch.tensor(lens, dtype=torch.int32, device=d))
+    want = torch.empty((T, nq * hd), dtype=torch.float64)
+    R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 1.0 / math.sqrt(hd), 25.0, 0)
+    close(out, want, 2 * BF16_TOL, "attn_prefill of a few tokens")
+    assert ops().attn_tc05_timeouts(hd) == 0
+
+
 @pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 2, 64), (3, 1, 80), (2, 2, 128)])
 @pytest.mark.parametrize("window,cap", [(0, 0.0), (100, 30.0), (300, 50.0)])
 def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, prefill_kernel):
