@@ -334,7 +334,7 @@ def test_attn_prefill(dtype, nq, nkv, hd, window, cap):
 def prefill_kernel(request):
     """Both bfloat16 prompt kernels (head sizes the tcgen05 kernel does not take run mma.sync either way)."""
     yield request.param
-    for hd in {shape[2] for shape in ATTN_SHAPES} | {96, 112, 80}:
+    for hd in list(ops()._attn):                # the libraries that are loaded: back to their default
         ops().attn_set_prefill_kernel(hd, 1)
 
 
@@ -482,6 +482,59 @@ def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, kernel):
     R.attn_decode(qkv.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, scale, cap, window,
                   ring, chunk, max_chunks)
     close(out, want, tol_of(dtype), "attn_decode")
+
+
+@pytest.mark.parametrize("window,ring", [(0, 0), (1024, 1024)])
+def test_attn_decode_over_thousands_of_keys(window, ring):
+    """Long sequences: many tiles per chunk, many chunks, pages far apart, a far key that must win."""
+    nq, nkv, hd, chunk = 4, 2, 128, 704
+    lens = [5000, 3, 2049]
+    slots = [1, 2, 0]
+    pages_per_seq = 80 if ring == 0 else ring // R.PAGE
+    n_pages = 3 * pages_per_seq + 5
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3))[:3 * pages_per_seq].view(3, pages_per_seq).int()
+    k, v = _paged(n_pages, nkv, hd, torch.bfloat16, 50)
+    qkv = rnd((3, nq + 2 * nkv, hd), torch.bfloat16, 52)
+    far = 0 if window == 0 else 5000 - window          # the oldest key the first sequence still sees
+    idx = far % ring if ring else far
+    k[perm[1, idx // R.PAGE].item(), 0, idx % R.PAGE] = (qkv[0, 0] * 4.0).to(torch.bfloat16)
+    d = dev()
+    seq_slot, seq_len = torch.tensor(slots, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32)
+    max_chunks = (5000 if window == 0 else window) // chunk + 2
+    scratch = torch.empty(ops().attn_decode_scratch_floats(3, nq, hd, max_chunks), dtype=torch.float32, device=d)
+    out = torch.full((3, nq * hd), 7.0, dtype=torch.bfloat16, device=d)
+    ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, 1.0 / math.sqrt(hd),
+                      50.0, window, ring, chunk, max_chunks)
+    want = torch.empty((3, nq * hd), dtype=torch.float64)
+    R.attn_decode(qkv.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, 1.0 / math.sqrt(hd), 50.0,
+                  window, ring, chunk, max_chunks)
+    close(out, want, BF16_TOL, "attn_decode over thousands of keys")
+    assert ops().attn_wait_timeouts(hd) == 0
+
+
+@pytest.mark.parametrize("window", [0, 600])
+def test_attn_prefill_of_a_long_prompt(window, prefill_kernel):
+    """A prompt of many tiles next to short ones (no tile is shared: the step has enough of them)."""
+    nq, nkv, hd = 4, 2, 128
+    ops().attn_set_prefill_kernel(hd, prefill_kernel)
+    lens = [1500, 70, 900]
+    T = sum(lens)
+    first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).int()
+    qkv = rnd((T, nq + 2 * nkv, hd), torch.bfloat16, 53)
+    if window == 0:
+        qkv[0, nq] = qkv[1499, 0] * 3.0            # position 0 of the long prompt answers its last query
+    d = dev()
+    n = ops().attn_prefill_scratch_floats(T, len(lens), nq, hd)
+    scratch = torch.empty((n,), dtype=torch.float32, device=d) if n else None
+    out = torch.full((T, nq * hd), 9.0, dtype=torch.bfloat16, device=d)
+    ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, 1.0 / math.sqrt(hd), 50.0, window,
+                       seq_len=torch.tensor(lens, dtype=torch.int32, device=d), scratch=scratch)
+    want = torch.empty((T, nq * hd), dtype=torch.float64)
+    R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 1.0 / math.sqrt(hd), 50.0, window)
+    close(out, want, 2 * BF16_TOL, "attn_prefill of a long prompt")
+    assert ops().attn_tc05_timeouts(hd) == 0
 
 
 def test_a_wait_that_nothing_ends_gives_up_and_returns():
