@@ -512,6 +512,36 @@ def test_attn_decode_over_thousands_of_keys(window, ring):
     assert ops().attn_wait_timeouts(hd) == 0
 
 
+@pytest.mark.parametrize("slope", [1.0, -1.0])
+@pytest.mark.parametrize("hd", [64, 256])
+def test_attn_prefill_with_scores_that_climb(hd, slope, prefill_kernel):
+    """Scores that grow (or fall) steadily along the keys, by far more than the step after which the tcgen05
+    kernel moves the reference of its exponentials: the accumulator is rescaled many times, and each row's
+    weight sits on its newest (or oldest) keys."""
+    nq, nkv = 2, 1
+    ops().attn_set_prefill_kernel(hd, prefill_kernel)
+    T = 700
+    g = torch.Generator().manual_seed(77)
+    u = torch.randn(hd, generator=g)
+    u = u / u.norm()
+    qkv = (torch.randn(T, nq + 2 * nkv, hd, generator=g) * 0.05)
+    qkv[:, :nq] += u * 8.0                                        # every query points along u
+    ramp = torch.arange(T, dtype=torch.float32) / T * slope       # key j: u * 60 j / T / 8 * sqrt(hd) -> score 60 j / T
+    qkv[:, nq] += u[None, :] * (ramp[:, None] * 60.0 / 8.0 * math.sqrt(hd))
+    qkv = qkv.to(torch.bfloat16).to(dev())
+    first = torch.tensor([0], dtype=torch.int32)
+    tok_pos = torch.arange(T).int()
+    tok_seq = torch.zeros(T, dtype=torch.int32)
+    d = dev()
+    out = torch.full((T, nq * hd), 9.0, dtype=torch.bfloat16, device=d)
+    ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, 1.0 / math.sqrt(hd), 0.0, 0,
+                       seq_len=torch.tensor([T], dtype=torch.int32, device=d))
+    want = torch.empty((T, nq * hd), dtype=torch.float64)
+    R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 1.0 / math.sqrt(hd), 0.0, 0)
+    close(out, want, 2 * BF16_TOL, "attn_prefill with climbing scores")
+    assert ops().attn_tc05_timeouts(hd) == 0
+
+
 @pytest.mark.parametrize("window", [0, 600])
 def test_attn_prefill_of_a_long_prompt(window, prefill_kernel):
     """A prompt of many tiles next to short ones (no tile is shared: the step has enough of them)."""
