@@ -31,6 +31,10 @@ namespace janis {
 #define JANIS_GEMV_AHEAD 1            // rounds of weights asked for before the wait (0: none; a tuning switch)
 #endif
 
+#ifndef JANIS_GEMV_U1
+#define JANIS_GEMV_U1 4               // blocks of K a warp has in flight per round, up to 8 batch rows (a tuning switch)
+#endif
+
 constexpr int GEMV_WARPS = 8;        // warps of a CTA that split K (4 when N alone gives CTAs enough)
 
 enum { EPI_NONE = 0, EPI_GATED_GELU = 1, EPI_SOFTCAP = 2, EPI_GATED_SILU = 3 };
@@ -263,7 +267,7 @@ JANIS_EXPORT int janis_gemv_bf16(const void* x, const void* W, void* out, int ou
         cluster = 1;
         while (cluster < 4 && tiles * cluster < 512 && nblk >= GEMV_WARPS * cluster * 2 * 2) cluster *= 2;
     }
-    if (M <= 8) return launch_gemv<1, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
+    if (M <= 8) return launch_gemv<1, JANIS_GEMV_U1>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     if (M <= 16) return launch_gemv<2, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     if (M <= 32) return launch_gemv<4, 2>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     return launch_gemv<8, 1>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
