@@ -6,8 +6,9 @@
 // A tile of 16 rows of W belongs to one CTA, or to a thread-block cluster of CL CTAs
 // when N is small (the o and down projections have few rows and long K): the warps of
 // the cluster split K between them in blocks of 32, each CTA adds its warps' partial
-// sums in warp order in its own shared memory, and CTA 0 of the cluster adds the CTAs'
-// sums in rank order through distributed shared memory.  So more SMs pull on the same
+// sums in warp order in its own shared memory, writes them into CTA 0's shared memory
+// (distributed shared memory), and CTA 0 adds the CTAs' sums in rank order after one
+// cluster barrier (tiles of more than 32 batch rows: CTA 0 reads them).  So more SMs pull on the same
 // rows without any scratch in global memory, and a result does not depend on the grid
 // beyond the fixed order of that sum.  Each thread reads 16 contiguous bytes of two
 // rows of W straight into registers; the k order inside a block of 32 is permuted the
@@ -31,6 +32,9 @@ namespace janis {
 #define JANIS_GEMV_AHEAD 1            // rounds of weights asked for before the wait (0: none; a tuning switch)
 #endif
 
+#ifndef JANIS_GEMV_PUSH
+#define JANIS_GEMV_PUSH 1             // the CTAs of a cluster write their sums into CTA 0 (one barrier); 0: CTA 0 reads them (two)
+#endif
 #ifndef JANIS_GEMV_U1
 #define JANIS_GEMV_U1 4               // blocks of K a warp has in flight per round, up to 8 batch rows (a tuning switch)
 #endif
@@ -62,6 +66,9 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
                  int K, int epi, float cap) {
     __shared__ float red[NW][MT][32][4];
     __shared__ float cta_sum[MT * 128];        // this CTA's sum over its warps; read by CTA 0 of the cluster
+    constexpr bool PUSH = JANIS_GEMV_PUSH && CL > 1 && MT <= 4;      // (the gather area of 8 row tiles does not fit)
+    __shared__ float gather[PUSH ? CL : 1][PUSH ? MT * 128 : 1];     // in CTA 0 of a cluster: every CTA's sums, written by their owners
+    if (PUSH) asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");   // "I am running": waited for before the push
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int rank = CL > 1 ? (int)cg::this_cluster().block_rank() : 0;
@@ -159,7 +166,24 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
         for (int w = 0; w < NW; ++w) v += red[w][i][ln][c];
         cta_sum[idx] = v;
     }
-    if (CL > 1) {
+    if (PUSH) {
+        // every CTA writes its sums into CTA 0's shared memory (all CTAs of the cluster are running: the
+        // barrier they arrived at when they started), one cluster barrier publishes them, CTA 0 adds them
+        // in rank order and the others are done
+        cg::cluster_group cluster = cg::this_cluster();
+        asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory");
+        float* dst = cluster.map_shared_rank(&gather[0][0], 0) + rank * MT * 128;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < MT * 128; idx += blockDim.x) dst[idx] = cta_sum[idx];
+        cluster.sync();
+        if (rank != 0) return;
+        for (int idx = threadIdx.x; idx < MT * 128; idx += blockDim.x) {
+            float v = gather[0][idx];
+#pragma unroll
+            for (int r = 1; r < CL; ++r) v += gather[r][idx];   // rank order
+            red[0][idx / 128][(idx / 4) % 32][idx % 4] = v;
+        }
+    } else if (CL > 1) {
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();                              // every CTA's sum is in its shared memory
         if (rank == 0) {
