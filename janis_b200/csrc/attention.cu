@@ -526,12 +526,12 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
     // key but the newest was stored by an earlier step: the first tiles are asked for before this
     // kernel waits for the one that stores the newest key and rotates the queries.
     const int slot = seq_slot[s];
+    const int len = seq_len[s];                      // (asked for together: one trip to memory, not two)
     if (slot < 0) {
         grid_dependency_wait();
         if (DIRECT) fill_heads(out, s, nq, nkv, blockIdx.y, RB, 0.f);   // a padding row
         return;
     }
-    const int len = seq_len[s];
     int lo, first_chunk, n_chunks;
     chunk_range(len, window, chunk, lo, first_chunk, n_chunks);
     if (DIRECT && n_chunks > 1) {
@@ -562,6 +562,21 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
     const int t_first = (k_begin / S::TILE) * S::TILE;
     const int n_tiles = (k_end - t_first + S::TILE - 1) / S::TILE;
     const int* table = page_table + (size_t)slot * table_stride;
+    auto page_of = [&](int i) {                      // the page that holds tile i
+        const int p0 = t_first + i * S::TILE;
+        return table[(ring_len > 0 ? p0 % ring_len : p0) / JANIS_PAGE];
+    };
+    auto issue_from = [&](int i, int page) {
+        const int p0 = t_first + i * S::TILE;
+        const int idx = ring_len > 0 ? p0 % ring_len : p0;
+        const size_t off = (((size_t)page * nkv + kvh) * JANIS_PAGE + idx % JANIS_PAGE) * HD;
+        const int st_i = i % S::STAGES;
+        const uint32_t dst = stage0 + st_i * S::STAGE_BYTES, bar = bar0 + 8 * st_i;
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_expect_tx(bar, S::STAGE_BYTES);
+        bulk_load(dst, kpool + off, S::TILE_BYTES, bar);
+        bulk_load(dst + S::TILE_BYTES, vpool + off, S::TILE_BYTES, bar);
+    };
     auto issue = [&](int i) {
         const int p0 = t_first + i * S::TILE;
         const int idx = ring_len > 0 ? p0 % ring_len : p0;
@@ -581,13 +596,20 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
         const int newest = len - 1, shadow = len - 1 - ring_len;
         return !(newest >= p0 && newest < p0 + S::TILE) && !(ring_len > 0 && shadow >= p0 && shadow < p0 + S::TILE);
     };
-    if (threadIdx.x == 0)
-        for (int i = 0; i < S::STAGES && i < n_tiles; ++i)
-            if (early(i)) issue(i);
+    int first_pages[S::STAGES];                      // asked for together, before any of them is needed
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < S::STAGES; ++i) first_pages[i] = i < n_tiles ? page_of(i) : 0;
+#pragma unroll
+        for (int i = 0; i < S::STAGES; ++i)
+            if (i < n_tiles && early(i)) issue_from(i, first_pages[i]);
+    }
     grid_dependency_wait();
-    if (threadIdx.x == 0)
-        for (int i = 0; i < S::STAGES && i < n_tiles; ++i)
-            if (!early(i)) issue(i);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < S::STAGES; ++i)
+            if (i < n_tiles && !early(i)) issue_from(i, first_pages[i]);
+    }
 
     // query fragments: row g of the 16-row operand is head h0 + g (zero beyond nh_here); a thread keeps, for
     // each block of 32 features, the 8 features t*8 .. t*8+7 as the pairs that two k-steps want
@@ -753,24 +775,24 @@ attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kp
             }
             out[((size_t)s * nq + h0 + r) * HD + d] = __float2bfloat16_rn(v / l);
         }
-        return;
-    }
-    for (int idx = threadIdx.x; idx < nh_here * (HD + 2); idx += blockDim.x) {
-        const int r = idx / (HD + 2), d = idx % (HD + 2);
-        float mx = -INFINITY;
+    } else {
+        for (int idx = threadIdx.x; idx < nh_here * (HD + 2); idx += blockDim.x) {
+            const int r = idx / (HD + 2), d = idx % (HD + 2);
+            float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < S::WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
-        float v;
-        if (d == 0) v = mx;
-        else {
-            v = 0.f;
+            for (int w = 0; w < S::WARPS; ++w) mx = fmaxf(mx, sm[w][r][0]);
+            float v;
+            if (d == 0) v = mx;
+            else {
+                v = 0.f;
 #pragma unroll
-            for (int w = 0; w < S::WARPS; ++w) {
-                const float mw = sm[w][r][0];
-                if (mw != -INFINITY) v += sm[w][r][d] * expf(mw - mx);
+                for (int w = 0; w < S::WARPS; ++w) {
+                    const float mw = sm[w][r][0];
+                    if (mw != -INFINITY) v += sm[w][r][d] * expf(mw - mx);
+                }
             }
+            partial[(((size_t)s * nq + h0 + r) * max_chunks + blockIdx.x) * (HD + 2) + d] = v;
         }
-        partial[(((size_t)s * nq + h0 + r) * max_chunks + blockIdx.x) * (HD + 2) + d] = v;
     }
 }
 
@@ -784,24 +806,56 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const int* 
     __shared__ float red[32];
     const int s = blockIdx.x, h = blockIdx.y;
     grid_dependents_launch();
+    const int slot = seq_slot[s], len = seq_len[s];          // the step's tables: read before the wait
     grid_dependency_wait();
     T* o = out + ((size_t)s * nq + h) * HD;
-    if (seq_slot[s] < 0) {
+    if (slot < 0) {
         for (int d = threadIdx.x; d < HD; d += blockDim.x) o[d] = from_float<T>(0.f);
         return;
     }
     int lo, first_chunk, n_chunks;
-    chunk_range(seq_len[s], window, chunk, lo, first_chunk, n_chunks);
+    chunk_range(len, window, chunk, lo, first_chunk, n_chunks);
     if (n_chunks > max_chunks) {   // the launch was sized for shorter sequences: make it visible
         for (int d = threadIdx.x; d < HD; d += blockDim.x) o[d] = from_float<T>(__int_as_float(0x7fc00000));
         return;
     }
     const float* p = partial + ((size_t)s * nq + h) * max_chunks * (HD + 2);
+    const int lane = threadIdx.x & 31;
+    if (n_chunks <= 32) {
+        // Up to 32 chunks: every warp forms the weights by itself, lane c for chunk c, and hands them round by
+        // shuffles: one trip to memory for the maxima and sums, one for the values, no block barrier.
+        const bool mine = lane < n_chunks;
+        const float mc = mine ? p[(size_t)lane * (HD + 2)] : -INFINITY;
+        const float lc = mine ? p[(size_t)lane * (HD + 2) + 1] : 0.f;
+        const float mx = warp_max(mc);
+        const float w = mc == -INFINITY ? 0.f : expf(mc - mx);
+        float l = 0.f;                           // in chunk order, the same in every thread
+        for (int c = 0; c < n_chunks; ++c) l += __shfl_sync(0xffffffffu, lc * w, c);
+        const float inv = 1.0f / l;
+        for (int d0 = 0; d0 < HD; d0 += blockDim.x) {         // the same trips for every lane: the shuffles stay whole
+            const int d = d0 + threadIdx.x;
+            float a0 = 0.f, a1 = 0.f;
+            int c = 0;
+            for (; c + 2 <= n_chunks; c += 2) {
+                const float w0 = __shfl_sync(0xffffffffu, w, c), w1 = __shfl_sync(0xffffffffu, w, c + 1);
+                if (d < HD) {
+                    a0 += p[(size_t)c * (HD + 2) + 2 + d] * w0;
+                    a1 += p[(size_t)(c + 1) * (HD + 2) + 2 + d] * w1;
+                }
+            }
+            if (c < n_chunks) {
+                const float w0 = __shfl_sync(0xffffffffu, w, c);
+                if (d < HD) a0 += p[(size_t)c * (HD + 2) + 2 + d] * w0;
+            }
+            if (d < HD) o[d] = from_float<T>((a0 + a1) * inv);
+        }
+        return;
+    }
     // the maximum over chunks (any order gives the same value)
     float mx = -INFINITY;
     for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) mx = fmaxf(mx, p[(size_t)c * (HD + 2)]);
     mx = warp_max(mx);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    if (lane == 0) red[threadIdx.x >> 5] = mx;
     __syncthreads();
     mx = red[0];
     for (int w = 1; w < (int)((blockDim.x + 31) >> 5); ++w) mx = fmaxf(mx, red[w]);
