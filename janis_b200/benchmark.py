@@ -234,7 +234,8 @@ def measure_e2e(engine, batch: int, context: int, steps: int) -> dict:
             t_first[0] = time.perf_counter()
         count[0] += 1
 
-    engine.generate(prompts, temp=0.0, max_tokens=4, stop=())          # warm-up: the same call, a few tokens
+    # warm-up: the same call over the same lengths, so that every graph the timed call replays exists
+    engine.generate(prompts, temp=0.0, max_tokens=steps + 1, stop=())
     torch.cuda.synchronize()
     engine.generate(prompts, temp=0.0, max_tokens=steps + 1, stop=(), on_token=on_token)
     torch.cuda.synchronize()
