@@ -6,7 +6,11 @@
 // The random number of a draw is Philox4x32-10 keyed by the seed and counted by
 // (request id, index of the token in its reply): it does not depend on which
 // other requests share the batch.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace janis {
 
@@ -52,24 +56,16 @@ __device__ void block_argmax(float v, int i, float* sv, int* si, float& out_v, i
     out_i = bi;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * V;
-    grid_dependents_launch();
-    grid_dependency_wait();
-    float v = -INFINITY;
-    int i = 0x7fffffff;
-    // four independent loads per round keep the memory pipe busy (one dependent load per round is
-    // bound by latency); a thread sees its ids in ascending order, so `>` keeps the lowest id
-    int j = threadIdx.x;
-    if ((V & 3) == 0 && (((uintptr_t)row) & 15) == 0) {
+// The largest value of row[lo, hi) and the lowest id that attains it, as far as this thread's ids go (they
+// ascend, so `>` keeps the lowest).  Four independent loads per round keep the memory pipe busy.
+__device__ __forceinline__ void argmax_scan(const float* __restrict__ row, int lo, int hi, float& v, int& i) {
+    int j = lo + threadIdx.x;
+    if ((lo & 3) == 0 && (((uintptr_t)row) & 15) == 0) {
         // 16-byte loads, two in flight per round; within a load the ids ascend, across rounds too
         const float4* row4 = reinterpret_cast<const float4*>(row);
-        const int V4 = V >> 2;
-        int q = threadIdx.x;
-        for (; q + (int)blockDim.x < V4; q += 2 * blockDim.x) {
+        const int q_end = lo / 4 + (hi - lo) / 4;
+        int q = lo / 4 + threadIdx.x;
+        for (; q + (int)blockDim.x < q_end; q += 2 * blockDim.x) {
             const float4 a = row4[q], b = row4[q + blockDim.x];
             const int ja = q * 4, jb = (q + blockDim.x) * 4;
             if (a.x > v) { v = a.x; i = ja; }
@@ -81,7 +77,7 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
             if (b.z > v) { v = b.z; i = jb + 2; }
             if (b.w > v) { v = b.w; i = jb + 3; }
         }
-        for (; q < V4; q += blockDim.x) {
+        for (; q < q_end; q += blockDim.x) {
             const float4 a = row4[q];
             const int ja = q * 4;
             if (a.x > v) { v = a.x; i = ja; }
@@ -89,23 +85,72 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
             if (a.z > v) { v = a.z; i = ja + 2; }
             if (a.w > v) { v = a.w; i = ja + 3; }
         }
-        j = V;                                             // nothing left for the scalar loops
+        j = q_end * 4 + threadIdx.x;                       // the few ids the 16-byte loads left over
     }
-    for (; j + 3 * (int)blockDim.x < V; j += 4 * blockDim.x) {
+    for (; j + 3 * (int)blockDim.x < hi; j += 4 * blockDim.x) {
         const float x0 = row[j], x1 = row[j + blockDim.x], x2 = row[j + 2 * blockDim.x], x3 = row[j + 3 * blockDim.x];
         if (x0 > v) { v = x0; i = j; }                       // NaN never wins
         if (x1 > v) { v = x1; i = j + blockDim.x; }
         if (x2 > v) { v = x2; i = j + 2 * blockDim.x; }
         if (x3 > v) { v = x3; i = j + 3 * blockDim.x; }
     }
-    for (; j < V; j += blockDim.x) {
+    for (; j < hi; j += blockDim.x) {
         const float x = row[j];
         if (x > v) { v = x; i = j; }
     }
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    grid_dependents_launch();
+    grid_dependency_wait();
+    float v = -INFINITY;
+    int i = 0x7fffffff;
+    argmax_scan(row, 0, V, v, i);
     float bv;
     int bi;
     block_argmax(v, i, sv, si, bv, bi);
     if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+}
+
+// The same for few rows of a large vocabulary: a thread-block cluster of ARGMAX_CLUSTER CTAs shares a row,
+// each takes a stretch of ids, and CTA 0 picks among their results through distributed shared memory
+// (one CTA reads a row of 256,000 logits in 24 us; eight read it in 5).
+constexpr int ARGMAX_CLUSTER = 8;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ float best_v;
+    __shared__ int best_i;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank(), r = blockIdx.x / ARGMAX_CLUSTER;
+    const float* row = logits + (size_t)r * V;
+    const int seg = ((V + ARGMAX_CLUSTER - 1) / ARGMAX_CLUSTER + 3) & ~3;      // a multiple of 4: stretches start 16-byte aligned
+    const int lo = min(V, rank * seg), hi = min(V, lo + seg);
+    grid_dependents_launch();
+    grid_dependency_wait();
+    float v = -INFINITY;
+    int i = 0x7fffffff;
+    argmax_scan(row, lo, hi, v, i);
+    float bv;
+    int bi;
+    block_argmax(v, i, sv, si, bv, bi);
+    if (threadIdx.x == 0) { best_v = bv; best_i = bi; }
+    cluster.sync();                                  // every CTA's result is in its shared memory
+    if (rank == 0 && threadIdx.x == 0) {
+        for (int c = 1; c < ARGMAX_CLUSTER; ++c) {   // stretches ascend with the rank: `>` keeps the lowest id
+            const float ov = *cluster.map_shared_rank(&best_v, c);
+            const int oi = *cluster.map_shared_rank(&best_i, c);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        out[r] = bi == 0x7fffffff ? 0 : bi;
+    }
+    cluster.sync();                                  // nobody leaves while its shared memory is being read
 }
 
 // Exclusive scan of one value per thread, in thread order, by thread 0.
@@ -287,6 +332,9 @@ using namespace janis;
 JANIS_EXPORT int janis_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return fail("argmax: empty vocabulary");
+    if (R <= 32 && V >= 16384)
+        return launch_kernel("argmax", argmax_cluster_kernel, dim3(R * ARGMAX_CLUSTER), dim3(SAMPLE_THREADS), 0, stream,
+                             ARGMAX_CLUSTER, logits, out, V);
     return launch_kernel("argmax", argmax_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 1, logits, out, V);
 }
 

@@ -598,7 +598,7 @@ def test_attn_decode_marks_an_undersized_launch():
     assert torch.isnan(outb.float()).all()
 
 
-@pytest.mark.parametrize("Rn,V", [(1, 7), (5, 384), (3, 256000), (64, 1000)])
+@pytest.mark.parametrize("Rn,V", [(1, 7), (5, 384), (3, 256000), (64, 1000), (2, 50003), (8, 32001), (32, 16384), (33, 20000)])
 def test_argmax_lowest_id_wins(Rn, V):
     logits = rnd((Rn, V), torch.float32, 35)
     logits[0, V // 2] = 50.0
