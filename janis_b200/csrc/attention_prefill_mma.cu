@@ -18,9 +18,11 @@
 // Shared-memory rows are XOR-swizzled in 16-byte pieces against ldmatrix bank conflicts.
 //
 // A prompt step with few tiles of queries (a short prompt, few heads) leaves SMs idle, and its last tile
-// walks all the keys while the first walks one tile of them.  Such a step runs with `parts` = 2: a tile
-// of queries with at least `split_min` key tiles is shared by two CTAs, each walks half of the keys and
-// writes its maximum, sum and unnormalised output to scratch, and a second kernel adds the halves.
+// walks all the keys while the first walks one tile of them.  Such a step cuts the key tiles of a tile of
+// queries into pieces of at most `piece` tiles (no more than `parts` = 4 pieces): each piece is one CTA's, which
+// writes its maximum, sum and unnormalised output to scratch, and a second kernel adds the pieces.
+#include <algorithm>
+
 #include "attention_prefill_tiles.cuh"
 
 namespace janis {
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(THREADS)
 attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__ kv_src,
                         const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
                         bf16* __restrict__ out, int nq, int nkv, int q_row_heads, int kv_row_heads,
-                        int kv_k_head0, float scale, float cap, int window, int parts, int split_min,
+                        int kv_k_head0, float scale, float cap, int window, int parts, int piece,
                         float* __restrict__ partial) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // Which sequence, which tile of BM queries and which part of its keys is this CTA's.  Items are handed
@@ -101,10 +103,11 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     const size_t q_stride = (size_t)q_row_heads * HD, kv_stride = (size_t)kv_row_heads * HD;
     int k_first, n_tiles;
     key_tiles(q0, len, window, k_first, n_tiles);
-    const bool shared_tile = parts > 1 && n_tiles >= split_min;     // the merge kernel decides the same way
-    if (!shared_tile && part > 0) return;
+    const int np = pf::parts_of(n_tiles, parts, piece);
+    const bool shared_tile = np > 1;
+    if (part >= np) return;
     if (shared_tile) {                                               // this part's share of the key tiles
-        const int t0 = (int)((long long)n_tiles * part / parts), t1 = (int)((long long)n_tiles * (part + 1) / parts);
+        const int t0 = (int)((long long)n_tiles * part / np), t1 = (int)((long long)n_tiles * (part + 1) / np);
         k_first += t0 * BN;
         n_tiles = t1 - t0;
     }
@@ -259,37 +262,58 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
 }
 
 // Adds the parts of the shared tiles: out = sum_p o_p 2^(m_p - m) / sum_p l_p 2^(m_p - m), parts in index order.
+// A thread has one piece of 4 outputs of a row and asks for all parts' maxima at once, then for all their sums
+// and outputs at once: two round trips to the scratch (which the attention kernel has just written: L2), not
+// two per part.
+constexpr int MAX_PARTS = 4;
+constexpr int MERGE_ROWS = 8;                         // rows of the tile per CTA
+
 __global__ void __launch_bounds__(256)
 attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restrict__ seq_first_row,
                           const int* __restrict__ seq_len, int n_seq, bf16* __restrict__ out, int nq, int window,
-                          int parts, int split_min) {
+                          int parts, int piece) {
     const int gtile = blockIdx.x, head = blockIdx.y;
-    constexpr int ROWS = 16;                          // rows of the tile per CTA
-    const int r_begin = blockIdx.z * ROWS;
+    const int r_begin = blockIdx.z * MERGE_ROWS;
+    // the step's tables were written before the attention kernel started: they are read while it still runs
+    int seq = -1, q0 = 0, len = 0;
+    const bool found = find_tile(gtile, seq_len, n_seq, seq, q0, len);
+    int k_first = 0, n_tiles = 0;
+    if (found) key_tiles(q0, len, window, k_first, n_tiles);
+    const int np = found ? parts_of(n_tiles, parts, piece) : 1;
+    const int first = found ? seq_first_row[seq] : 0;
     grid_dependents_launch();
     grid_dependency_wait();
-    int seq = -1, q0 = 0, len = 0;
-    if (!find_tile(gtile, seq_len, n_seq, seq, q0, len)) return;
-    int k_first, n_tiles;
-    key_tiles(q0, len, window, k_first, n_tiles);
-    if (n_tiles < split_min) return;
-    const int rows = min(ROWS, len - q0 - r_begin);
-    const int first = seq_first_row[seq];
+    if (np <= 1) return;
+    const int rows = min(MERGE_ROWS, len - q0 - r_begin);
     const float* base = partial + (((size_t)gtile * nq + head) * parts * BM) * PART_ROW;
-    constexpr int VEC = HD / 4;                       // float4 pieces of an output row
+    constexpr int VEC = HD / 4;                       // pieces of 4 outputs in a row
     for (int idx = threadIdx.x; idx < rows * VEC; idx += blockDim.x) {
         const int r = r_begin + idx / VEC, c = (idx % VEC) * 4;
+        const float* row0 = base + (size_t)r * PART_ROW;
+        float mp[MAX_PARTS];
         float m = -INFINITY;
-        for (int p = 0; p < parts; ++p) m = fmaxf(m, base[((size_t)p * BM + r) * PART_ROW]);
+#pragma unroll
+        for (int p = 0; p < MAX_PARTS; ++p) {
+            mp[p] = p < np ? row0[(size_t)p * BM * PART_ROW] : -INFINITY;
+            m = fmaxf(m, mp[p]);
+        }
+        float lp[MAX_PARTS];
+        float2 a[MAX_PARTS], b[MAX_PARTS];
+#pragma unroll
+        for (int p = 0; p < MAX_PARTS; ++p) {
+            const float* row = row0 + (size_t)p * BM * PART_ROW;
+            const bool has = p < np;
+            lp[p] = has ? row[1] : 0.f;
+            a[p] = has ? *reinterpret_cast<const float2*>(row + 2 + c) : make_float2(0.f, 0.f);
+            b[p] = has ? *reinterpret_cast<const float2*>(row + 4 + c) : make_float2(0.f, 0.f);
+        }
         float l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int p = 0; p < parts; ++p) {
-            const float* row = base + ((size_t)p * BM + r) * PART_ROW;
-            const float mp = row[0];
-            if (mp == -INFINITY) continue;            // this part saw no key of the row
-            const float w = ex2(mp - m);
-            l += row[1] * w;
-            const float2 a = *reinterpret_cast<const float2*>(row + 2 + c), b = *reinterpret_cast<const float2*>(row + 4 + c);
-            acc[0] += a.x * w; acc[1] += a.y * w; acc[2] += b.x * w; acc[3] += b.y * w;
+#pragma unroll
+        for (int p = 0; p < MAX_PARTS; ++p) {
+            if (mp[p] == -INFINITY) continue;         // no such part, or it saw no key of the row
+            const float w = ex2(mp[p] - m);
+            l += lp[p] * w;
+            acc[0] += a[p].x * w; acc[1] += a[p].y * w; acc[2] += b[p].x * w; acc[3] += b[p].y * w;
         }
         const float inv = 1.0f / l;
         bf16* o = out + (size_t)(first + q0 + r) * nq * HD + (size_t)head * HD + c;
@@ -314,15 +338,20 @@ static int sm_count() {
     return n;
 }
 
-// CTAs that share a tile of queries in a step of n_tiles_bound tiles and nq heads (1 or 2), and the
-// floats of scratch such a step needs (0 when nothing is shared).
+// The most CTAs that share a tile of queries in a step of n_tiles_bound tiles and nq heads (1: none is shared),
+// and the floats of scratch such a step needs (0 when nothing is shared).
 JANIS_EXPORT int janis_attn_prefill_parts(int n_tiles_bound, int nq) {
-    return (long long)n_tiles_bound * nq < 2LL * sm_count() ? 2 : 1;
+    return (long long)n_tiles_bound * nq < 2LL * sm_count() ? pf::MAX_PARTS : 1;
 }
 JANIS_EXPORT long long janis_attn_prefill_scratch(int n_tiles_bound, int nq) {
     const int parts = janis_attn_prefill_parts(n_tiles_bound, nq);
     return parts > 1 ? (long long)n_tiles_bound * nq * parts * pf::BM * pf::PART_ROW : 0;
 }
+
+static int g_prefill_piece = 0;     // key tiles per piece of a shared tile of queries; 0: chosen from the step's size
+
+// Fixes the size of the pieces that shared tiles of queries are cut into (0: automatic again).
+JANIS_EXPORT void janis_attn_set_prefill_piece(int piece) { g_prefill_piece = piece > 0 ? piece : 0; }
 
 static int g_prefill_kernel = 1;    // 1: tcgen05 where the head size allows it, else mma.sync; 0: mma.sync always
 
@@ -353,25 +382,28 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
     }
     int parts = janis_attn_prefill_parts(n_tiles_bound, nq);
     if (partial == nullptr || partial_floats < janis_attn_prefill_scratch(n_tiles_bound, nq)) parts = 1;
-    // Every tile of queries with at least 4 key tiles is shared.  (Sharing only the tiles longer than an SM's even
-    // share of the step was slower: items are handed out in tile order, and an unshared tile of 14 key tiles then
-    // starts after the halves of longer ones that are shorter than it.)
-    const int split_min = 4;
+    // The pieces that a tile of queries is cut into grow with an SM's even share of the step's key tiles (the
+    // step's lengths are on the device: the estimate takes sequences of equal length).  A CTA costs about as much
+    // as 3 key tiles before and after its tiles, and a piece more is a row of scratch more to merge: measured on
+    // prompts of 512 to 4,096 tokens, pieces of the share plus 3, at most 16, were the fastest or close to it.
+    const long long avg_key_tiles = (long long)n_tok / n_seq / (2 * pf::BN) + 1;
+    const long long share = (long long)n_tiles_bound * nq * avg_key_tiles / sm_count();
+    const int piece = g_prefill_piece > 0 ? g_prefill_piece : (int)std::min<long long>(16, std::max<long long>(4, share + 3));
     if ((long long)n_tiles_bound * parts > 65535) return fail("attn_prefill_mma: %d tiles of queries exceed the grid", n_tiles_bound);
     int done = -1;
     if (g_prefill_kernel == 1)
         done = launch_prefill_tc05(q_src, kv_src, n_tok, seq_first_row, seq_len, n_seq, n_tiles_bound, out, nq, nkv,
-                                   q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window, parts, split_min, partial,
+                                   q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial,
                                    stream);
     if (done > 0) return 1;
     if (done < 0) {
         dim3 grid(nq, n_tiles_bound * parts);
         pf::attn_prefill_mma_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
             (const bf16*)q_src, (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
-            kv_row_heads, kv_k_head0, scale, cap, window, parts, split_min, partial);
+            kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial);
         if (launched("attn_prefill_mma")) return 1;
     }
     if (parts == 1) return 0;
-    return launch_kernel("attn_prefill_merge", pf::attn_prefill_merge_kernel, dim3(n_tiles_bound, nq, pf::BM / 16), dim3(256), 0, stream, 1,
-                         (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts, split_min);
+    return launch_kernel("attn_prefill_merge", pf::attn_prefill_merge_kernel, dim3(n_tiles_bound, nq, pf::BM / pf::MERGE_ROWS), dim3(256), 0, stream, 1,
+                         (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts, piece);
 }

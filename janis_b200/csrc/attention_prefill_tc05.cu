@@ -5,7 +5,7 @@
 // causal mask and the window leave (the tiling, the sharing of long tiles between CTAs and the merge
 // are those of attention_prefill_mma.cu).  Three roles:
 //   * one thread brings Q once and then K and V tiles by TMA tensor maps (128-byte swizzle, slabs of 64
-//     features) into a ring of two stages;
+//     features) into rings of two stages each;
 //   * one thread issues tcgen05.mma: S = Q K^T (K-major operands) into one of two [128 x 64] float
 //     buffers in tensor memory, and O += P V (V is the MN-major operand: its rows are keys) into a
 //     [128 x head size] float accumulator in tensor memory;
@@ -14,7 +14,9 @@
 //     the row's maximum through shared memory, exponentials, P rounded to bfloat16 into shared memory
 //     for the second product.  Four softmax warps per scheduler hide each other's latencies; with one
 //     the kernel ran at a sixth of an instruction per cycle.
-// While the softmax works on tile i the tensor cores compute S of tile i + 1.  The accumulator is
+// The scores run two tiles ahead of P V, and every softmax thread has two tiles in flight: it takes tile
+// i + 1 out of tensor memory, caps and masks it and publishes its maximum before it turns tile i into P, so
+// that it waits neither for the products nor for the other threads of its row.  The accumulator is
 // rescaled only when a row's maximum has grown by more than 2^8 since the reference the exponentials
 // use (P stays below 256, far inside bfloat16 and float range), so most tiles leave it untouched.
 // Every wait is bounded: on a timeout the CTA records it (janis_attn_tc05_timeouts), frees its tensor
@@ -56,7 +58,7 @@ constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr int OCOLS = HD / SPLIT;                     // accumulator columns a softmax thread looks after
 constexpr float RESCALE_STEP = 8.0f;                  // in units of log2: P stays below 2^8
 
-enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_DONE = 14, ROW_X = 15, N_BARS = 16 };
+enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_DONE = 14, ROW_X = 15, N_BARS = 17 };
 
 __device__ int g_timeouts = 0;
 
@@ -69,19 +71,19 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, int bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
-// try_wait parks the thread for a while instead of spinning (eighteen warps poll here, and spinning took the
-// issue slots of the ones that compute); a bounded number of tries, then give up.  `failed` lets the other
-// roles give up sooner.
+// try_wait parks the thread until the phase completes or the hinted time has passed (without the hint it came
+// back after about a hundred cycles, and nineteen warps polling took issue slots from the ones that compute);
+// a bounded number of tries, then give up.  `failed` lets the other roles give up sooner.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* failed) {
-    for (int it = 0; it < (1 << 22); ++it) {
+    for (int it = 0; it < (1 << 18); ++it) {
         uint32_t done;
         asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
             : "=r"(done)
-            : "r"(bar), "r"(parity)
+            : "r"(bar), "r"(parity), "r"(2000u)        // nanoseconds
             : "memory");
         if (done) return true;
-        if ((it & 63) == 63 && *failed) return false;
+        if ((it & 15) == 15 && *failed) return false;
     }
     return false;
 }
@@ -159,16 +161,19 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
+template <bool CAPPED>                                // CAPPED: scores go through cap * tanh(s / cap)
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                          const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
                          bf16* __restrict__ out, int nq, int nkv, int kv_k_head0, float scale, float cap, int window,
-                         int parts, int split_min, float* __restrict__ partial) {
+                         int parts, int piece, float* __restrict__ partial) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[N_BARS];
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
-    __shared__ float row_max[2][SPLIT][BM];          // the threads of a row tell each other their maxima (two tiles' worth)
+    // the threads of a row tell each other their maxima; four tiles' worth, since a warp writes tile i + 1 while
+    // another may still read tile i - 1 (it cannot be behind by more: tile i - 1's exchange needs its arrival)
+    __shared__ float row_max[4][SPLIT][BM];
     __shared__ float row_sum[SPLIT][BM];             // and, at the end, their sums
     grid_dependents_launch();
     grid_dependency_wait();
@@ -182,10 +187,11 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int first = seq_first_row[seq];
     int k_first, n_tiles;
     pf::key_tiles(q0, len, window, k_first, n_tiles);
-    const bool shared_tile = parts > 1 && n_tiles >= split_min;
-    if (!shared_tile && part > 0) return;
+    const int np = pf::parts_of(n_tiles, parts, piece);
+    const bool shared_tile = np > 1;
+    if (part >= np) return;
     if (shared_tile) {
-        const int t0 = (int)((long long)n_tiles * part / parts), t1 = (int)((long long)n_tiles * (part + 1) / parts);
+        const int t0 = (int)((long long)n_tiles * part / np), t1 = (int)((long long)n_tiles * (part + 1) / np);
         k_first += t0 * BN;
         n_tiles = t1 - t0;
     }
@@ -212,6 +218,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         mbar_init(bar(P_FULL), SOFTMAX_WARPS);
         mbar_init(bar(O_DONE), 1);
         mbar_init(bar(ROW_X), SOFTMAX_WARPS);
+        mbar_init(bar(ROW_X + 1), SOFTMAX_WARPS);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -228,13 +235,15 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const volatile int* fail_flag = &failed;
 
     if (warp == LOADER_WARP && lane == 0) {
-        // ---- loader
+        // ---- loader.  A tile of keys is free again as soon as its scores are done, and those run two tiles ahead
+        // of P V, which frees the values: the loads follow the order in which the products finish
+        // (K0 K1 V0 V1 K2 K3, then V(i + 2) after O(i) and K(i + 4) after S(i + 2), which is done by then), so
+        // that a wait for values never holds back the keys that the next scores want.
         mbar_expect_tx(bar(Q_FULL), Q_BYTES);
         for (int sl = 0; sl < SLABS; ++sl) tma_load_2d(sQ + sl * Q_SLAB, &map_q, head * HD + sl * 64, first + q0, bar(Q_FULL));
-        // Keys are free again as soon as their scores are done, values only after P V: the loads follow the
-        // order in which the products finish (K0 K1 V0 V1, then K(i+2) after S(i), V(i+2) after O(i)).
         bool ok = true;
         auto load_k = [&](int i) {
+            if (!ok || i >= n_tiles) return;
             const int s = i & 1;
             if (i >= 2 && !mbar_wait(bar(K_EMPTY + s), ((i >> 1) - 1) & 1, fail_flag)) { ok = false; return; }
             const uint32_t sK = sKV + s * 2 * KV_TILE;
@@ -243,6 +252,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tma_load_2d(sK + sl * KV_SLAB, &map_kv, (kv_k_head0 + kvh) * HD + sl * 64, first + k_first + i * BN, bar(K_FULL + s));
         };
         auto load_v = [&](int i) {
+            if (!ok || i >= n_tiles) return;
             const int s = i & 1;
             if (i >= 2 && !mbar_wait(bar(V_EMPTY + s), ((i >> 1) - 1) & 1, fail_flag)) { ok = false; return; }
             const uint32_t sV = sKV + s * 2 * KV_TILE + KV_TILE;
@@ -251,13 +261,12 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tma_load_2d(sV + sl * KV_SLAB, &map_kv, (kv_k_head0 + nkv + kvh) * HD + sl * 64, first + k_first + i * BN,
                             bar(V_FULL + s));
         };
-        load_k(0);
-        if (n_tiles > 1) load_k(1);
-        load_v(0);
-        if (n_tiles > 1) load_v(1);
-        for (int i = 2; ok && i < n_tiles; ++i) {
-            load_k(i);
-            if (ok) load_v(i);
+        load_k(0); load_k(1);
+        load_v(0); load_v(1);
+        load_k(2); load_k(3);
+        for (int i = 0; ok && i + 2 < n_tiles; ++i) {
+            load_v(i + 2);
+            load_k(i + 4);
         }
         if (!ok) atomicExch(&failed, 1);
     } else if (warp == ISSUER_WARP && lane == 0) {
@@ -278,11 +287,18 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             fence_after();
             scores(0);
         }
+        if (ok && n_tiles > 1) {
+            ok = mbar_wait(bar(K_FULL + 1), 0, fail_flag);
+            if (ok) {
+                fence_after();
+                scores(1);
+            }
+        }
         for (int it = 0; ok && it < n_tiles; ++it) {
-            if (it + 1 < n_tiles) {                   // the next tile's scores run under this tile's softmax
-                const int nx = it + 1, b = nx & 1;
+            if (it + 2 < n_tiles) {                   // the scores run two tiles ahead: the softmax reads tile it + 1
+                const int nx = it + 2, b = nx & 1;    // while it finishes tile it
                 ok = mbar_wait(bar(K_FULL + b), (nx >> 1) & 1, fail_flag) &&
-                     (nx < 2 || mbar_wait(bar(S_EMPTY + b), ((nx >> 1) - 1) & 1, fail_flag));
+                     mbar_wait(bar(S_EMPTY + b), ((nx >> 1) - 1) & 1, fail_flag);
                 if (!ok) break;
                 fence_after();
                 scores(nx);
@@ -305,27 +321,38 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int r = quarter * 32 + lane, row_pos = q0 + r;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const float LOG2E = 1.4426950408889634f;
-        const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
-        const float cap2 = cap * LOG2E, scale2 = scale * LOG2E, scale_c = scale * inv_cap;
+        // scores in units of log2(e): cap2 tanh(s scale / cap) = cap2 - 2 cap2 / (2^(s k_tanh) + 1), or s scale2
+        const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
+        const float k_tanh = CAPPED ? scale / cap * (2.0f * LOG2E) : 0.f;
         float m_ref = -INFINITY, l_run = 0.f;         // reference of the exponentials (log2 units); sum over this thread's keys
-        bool ok = true;
-        for (int it = 0; it < n_tiles; ++it) {
+        // Two tiles are in flight in every thread: stage one of tile it + 1 (scores out of tensor memory, scale,
+        // cap, masks, this thread's maximum told to the row's other threads) runs before stage two of tile it (the
+        // row's maximum, exponentials, P), so that neither the exchange nor the products are waited for.
+        // Stage one already subtracts the reference of the exponentials as it stands then (`base`), in the same
+        // fused multiply-add that ends the cap; stage two corrects the few tiles whose reference has moved since.
+        auto stage_one = [&](int it, uint32_t (&sv)[CPT], float& base) -> bool {
             const int b = it & 1, k0 = k_first + it * BN;
-            ok = mbar_wait(bar(S_FULL + b), (it >> 1) & 1, fail_flag);
-            if (!ok) break;
+            if (!mbar_wait(bar(S_FULL + b), (it >> 1) & 1, fail_flag)) return false;
             fence_after();
-            uint32_t sv[CPT];
             tmem_ld16(tS + 64 * b + CPT * h + lane_base, sv);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             fence_before();
             warp_arrive(bar(S_EMPTY + b), lane);      // the scores are in registers
-            // scale, cap, masks; scores end up in units of log2(e)
+            base = m_ref == -INFINITY ? 0.f : m_ref;
+            const float c0 = CAPPED ? cap2 - base : -base, c1 = -2.0f * cap2;
             const bool inner = k0 + BN - 1 <= q0 && k0 + BN <= len && (window <= 0 || k0 > q0 + BM - 1 - window);
             float mx = -INFINITY;
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
                 const float s = __uint_as_float(sv[j]);
-                float v = cap > 0.f ? cap2 * pf::fast_tanh(s * scale_c) : s * scale2;
+                float v;
+                if (CAPPED) {
+                    float rc;
+                    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(rc) : "f"(pf::ex2(s * k_tanh) + 1.0f));
+                    v = fmaf(rc, c1, c0);              // exact limits: 2^x = inf gives cap2, 2^x = 0 gives -cap2
+                } else {
+                    v = fmaf(s, scale2, c0);
+                }
                 if (!inner) {
                     const int key = k0 + CPT * h + j;
                     const bool seen = key <= row_pos && key < len && (window <= 0 || key > row_pos - window);
@@ -334,13 +361,17 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 sv[j] = __float_as_uint(v);
                 mx = fmaxf(mx, v);
             }
-            // (an mbarrier, not bar.sync: a thread that has given up a wait must not leave the others stuck)
-            row_max[b][h][r] = mx;
-            warp_arrive(bar(ROW_X), lane);
-            ok = mbar_wait(bar(ROW_X), it & 1, fail_flag);
-            if (!ok) break;
+            // (an mbarrier, not bar.sync: a thread that has given up a wait must not leave the others stuck;
+            // two of them in turn, since a warp arrives for tile it + 1 before all have arrived for tile it)
+            row_max[it & 3][h][r] = mx + base;
+            warp_arrive(bar(ROW_X + b), lane);
+            return true;
+        };
+        auto stage_two = [&](int it, uint32_t (&sv)[CPT], float base) -> bool {
+            if (!mbar_wait(bar(ROW_X + (it & 1)), (it >> 1) & 1, fail_flag)) return false;
+            float mx = row_max[it & 3][0][r];
 #pragma unroll
-            for (int hh = 0; hh < SPLIT; ++hh) mx = fmaxf(mx, row_max[b][hh][r]);
+            for (int hh = 1; hh < SPLIT; ++hh) mx = fmaxf(mx, row_max[it & 3][hh][r]);
             // the reference moves only when the maximum has outgrown it by more than RESCALE_STEP
             // (every thread of the row sees the same maximum and decides the same)
             float factor = 1.0f;
@@ -351,17 +382,21 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             l_run *= factor;
+            if (base != m_use) {                       // the reference has moved since stage one of this tile
+                const float shift = base - m_use;
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) sv[j] = __float_as_uint(__uint_as_float(sv[j]) + shift);
+            }
             uint32_t pk[CPT / 2];
 #pragma unroll
             for (int j = 0; j < CPT; j += 2) {
-                const float p0 = pf::ex2(__uint_as_float(sv[j]) - m_use), p1 = pf::ex2(__uint_as_float(sv[j + 1]) - m_use);
+                const float p0 = pf::ex2(__uint_as_float(sv[j])), p1 = pf::ex2(__uint_as_float(sv[j + 1]));
                 l_run += p0 + p1;
                 pk[j / 2] = pf::pack_bf16(p0, p1);
             }
             // P's buffer and the accumulator are free once the products of the tile before have finished
             if (it > 0) {
-                ok = mbar_wait(bar(O_DONE), (it - 1) & 1, fail_flag);
-                if (!ok) break;
+                if (!mbar_wait(bar(O_DONE), (it - 1) & 1, fail_flag)) return false;
                 fence_after();
                 if (__any_sync(0xffffffffu, grow)) {  // tensor-memory accesses are warp-wide: rows that keep their reference use 1
 #pragma unroll 1
@@ -386,24 +421,40 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             fence_before();
             warp_arrive(bar(P_FULL), lane);
+            return true;
+        };
+        uint32_t sv[CPT], sv_next[CPT];
+        float base = 0.f, base_next = 0.f;
+        bool ok = stage_one(0, sv, base);
+        for (int it = 0; ok && it < n_tiles; ++it) {
+            if (it + 1 < n_tiles) ok = stage_one(it + 1, sv_next, base_next);
+            ok = ok && stage_two(it, sv, base);
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) sv[j] = sv_next[j];
+            base = base_next;
         }
         if (ok) ok = mbar_wait(bar(O_DONE), (n_tiles - 1) & 1, fail_flag);
         if (!ok) atomicExch(&failed, 1);
         // the row's sum, in the order of the threads' keys
         if (ok) {
-            row_sum[h][r] = l_run;
-            warp_arrive(bar(ROW_X), lane);
-            ok = mbar_wait(bar(ROW_X), n_tiles & 1, fail_flag);
+            row_sum[h][r] = l_run;                     // exchanged like the maximum of a tile after the last
+            warp_arrive(bar(ROW_X + (n_tiles & 1)), lane);
+            ok = mbar_wait(bar(ROW_X + (n_tiles & 1)), (n_tiles >> 1) & 1, fail_flag);
             if (!ok) atomicExch(&failed, 1);
         }
+        // The tile leaves through shared memory (the rings of keys and values are free now): a thread owns a row
+        // of the accumulator, so stores straight from its registers would touch a different row of the output with
+        // every lane.  Staged in pieces of 16 bytes, XOR-swizzled by row against bank conflicts, the rows then go
+        // out as whole lines.
+        unsigned char* stage = smem_raw + (sKV - raw);
         if (ok) {
             fence_after();
             float l_row = 0.f;
 #pragma unroll
             for (int hh = 0; hh < SPLIT; ++hh) l_row += row_sum[hh][r];
             if (shared_tile) {
-                float* prow = partial + ((((size_t)gtile * nq + head) * parts + part) * BM + r) * pf::PART_ROW;
                 if (h == 0) {
+                    float* prow = partial + ((((size_t)gtile * nq + head) * parts + part) * BM + r) * pf::PART_ROW;
                     prow[0] = m_ref;
                     prow[1] = l_row;
                 }
@@ -413,28 +464,52 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     tmem_ld16(tO + c + lane_base, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2)
-                        *reinterpret_cast<float2*>(prow + 2 + c + j) = make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1]));
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<uint4*>(stage + (size_t)r * (HD * 4) + ((((c + j) >> 2) ^ (r & 7)) << 4)) =
+                            make_uint4(o[j], o[j + 1], o[j + 2], o[j + 3]);
                 }
             } else {
                 const float inv = 1.0f / l_row;
-                bf16* orow = out + (size_t)(first + row_pos) * nq * HD + (size_t)head * HD;
 #pragma unroll 1
                 for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
                     uint32_t o[16];
                     tmem_ld16(tO + c + lane_base, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                    if (row_pos < len) {
 #pragma unroll
-                        for (int j = 0; j < 16; j += 8) {
-                            uint4 w;
-                            w.x = pf::pack_bf16(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
-                            w.y = pf::pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
-                            w.z = pf::pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
-                            w.w = pf::pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
-                            *reinterpret_cast<uint4*>(orow + c + j) = w;
-                        }
+                    for (int j = 0; j < 16; j += 8) {
+                        uint4 w;
+                        w.x = pf::pack_bf16(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+                        w.y = pf::pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+                        w.z = pf::pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+                        w.w = pf::pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+                        *reinterpret_cast<uint4*>(stage + (size_t)r * (HD * 2) + ((((c + j) >> 3) ^ (r & 7)) << 4)) = w;
                     }
+                }
+            }
+            // all rows are staged (the exchange barrier once more, as for a tile after the sums)
+            warp_arrive(bar(ROW_X + ((n_tiles + 1) & 1)), lane);
+            ok = mbar_wait(bar(ROW_X + ((n_tiles + 1) & 1)), ((n_tiles + 1) >> 1) & 1, fail_flag);
+            if (!ok) atomicExch(&failed, 1);
+        }
+        if (ok) {
+            const int rows = min(BM, len - q0);
+            if (shared_tile) {
+                constexpr int PIECES = HD / 4;        // pieces of 4 floats in a row
+                float* pbase = partial + (((size_t)gtile * nq + head) * parts + part) * BM * pf::PART_ROW;
+                for (int idx = threadIdx.x; idx < rows * PIECES; idx += SOFTMAX_WARPS * 32) {
+                    const int rr = idx / PIECES, pc = idx % PIECES;
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + (size_t)rr * (HD * 4) + ((pc ^ (rr & 7)) << 4));
+                    float* dst = pbase + (size_t)rr * pf::PART_ROW + 2 + pc * 4;    // 8-byte aligned
+                    *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+                    *reinterpret_cast<uint2*>(dst + 2) = make_uint2(v.z, v.w);
+                }
+            } else {
+                constexpr int PIECES = HD / 8;        // pieces of 8 bfloat16 in a row
+                bf16* obase = out + (size_t)(first + q0) * nq * HD + (size_t)head * HD;
+                for (int idx = threadIdx.x; idx < rows * PIECES; idx += SOFTMAX_WARPS * 32) {
+                    const int rr = idx / PIECES, pc = idx % PIECES;
+                    *reinterpret_cast<uint4*>(obase + (size_t)rr * nq * HD + pc * 8) =
+                        *reinterpret_cast<const uint4*>(stage + (size_t)rr * (HD * 2) + ((pc ^ (rr & 7)) << 4));
                 }
             }
         }
@@ -482,7 +557,7 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int 
 
 int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const int* seq_first_row, const int* seq_len,
                         int n_seq, int n_tiles_bound, void* out, int nq, int nkv, int q_row_heads, int kv_row_heads,
-                        int kv_k_head0, float scale, float cap, int window, int parts, int split_min, float* partial,
+                        int kv_k_head0, float scale, float cap, int window, int parts, int piece, float* partial,
                         cudaStream_t stream) {
     if (!pt::SUPPORTED) return -1;
     CUtensorMap mq, mkv;
@@ -491,15 +566,19 @@ int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const 
         return -1;                                    // no encoder, or operands it refuses: the other kernel runs
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(pt::attn_prefill_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(pt::attn_prefill_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              pt::SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(pt::attn_prefill_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     pt::SMEM_BYTES);
         if (e != cudaSuccess) return fail("attn_prefill_tc05: shared memory of %d bytes refused: %s", pt::SMEM_BYTES,
                                           cudaGetErrorString(e));
         configured = true;
     }
-    return launch_kernel("attn_prefill_tc05", pt::attn_prefill_tc05_kernel, dim3(nq, n_tiles_bound * parts), dim3(pt::THREADS),
-                         pt::SMEM_BYTES, stream, 1, mq, mkv, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, kv_k_head0,
-                         scale, cap, window, parts, split_min, partial);
+    auto kernel = cap > 0.f ? pt::attn_prefill_tc05_kernel<true> : pt::attn_prefill_tc05_kernel<false>;
+    return launch_kernel("attn_prefill_tc05", kernel, dim3(nq, n_tiles_bound * parts), dim3(pt::THREADS), pt::SMEM_BYTES,
+                         stream, 1, mq, mkv, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, kv_k_head0, scale, cap,
+                         window, parts, piece, partial);
 }
 
 }  // namespace janis

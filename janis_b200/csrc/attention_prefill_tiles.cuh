@@ -55,13 +55,21 @@ __device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_fi
     n_tiles = (q_last - k_first) / BN + 1;
 }
 
+// CTAs that share a tile of queries with n_tiles key tiles: pieces of at most `piece` key tiles, but no more
+// than `parts` of them (1: the tile is one CTA's, which writes the output itself).  The attention kernels and
+// the merge kernel decide the same way.
+__host__ __device__ __forceinline__ int parts_of(int n_tiles, int parts, int piece) {
+    const int want = (n_tiles + piece - 1) / piece;
+    return parts <= 1 || want <= 1 ? 1 : (want < parts ? want : parts);
+}
+
 }  // namespace pf
 
 // The tcgen05 kernel of the same step (attention_prefill_tc05.cu): 0 launched, 1 failed (message set),
 // -1 this head size or these operands are not for it.
 int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const int* seq_first_row, const int* seq_len,
                         int n_seq, int n_tiles_bound, void* out, int nq, int nkv, int q_row_heads, int kv_row_heads,
-                        int kv_k_head0, float scale, float cap, int window, int parts, int split_min, float* partial,
+                        int kv_k_head0, float scale, float cap, int window, int parts, int piece, float* partial,
                         cudaStream_t stream);
 
 }  // namespace janis

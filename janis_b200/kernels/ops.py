@@ -85,6 +85,8 @@ def attention_lib(head_dim: int):
         lib.janis_attn_prefill_mma.argtypes = [P, P, I, P, P, I, I, P, I, I, I, I, I, F, F, I, P, c_longlong, P]
         lib.janis_attn_set_prefill_kernel.argtypes = [I]
         lib.janis_attn_set_prefill_kernel.restype = None
+        lib.janis_attn_set_prefill_piece.argtypes = [I]
+        lib.janis_attn_set_prefill_piece.restype = None
         lib.janis_attn_tc05_timeouts.restype = I
         lib.janis_attn_prefill_scratch.argtypes = [I, I]
         lib.janis_attn_prefill_scratch.restype = c_longlong
@@ -329,7 +331,7 @@ def matmul_bf16_to_f32(x, w, out):
 
 def attn_prefill_scratch_floats(n_tok: int, n_seq: int, nq: int, hd: int, dtype=torch.bfloat16) -> int:
     """Floats of scratch that attn_prefill wants for a step of n_tok tokens in n_seq sequences: a bfloat16
-    step with few tiles of queries shares each long tile between two CTAs, which meet through the scratch
+    step with few tiles of queries shares each long tile between up to four CTAs, which meet through the scratch
     (0: nothing is shared).  Without the scratch the step runs unshared."""
     if dtype != torch.bfloat16:
         return 0
@@ -407,6 +409,12 @@ def attn_set_prefill_kernel(hd: int, which: int = 1) -> None:
     """Choose the bfloat16 prompt kernel of the head size's library: 1 = tcgen05 with the accumulators in
     tensor memory where the head size allows it (a multiple of 64 up to 256; the default), 0 = mma.sync."""
     attention_lib(hd).janis_attn_set_prefill_kernel(int(which))
+
+
+def attn_set_prefill_piece(hd: int, piece: int = 0) -> None:
+    """Fix how many key tiles a piece of a shared tile of queries holds in the bfloat16 prompt kernels of the
+    head size's library (0: chosen from the step's size, the default).  For tests and tuning."""
+    attention_lib(hd).janis_attn_set_prefill_piece(int(piece))
 
 
 def attn_tc05_timeouts(hd: int) -> int:

@@ -336,6 +336,7 @@ def prefill_kernel(request):
     yield request.param
     for hd in list(ops()._attn):                # the libraries that are loaded: back to their default
         ops().attn_set_prefill_kernel(hd, 1)
+        ops().attn_set_prefill_piece(hd, 0)
 
 
 @pytest.mark.parametrize("nq,nkv,hd", ATTN_SHAPES + [(2, 1, 96), (2, 2, 112)])
@@ -391,13 +392,16 @@ def test_attn_prefill_of_a_few_tokens(nq, nkv, hd, lens, prefill_kernel):
 
 @pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 2, 64), (3, 1, 80), (2, 2, 128)])
 @pytest.mark.parametrize("window,cap", [(0, 0.0), (100, 30.0), (300, 50.0)])
-def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, prefill_kernel):
-    """Few tiles of queries: the long ones are shared by two CTAs that meet through scratch.  Sequences long
-    enough for tiles with many key tiles, a window that leaves some tiles unshared, a far key that must win,
-    and the same call without scratch."""
+@pytest.mark.parametrize("piece", [0, 1, 3])
+def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, piece, prefill_kernel):
+    """Few tiles of queries: the long ones are cut into pieces for two to four CTAs that meet through scratch.
+    Sequences long enough for tiles with many key tiles (2 to 11 of them: with pieces of 1, 3 and the automatic 4
+    every number of pieces occurs, in equal and unequal cuts), a window that leaves some tiles unshared, a far
+    key that must win, and the same call without scratch."""
     if prefill_kernel == 1 and (hd % 64 or hd > 256):
         pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
     ops().attn_set_prefill_kernel(hd, prefill_kernel)
+    ops().attn_set_prefill_piece(hd, piece)
     lens = [700, 129, 300, 1]
     T = sum(lens)
     first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
