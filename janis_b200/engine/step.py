@@ -10,7 +10,11 @@ Prompt steps with many tokens are cut at sequence borders into pieces of at
 most `max_step_tokens`; the pieces are independent, so nothing changes but the
 size of the scratch buffers.  Decode steps are replayed from CUDA graphs, one
 per (padded batch size, bound on the lengths); padding rows carry slot -1, touch
-no cache and change no other row.
+no cache and change no other row.  Short prompt steps, whose three hundred
+launches cost the host more time than the device needs for them, are replayed
+from graphs too, one per (padded token count, padded sequence count) once a
+shape has come twice; padding tokens belong to a padding sequence of slot -1 and
+length 0 that stands behind the real ones.
 
 The reference's forward takes one sequence, one offset, and returns the last
 position's logits (`qwen/model.go:346-349`, `gemma/gemma.go:196-213`).
@@ -50,8 +54,29 @@ def _bucket_len(n: int) -> int:
     return b
 
 
+_PROMPT_TOKEN_BUCKETS = (16, 32, 48, 64, 96, 128, 192, 256, 320, 384, 448, 512)
+
+
+def _bucket_prompt_tokens(n: int) -> int:
+    for b in _PROMPT_TOKEN_BUCKETS:
+        if n <= b:
+            return b
+    raise ValueError(n)
+
+
+def _bucket_prompt_seqs(n: int) -> int:
+    """Sequences of a graphed prompt step: the real ones and at least one padding sequence."""
+    b = 2
+    while b < n + 1:
+        b *= 2
+    return b
+
+
 class Stepper:
     MAX_GRAPH_BATCH = 256
+    PROMPT_GRAPH_TOKENS = _PROMPT_TOKEN_BUCKETS[-1]     # longer prompt steps keep the device busy past the host
+    PROMPT_GRAPH_SEQS = 32                              # padded sequence count of a graphed prompt step, at most
+    PROMPT_GRAPHS = 48                                  # graphs kept; the least recently used one goes first
 
     def __init__(self, model: DecoderModel, cache: ModelCache, rt: Runtime, max_step_tokens: int = 16384,
                  use_graphs: bool = True):
@@ -60,6 +85,13 @@ class Stepper:
         self.max_step_tokens = max(1, int(max_step_tokens))
         self.use_graphs = bool(use_graphs) and torch.device(rt.device).type == "cuda" and model.graph_safe
         self._graphs: dict[tuple[int, int], tuple] = {}
+        self._prompt_graphs: dict[tuple, tuple] = {}   # (padded tokens, padded sequences, logits wanted) -> (graph,)
+        self._prompt_seen: set[tuple] = set()          # shapes that have come once
+        self._prompt_meta = None
+        self._prompt_logits = None
+        self._prompt_stage: list = []
+        self._prompt_stage_done: list = []
+        self._prompt_stage_next = 0
         self._decode_meta = None
         self._decode_logits = None
         self._stage: list = []
@@ -145,6 +177,13 @@ class Stepper:
         n_seq = len(entries)
         lens = [len(e.tokens) for e in entries]
         T = sum(lens)
+        if self.use_graphs and T <= self.PROMPT_GRAPH_TOKENS and n_seq < self.PROMPT_GRAPH_SEQS:
+            n_want = 0 if out is None else out.shape[0]
+            key = (_bucket_prompt_tokens(T), _bucket_prompt_seqs(n_seq), n_want > 0)
+            if n_want <= key[1]:
+                if key in self._prompt_seen:
+                    return self._prefill_graphed(entries, lens, out, key)
+                self._prompt_seen.add(key)        # a shape that never comes back is not worth a capture
         first = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
         tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
         tok_pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
@@ -175,6 +214,91 @@ class Stepper:
             self.model.logits(ctx, h, rows_dev, len(rows), out)
         for e, n in zip(entries, lens):
             self.cache.advance(e.slot, n)
+
+    def _prefill_graphed(self, entries, lens, out, key) -> None:
+        """A short prompt step through a CUDA graph of its padded shape.  The tables live in one static device
+        buffer laid out for the largest shape; padding tokens (token 0, position 0) belong to sequence n_seq,
+        which like the sequences after it has slot -1, length 0 and its first row at the end of the real
+        tokens; wanted rows beyond the real ones point at row 0 and their logits are dropped."""
+        Tb, Sb, wanted = key
+        Tmax, Smax = self.PROMPT_GRAPH_TOKENS, self.PROMPT_GRAPH_SEQS
+        n_seq, T = len(entries), sum(lens)
+        dev = self.rt.device
+        if self._prompt_meta is None:
+            self._prompt_meta = torch.zeros(3 * Tmax + 5 * Smax, dtype=torch.int32, device=dev)
+        if self._prompt_logits is None or self._prompt_logits.shape[0] < Sb:
+            self._prompt_graphs.clear()                 # graphs hold the address of the old buffer
+            self._prompt_logits = torch.empty((Sb, self.model.vocab), dtype=torch.float32, device=dev)
+        host = np.zeros(3 * Tmax + 5 * Smax, dtype=np.int32)
+        first = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+        host[0:T] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        host[Tmax:Tmax + T] = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+        host[2 * Tmax:2 * Tmax + T] = np.repeat(np.arange(n_seq, dtype=np.int32), lens)
+        host[2 * Tmax + T:2 * Tmax + Tb] = n_seq
+        o = 3 * Tmax
+        host[o:o + Smax] = -1                            # slots
+        host[o:o + n_seq] = [e.slot for e in entries]
+        host[o + 2 * Smax:o + 2 * Smax + n_seq] = lens   # lengths after the step (before it: 0)
+        host[o + 3 * Smax:o + 4 * Smax] = T              # first rows
+        host[o + 3 * Smax:o + 3 * Smax + n_seq] = first
+        n_want = 0 if out is None else out.shape[0]
+        if n_want:
+            host[o + 4 * Smax:o + 4 * Smax + n_want] = np.concatenate(
+                [first[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries)])
+        for e, n in zip(entries, lens):
+            self.cache.reserve(e.slot, n)
+        self.cache.sync()
+        meta = self._prompt_meta
+        self._upload_prompt(host)
+        ctx = StepContext(rt=self.rt, ws=self.ws, mode="prefill", n_tok=Tb, n_seq=Sb, tokens=meta[0:Tb],
+                          tok_pos=meta[Tmax:Tmax + Tb], tok_seq=meta[2 * Tmax:2 * Tmax + Tb],
+                          seq_slot=meta[o:o + Sb], seq_start=meta[o + Smax:o + Smax + Sb],
+                          seq_end=meta[o + 2 * Smax:o + 2 * Smax + Sb],
+                          seq_first_row=meta[o + 3 * Smax:o + 3 * Smax + Sb], len_bound=Tb)
+        rows = meta[o + 4 * Smax:o + 4 * Smax + Sb]
+        logits = self._prompt_logits[:Sb]
+
+        def body():
+            h = self.model.forward(ctx, self.cache)
+            if wanted:
+                self.model.logits(ctx, h, rows, Sb, logits)
+
+        hit = self._prompt_graphs.pop(key, None)
+        if hit is None:
+            body()                                      # once kernel by kernel: every buffer exists afterwards
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            self.ws.begin_capture()
+            try:
+                with torch.cuda.graph(g):
+                    body()
+            finally:
+                self.ws.end_capture()
+            hit = (g,)
+            if len(self._prompt_graphs) >= self.PROMPT_GRAPHS:
+                self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
+        else:
+            hit[0].replay()
+        self._prompt_graphs[key] = hit                  # most recently used last
+        for e, n in zip(entries, lens):
+            self.cache.advance(e.slot, n)
+        if n_want:
+            out.copy_(logits[:n_want])
+
+    def _upload_prompt(self, host: np.ndarray) -> None:
+        """Host tables of a graphed prompt step -> the static device tables, through pinned staging buffers."""
+        if not self._prompt_stage:
+            self._prompt_stage = [torch.empty(host.shape[0], dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._prompt_stage_done = [None] * len(self._prompt_stage)
+        i = self._prompt_stage_next
+        self._prompt_stage_next = (i + 1) % len(self._prompt_stage)
+        if self._prompt_stage_done[i] is not None:
+            self._prompt_stage_done[i].synchronize()
+        self._prompt_stage[i].numpy()[...] = host
+        self._prompt_meta.copy_(self._prompt_stage[i], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._prompt_stage_done[i] = ev
 
     # ------------------------------------------------------------------
     def _decode(self, entries, copy: bool, tokens_on_device: bool = False) -> torch.Tensor | None:

@@ -71,8 +71,15 @@ class Workspace:
         self.frozen = False
         self._in_graph: set[str] = set()          # names whose current buffer a CUDA graph has recorded
         self._retired: list[torch.Tensor] = []    # outgrown buffers that a graph still writes to
+        self._views: dict[str, tuple] = {}        # name -> (shape, buffer, view): the view handed out last
 
     def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
+        last = self._views.get(name)
+        if last is not None and last[0] == shape and last[1].dtype == dtype and last[1] is self._bufs.get(name):
+            if self.frozen:
+                self._in_graph.add(name)
+            return last[2]                        # the same view as last step: no tensor objects to build
         n = 1
         for s in shape:
             n *= int(s)
@@ -87,7 +94,9 @@ class Workspace:
             self._bufs[name] = cur
         if self.frozen:
             self._in_graph.add(name)
-        return cur[:n].view(*shape)
+        view = cur[:n].view(*shape)
+        self._views[name] = (shape, cur, view)
+        return view
 
     def begin_capture(self) -> None:
         self.frozen = True
@@ -120,7 +129,9 @@ class StepContext:
 
 class Part:
     # False for a part whose step cannot be recorded into a CUDA graph (it synchronises, allocates by
-    # data-dependent sizes, or copies from the host); decode steps are then launched kernel by kernel.
+    # data-dependent sizes, or copies from the host); steps are then launched kernel by kernel.  A part that
+    # leaves it True meets padding in recorded steps, decode and prompt steps alike: sequences whose slot is
+    # negative (and the tokens that name them) must be stored nowhere and must change no other row.
     graph_safe = True
 
     def tensor_specs(self) -> dict[str, TensorSpec]:

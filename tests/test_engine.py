@@ -177,3 +177,44 @@ def test_prompts_of_several_tiles_at_head_size_64(dtype, engines, plain_models):
     alone = run_requests(eng, [reqs[0]], [330])[0]
     assert_logits(alone, plain_logits(plain_models, key, reqs[0]), dtype, f"{key} alone")
     assert eng.cache.live_slots() == []
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["A_hot", "B_hot", "C_hot"])
+def test_short_prompt_steps_replayed_from_graphs(key, dtype, model_dirs, plain_models):
+    """Short prompt steps whose padded shape has come before run from a CUDA graph: the first batch kernel by
+    kernel, the second recorded, the others replayed.  Unequal prompts (some longer than the window), a batch
+    that fills its padded shape exactly, padding tokens and padding sequences, the logits at the prompts' ends
+    and at the tokens decoded after them over the same cache, slots used again; and a step that wants no logits."""
+    from janis_b200 import StepEntry
+    eng = make_engine(model_dirs[key], dtype, "cuda", max_tokens=2048)
+    V = vocab_of(key)
+    batches = [(30, 75, 12), (41, 50, 33), (64, 64), (1, 100, 20), (3, 2, 1), (120,)]
+    for b, lens in enumerate(batches):
+        reqs = [random_tokens(V, n + 3, 400 + 10 * b + i) for i, n in enumerate(lens)]
+        want = [plain_logits(plain_models, key, r) for r in reqs]
+        slots = [eng.alloc_slot() for _ in reqs]
+        out = eng.step([StepEntry(s, r[:n], [n - 1]) for s, r, n in zip(slots, reqs, lens)])
+        for i, n in enumerate(lens):
+            assert_logits(out[i:i + 1], want[i][n - 1:n], dtype, f"{key} batch {b} prompt {i}")
+        for t in range(3):
+            out = eng.step([StepEntry(s, [r[n + t]], [0]) for s, r, n in zip(slots, reqs, lens)])
+            for i, n in enumerate(lens):
+                assert_logits(out[i:i + 1], want[i][n + t:n + t + 1], dtype, f"{key} batch {b} request {i} token {t}")
+        for s in slots:
+            eng.free_slot(s)
+        eng.cache.audit()
+    # the first four batches share a padded shape: one graph; the last two have one each, seen once: none
+    assert len(eng.stepper._prompt_graphs) == 1
+    # a prompt step that wants nothing, twice (the second is recorded), then a token over what it left
+    req = random_tokens(V, 50, 477)
+    want = plain_logits(plain_models, key, req)
+    for _ in range(3):
+        slot = eng.alloc_slot()
+        assert eng.step([StepEntry(slot, req[:49], [])]) is None
+        out = eng.step([StepEntry(slot, [req[49]], [0])])
+        assert_logits(out, want[49:50], dtype, f"{key} after a prompt step without logits")
+        eng.free_slot(slot)
+    assert len(eng.stepper._prompt_graphs) == 2
+    eng.close()
