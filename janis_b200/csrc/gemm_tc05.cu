@@ -5,14 +5,15 @@
 // batch rows, padded to a multiple of 16, are its N side, so one instruction multiplies a [128 x 16]
 // slice of W with all batch rows and the accumulator [128 x Mpad] float lives in tensor memory.
 //   * TMA (cp.async.bulk.tensor, 128-byte swizzle) brings [128 x 64] tiles of W and [Mpad x 64] tiles
-//     of x into a ring of stages; an mbarrier per stage counts the bytes in.
+//     of x into a ring of stages; an mbarrier per stage counts the bytes in.  The ring is as deep as the
+//     shared memory of an SM allows for the CTAs that share it: 3 stages when three CTAs do, 9 for one alone.
 //   * One thread issues four tcgen05.mma (K = 16 each) per stage and a tcgen05.commit that frees the
 //     stage when they have read it.
 //   * When N is small, a thread-block cluster of up to 8 CTAs splits K; the CTAs' partial sums are added
 //     in rank order through distributed shared memory, so the result does not depend on timing.
 //   * Epilogue: tcgen05.ld gives each thread the Mpad sums of its row of W; none / gated activation
-//     (rows alternate 8 gate, 8 up: the partner sits 8 lanes away) / cap * tanh(v / cap); the store is
-//     transposed back to [M, N].
+//     (rows alternate 8 gate, 8 up: the partner sits 8 lanes away) / cap * tanh(v / cap); the sums are
+//     turned through shared memory and leave as whole rows of out[M, N].
 // Every wait is bounded: on a timeout the CTA records it (janis_tc05_timeouts), frees its tensor memory
 // and returns.  No TMA load here uses cluster multicast.
 #include <cooperative_groups.h>
@@ -31,17 +32,15 @@ namespace tc {
 
 constexpr int BLOCK_N = 128;          // rows of W per CTA (TMEM lanes)
 constexpr int BLOCK_K = 64;           // bf16 elements per stage along K: one 128-byte swizzle row
-#ifndef JANIS_TC05_STAGES
-#define JANIS_TC05_STAGES 3      // 73 KB a CTA: two CTAs share an SM, one's epilogue under the other's loads
-#endif
-constexpr int STAGES = JANIS_TC05_STAGES;
+constexpr int MIN_STAGES = 3;         // 73 KB a CTA: three CTAs share an SM, one's epilogue under the others' loads
+constexpr int MAX_STAGES = 9;         // 217 KB: a CTA that has its SM to itself keeps nine tiles of W on the way
 constexpr int MAX_M = 64;
 constexpr int THREADS = 128;
 constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;                    // 16 KB
 constexpr int B_BYTES_MAX = MAX_M * BLOCK_K * 2;                  // 8 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES_MAX;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + room to align to 1024
-static_assert(sizeof(float) * BLOCK_N * MAX_M <= STAGES * STAGE_BYTES, "the partial sums reuse the stages");
+constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024; }   // + room to align to 1024
+static_assert(sizeof(float) * BLOCK_N * MAX_M <= MIN_STAGES * STAGE_BYTES, "the sums leave through the idle stages");
 
 enum { EPI_NONE = 0, EPI_GATED_GELU = 1, EPI_SOFTCAP = 2, EPI_GATED_SILU = 3 };
 
@@ -100,9 +99,9 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 template <typename TO>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 TO* __restrict__ out, int M, int Mpad, int N, int K, int split, int epi, float cap) {
+                 TO* __restrict__ out, int M, int Mpad, int N, int K, int split, int epi, float cap, int STAGES, int vec_ok) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ __align__(8) unsigned long long bars[2 * MAX_STAGES + 1];
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -150,28 +149,32 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         grid_dependency_wait();
         for (int i = 0; i < pre; ++i)
             tma_load_2d(stage0 + i * STAGE_BYTES + A_BYTES, &map_x, (rank + i * split) * BLOCK_K, 0, bar_full + 8 * i);
+        int s = pre == STAGES ? 0 : pre;                              // stage of tile i and how often it has been filled
+        uint32_t fills = pre == STAGES ? 1 : 0;
         for (int i = pre; i < nk; ++i) {
-            const int s = i % STAGES;
-            if (i >= STAGES && !mbar_wait(bar_empty + 8 * s, ((i / STAGES) - 1) & 1)) { atomicExch(&failed, 1); break; }
+            if (fills > 0 && !mbar_wait(bar_empty + 8 * s, (fills - 1) & 1)) { atomicExch(&failed, 1); break; }
             const uint32_t a = stage0 + s * STAGE_BYTES, b = a + A_BYTES;
             const int k0 = (rank + i * split) * BLOCK_K;
             mbar_expect_tx(bar_full + 8 * s, A_BYTES + b_bytes);
             tma_load_2d(a, &map_w, k0, n0, bar_full + 8 * s);
             tma_load_2d(b, &map_x, k0, 0, bar_full + 8 * s);
+            if (++s == STAGES) { s = 0; ++fills; }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- the thread that issues the products
         grid_dependency_wait();
         const uint32_t idesc = instr_desc(BLOCK_N, Mpad);
+        int s = 0;
+        uint32_t round = 0;
         for (int i = 0; i < nk; ++i) {
-            const int s = i % STAGES;
-            if (!mbar_wait(bar_full + 8 * s, (i / STAGES) & 1)) { atomicExch(&failed, 1); break; }
+            if (!mbar_wait(bar_full + 8 * s, round & 1)) { atomicExch(&failed, 1); break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t a = stage0 + s * STAGE_BYTES, b = a + A_BYTES;
 #pragma unroll
             for (int kk = 0; kk < BLOCK_K / 16; ++kk)                 // 32 bytes further along the swizzled row
                 umma(tmem, smem_desc(a + kk * 32), smem_desc(b + kk * 32), idesc, (i > 0 || kk > 0) ? 1u : 0u);
             umma_commit(bar_empty + 8 * s);                           // the stage is free once these have read it
+            if (++s == STAGES) { s = 0; ++round; }
         }
         umma_commit(bar_done);                                        // all products of this CTA have finished
     }
@@ -230,32 +233,62 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
     if (!ok) return;
 
-    // ---- epilogue: thread = row n of W; transposed store to out[m][n]
-    const int n = n0 + threadIdx.x;
-    if (epi == EPI_GATED_GELU || epi == EPI_GATED_SILU) {
-        const int I = N / 2;
-        const bool gate_row = (threadIdx.x & 15) < 8;                  // rows alternate 8 gate, 8 up
-        const int j = (n / 16) * 8 + (n & 7);
+    // ---- epilogue: thread = row n of W holds out[0 .. M)[n].  Stored from here a warp would write 2 bytes to each
+    // of 32 places per instruction (8.6 us a CTA, measured); the sums are turned through the idle stages instead
+    // and leave as whole rows of the tile.
+    float* turned = reinterpret_cast<float*>(stage_ptr);              // [M][cols]
+    const bool gated = epi == EPI_GATED_GELU || epi == EPI_GATED_SILU;
+    const int cols = gated ? BLOCK_N / 2 : BLOCK_N;                   // output columns of this tile
+    const int n_cols = gated ? N / 2 : N, c0 = gated ? n0 / 2 : n0;   // columns of out, and the tile's first
+    if (gated) {
+        const bool gate_row = (threadIdx.x & 15) < 8;                 // rows alternate 8 gate, 8 up
+        const int j = (threadIdx.x / 16) * 8 + (threadIdx.x & 7);
 #pragma unroll
         for (int m = 0; m < MAX_M; ++m) {
             if (m < Mpad) {
                 const float up = __shfl_down_sync(0xffffffffu, acc[m], 8);
-                if (gate_row && m < M && n < N) {
+                if (gate_row && m < M) {
                     const float g = acc[m];
-                    const float a = epi == EPI_GATED_GELU ? gelu_tanh(g) : g / (1.0f + expf(-g));
-                    out[(size_t)m * I + j] = from_float<TO>(a * up);
+                    const float act = epi == EPI_GATED_GELU ? gelu_tanh(g) : g / (1.0f + expf(-g));
+                    turned[m * cols + j] = act * up;
                 }
             }
         }
-        return;
-    }
-    if (n >= N) return;
+    } else {
 #pragma unroll
-    for (int m = 0; m < MAX_M; ++m) {
-        if (m < M) {
-            float v = acc[m];
-            if (epi == EPI_SOFTCAP && cap > 0.f) v = cap * tanhf(v / cap);
-            out[(size_t)m * N + n] = from_float<TO>(v);
+        for (int m = 0; m < MAX_M; ++m) {
+            if (m < M) {
+                float v = acc[m];
+                if (epi == EPI_SOFTCAP && cap > 0.f) v = cap * tanhf(v / cap);
+                turned[m * cols + threadIdx.x] = v;
+            }
+        }
+    }
+    __syncthreads();
+    constexpr int VEC = 16 / sizeof(TO);                              // values of a 16-byte store
+    if (vec_ok) {
+        const int per_row = cols / VEC;
+        for (int idx = threadIdx.x; idx < M * per_row; idx += THREADS) {
+            const int m = idx / per_row, c = (idx % per_row) * VEC;
+            if (c0 + c >= n_cols) continue;                           // n_cols is a multiple of VEC here
+            const float* src = turned + m * cols + c;
+            TO* dst = out + (size_t)m * n_cols + c0 + c;
+            if constexpr (sizeof(TO) == 2) {
+                const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(lo.x, lo.y), p1 = __floats2bfloat162_rn(lo.z, lo.w);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(hi.x, hi.y), p3 = __floats2bfloat162_rn(hi.z, hi.w);
+                uint4 w;
+                w.x = *reinterpret_cast<uint32_t*>(&p0); w.y = *reinterpret_cast<uint32_t*>(&p1);
+                w.z = *reinterpret_cast<uint32_t*>(&p2); w.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(dst) = w;
+            } else {
+                *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < M * cols; idx += THREADS) {
+            const int m = idx / cols, c = idx % cols;
+            if (c0 + c < n_cols) out[(size_t)m * n_cols + c0 + c] = from_float<TO>(turned[m * cols + c]);
         }
     }
 }
@@ -310,6 +343,23 @@ static const CUtensorMap* cached_map(const void* ptr, int rows, int K, int box_r
 
 using namespace janis;
 
+static int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+static int g_tc05_stages = 0;       // 0: chosen from the number of CTAs per SM
+
+// Fixes the depth of the ring of stages (3 to 9; 0: automatic again).  For tests and tuning.
+JANIS_EXPORT void janis_tc05_set_stages(int stages) {
+    g_tc05_stages = stages <= 0 ? 0 : (stages < tc::MIN_STAGES ? tc::MIN_STAGES : (stages > tc::MAX_STAGES ? tc::MAX_STAGES : stages));
+}
+
 JANIS_EXPORT int janis_tc05_timeouts() {
     int n = -1;
     if (cudaMemcpyFromSymbol(&n, tc::g_timeouts, sizeof(int)) != cudaSuccess) return -1;
@@ -333,8 +383,11 @@ JANIS_EXPORT int janis_gemm_tc05(const void* x, const void* W, void* out, int ou
     const int Mpad = (M + 15) / 16 * 16;
     const int tiles = (N + tc::BLOCK_N - 1) / tc::BLOCK_N, nk = (K + tc::BLOCK_K - 1) / tc::BLOCK_K;
     if (split == 0) {
+        // few tiles of W: K is shared by a cluster as long as each CTA keeps 16 tiles of it (measured in replayed
+        // graphs: N = 4096 and 2304 with K = 2304 and 2048 are fastest with 2 CTAs, N = 2304 with K = 9216 with 4;
+        // clusters of 8 were slower everywhere)
         split = 1;
-        while (split < 8 && tiles * split < 120 && nk >= split * 2 * 4) split *= 2;
+        while (split < 4 && tiles * split * 2 <= sm_count() && nk >= split * 2 * 16) split *= 2;
     }
     const CUtensorMap* mw = tc::cached_map(W, N, K, tc::BLOCK_N);
     const CUtensorMap* mx = tc::cached_map(x, M, K, Mpad);
@@ -342,15 +395,26 @@ JANIS_EXPORT int janis_gemm_tc05(const void* x, const void* W, void* out, int ou
     static bool configured[2] = {false, false};
     const int oi = out_dtype == JANIS_BF16 ? 0 : 1;
     if (!configured[oi]) {
-        cudaError_t e = oi == 0 ? cudaFuncSetAttribute(tc::gemm_tc05_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES)
-                                : cudaFuncSetAttribute(tc::gemm_tc05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
-        if (e != cudaSuccess) return fail("gemm_tc05: shared memory of %d bytes refused: %s", tc::SMEM_BYTES, cudaGetErrorString(e));
+        const int most = tc::smem_bytes(tc::MAX_STAGES);
+        cudaError_t e = oi == 0 ? cudaFuncSetAttribute(tc::gemm_tc05_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most)
+                                : cudaFuncSetAttribute(tc::gemm_tc05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        if (e != cudaSuccess) return fail("gemm_tc05: shared memory of %d bytes refused: %s", most, cudaGetErrorString(e));
         configured[oi] = true;
     }
+    // The ring is as deep as the SM's shared memory allows for the CTAs that share it: three CTAs with 3 stages
+    // each when there are that many, two with 4, or one with 9 (a CTA alone with 3 stages had one tile of W arrive
+    // every 0.6 us: a third of the SM's share of the memory bandwidth).
+    const int per_sm = (tiles * split + sm_count() - 1) / sm_count();
+    int stages = per_sm >= 3 ? tc::MIN_STAGES : (per_sm == 2 ? 4 : tc::MAX_STAGES);
+    if (split > 1 && stages > 4) stages = 4;    // clusters of CTAs with most of an SM's shared memory each are placed slowly
+    if (g_tc05_stages > 0) stages = g_tc05_stages;
+    const int n_cols = (epi == tc::EPI_GATED_GELU || epi == tc::EPI_GATED_SILU) ? N / 2 : N;
+    const int vec = out_dtype == JANIS_BF16 ? 8 : 4;
+    const int vec_ok = (n_cols % vec == 0 && ((uintptr_t)out & 15) == 0) ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * split);
     cfg.blockDim = dim3(tc::THREADS);
-    cfg.dynamicSmemBytes = tc::SMEM_BYTES;
+    cfg.dynamicSmemBytes = tc::smem_bytes(stages);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -366,9 +430,9 @@ JANIS_EXPORT int janis_gemm_tc05(const void* x, const void* W, void* out, int ou
     }
     cudaError_t e;
     if (oi == 0)
-        e = cudaLaunchKernelEx(&cfg, tc::gemm_tc05_kernel<bf16>, *mw, *mx, (bf16*)out, M, Mpad, N, K, split, epi, cap);
+        e = cudaLaunchKernelEx(&cfg, tc::gemm_tc05_kernel<bf16>, *mw, *mx, (bf16*)out, M, Mpad, N, K, split, epi, cap, stages, vec_ok);
     else
-        e = cudaLaunchKernelEx(&cfg, tc::gemm_tc05_kernel<float>, *mw, *mx, (float*)out, M, Mpad, N, K, split, epi, cap);
+        e = cudaLaunchKernelEx(&cfg, tc::gemm_tc05_kernel<float>, *mw, *mx, (float*)out, M, Mpad, N, K, split, epi, cap, stages, vec_ok);
     if (e != cudaSuccess) return fail("gemm_tc05: launch failed: %s", cudaGetErrorString(e));
     return launched("gemm_tc05");
 }

@@ -60,6 +60,8 @@ def core():
         lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
         lib.janis_gemm_tc05.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
         lib.janis_tc05_timeouts.restype = I
+        lib.janis_tc05_set_stages.argtypes = [I]
+        lib.janis_tc05_set_stages.restype = None
         lib.janis_argmax.argtypes = [P, P, I, I, P]
         lib.janis_sample.argtypes = [P, P, P, I, I, F, F, c_ulonglong, P, P, P]
         lib.janis_repeat_penalty.argtypes = [P, P, I, I, I, F, P]
@@ -315,6 +317,12 @@ def gemm_tc05(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0, split: int 
                                     _t(out, "out", _FLOATS, (M, n_out)), _DT[out.dtype], M, N, K, epilogue,
                                     float(cap), int(split), _stream()))
     return out
+
+
+def tc05_set_stages(stages: int = 0) -> None:
+    """Fix the depth of the tcgen05 product's ring of stages (3 to 9; 0: chosen from the CTAs per SM, the default).
+    For tests and tuning."""
+    core().janis_tc05_set_stages(int(stages))
 
 
 def tc05_timeouts() -> int:

@@ -56,3 +56,17 @@ def test_epilogues(epi, M, N, K):
         pytest.skip("gated rows come in groups of 16")
     check(M, N, K, epi, 0)
     check(M, N, K, epi, 0, out_dtype=torch.bfloat16)
+
+
+@pytest.mark.parametrize("stages", [3, 4, 9])
+@pytest.mark.parametrize("M,N,K,epi", [(64, 2304, 2048, 0), (17, 1002, 328, 0), (33, 1002, 328, 2), (40, 2000, 1032, 1),
+                                       (5, 18, 8, 0)])
+def test_depth_of_the_ring_and_row_stores(stages, M, N, K, epi):
+    """Every depth of the ring of stages (more stages than K has tiles too), outputs whose rows allow 16-byte
+    stores and outputs whose rows do not (N = 1002, 18)."""
+    ops().tc05_set_stages(stages)
+    try:
+        check(M, N, K, epi, 1)
+        check(M, N, K, epi, 1, out_dtype=torch.bfloat16)
+    finally:
+        ops().tc05_set_stages(0)
