@@ -71,6 +71,14 @@ __device__ __forceinline__ void grid_dependents_launch() {
 #endif
 }
 
+// The rotation of a rotary pair (a, b) by the angle whose sine and cosine are (s, c), with the roundings spelled
+// out: left to the compiler, a * c - b * s contracts to one of two fused forms that differ in the last bit, and
+// the kernels that rotate (the encoding kernels, the fused decode projection) must agree bit for bit.
+__device__ __forceinline__ void rotate_pair(float a, float b, float s, float c, float& lo, float& hi) {
+    lo = __fmaf_rn(a, c, -__fmul_rn(b, s));
+    hi = __fmaf_rn(a, s, __fmul_rn(b, c));
+}
+
 // one switch per library (the wrapper sets it in each): 0 launches plainly
 inline int& overlap_launches() {
     static int on = 1;

@@ -294,7 +294,9 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
                 float s = s0, c = c0;
                 if (i != i0) sincosf((float)pos * inv_freq[i], &s, &c);
                 const float a = to_float(p[i]), b = to_float(p[i + half]);
-                const T lo = from_float<T>(a * c - b * s), hi = from_float<T>(a * s + b * c);
+                float lo_f, hi_f;
+                rotate_pair(a, b, s, c, lo_f, hi_f);
+                const T lo = from_float<T>(lo_f), hi = from_float<T>(hi_f);
                 p[i] = lo;
                 p[i + half] = hi;
                 if (dst) { dst[i] = lo; dst[i + half] = hi; }
@@ -361,8 +363,7 @@ rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ tok_pos, cons
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float a = lo[e], b = hi[e];
-                lo[e] = a * cs[e] - b * sn[e];
-                hi[e] = a * sn[e] + b * cs[e];
+                rotate_pair(a, b, sn[e], cs[e], lo[e], hi[e]);
             }
             store8(p, lo);
             store8(p + half, hi);

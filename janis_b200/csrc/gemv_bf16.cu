@@ -17,6 +17,12 @@
 // Epilogues: none; gated activation over rows of W that alternate 8 gate rows and
 // 8 up rows (one mma tile then holds matching pairs); cap * tanh(v / cap).
 // Accumulation is float; the output is bfloat16 or float.  K must be a multiple of 8.
+//
+// The q/k/v projection of a decode step has a variant of its own (ROPE): a tile takes 8 rows of the first half
+// of a head and the 8 rows half a head further on, so that one mma tile holds the pairs that the rotary encoding
+// rotates; the epilogue rounds the sums to bfloat16 as the plain product would, rotates q and k by the angle of
+// the token's position, writes q to its rows and k and v straight into the paged cache: the projection, the
+// encoding and the cache write of a decode step are one kernel.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -43,6 +49,20 @@ constexpr int GEMV_WARPS = 8;        // warps of a CTA that split K (4 when N al
 
 enum { EPI_NONE = 0, EPI_GATED_GELU = 1, EPI_SOFTCAP = 2, EPI_GATED_SILU = 3 };
 
+// What the ROPE variant needs beside the product: the step's tables, the inverse frequencies and one cache line.
+struct RopeStore {
+    const int* tok_pos;        // [M] position of each row's token
+    const int* tok_seq;        // [M] its sequence in the step
+    const int* seq_slot;       // [n_seq] cache slot, < 0: padding (rotated, stored nowhere)
+    const int* seq_end;        // [n_seq] tokens cached after the step
+    const float* inv_freq;     // [hd / 2]
+    bf16* kpool;               // [pages, nkv, PAGE, hd]; null: the rows hold queries alone
+    bf16* vpool;
+    const int* page_table;     // [slots, table_stride]
+    int table_stride, ring_len, nq, nkv, hd;
+    int row_heads;             // heads in a row of the output that takes the queries (nq, or nq + 2 nkv)
+};
+
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -60,10 +80,10 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read once: do 
     return v;
 }
 
-template <int MT, int U, int CL, int NW, typename TO>
+template <int MT, int U, int CL, int NW, typename TO, bool ROPE = false>
 __global__ void __launch_bounds__(NW * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __restrict__ out, int M, int N,
-                 int K, int epi, float cap) {
+                 int K, int epi, float cap, const RopeStore rs) {
     __shared__ float red[NW][MT][32][4];
     __shared__ float cta_sum[MT * 128];        // this CTA's sum over its warps; read by CTA 0 of the cluster
     constexpr bool PUSH = JANIS_GEMV_PUSH && CL > 1 && MT <= 4;      // (the gather area of 8 row tiles does not fit)
@@ -75,7 +95,12 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
     const int tile = blockIdx.x / CL;
     const int r0 = tile * 16;
     // rows past the end read the last row; their results are never stored
-    const int row_lo = min(r0 + g, N - 1), row_hi = min(r0 + g + 8, N - 1);
+    int row_lo = min(r0 + g, N - 1), row_hi = min(r0 + g + 8, N - 1);
+    if (ROPE) {                                 // 8 rows of a head's first half and their partners half a head on
+        const int tiles_per_head = rs.hd >> 4;
+        row_lo = (tile / tiles_per_head) * rs.hd + (tile % tiles_per_head) * 8 + g;
+        row_hi = row_lo + (rs.hd >> 1);
+    }
     const bf16* wlo = W + (size_t)row_lo * K + t * 8;
     const bf16* whi = W + (size_t)row_hi * K + t * 8;
     const bf16* xr[MT];
@@ -108,6 +133,16 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
     };
     int kb = rank * NW + warp;
     grid_dependents_launch();
+    // ROPE: thread idx of the CTA that ends up with the sums has the pair (i, ln, p) of the epilogue below; its
+    // angle comes from the step's tables and the model's constants, so it is computed before the wait
+    float rope_sin = 0.f, rope_cos = 1.f;
+    if (ROPE && rank == 0 && threadIdx.x < MT * 64) {
+        const int i = threadIdx.x / 64, ln = (threadIdx.x / 2) % 32, p = threadIdx.x % 2;
+        const int m = i * 8 + (ln & 3) * 2 + p;
+        const int tiles_per_head = rs.hd >> 4;
+        const int head = tile / tiles_per_head, d = (tile % tiles_per_head) * 8 + (ln >> 2);
+        if (m < M && head < rs.nq + rs.nkv) sincosf((float)rs.tok_pos[m] * rs.inv_freq[d], &rope_sin, &rope_cos);
+    }
 #if JANIS_GEMV_BULK_AHEAD
     // The 16 rows of a tile lie one after another in memory: one bulk prefetch per CTA asks for this CTA's
     // share of them (into L2) while the kernel before this one still runs.
@@ -204,6 +239,50 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
     __syncthreads();
     const float (*tot)[32][4] = red[0];             // the tile's full sums
 
+    if (ROPE) {
+        // rows g of the tile are elements d of a head, rows g + 8 elements d + hd/2: a rotary pair per (token, g)
+        static_assert(!ROPE || MT * 64 <= NW * 32, "one pair per thread");
+        if (threadIdx.x < MT * 64) {
+            const int i = threadIdx.x / 64, ln = (threadIdx.x / 2) % 32, p = threadIdx.x % 2;
+            const int m = i * 8 + (ln & 3) * 2 + p;
+            if (m < M) {
+                const int hd = rs.hd, half = hd >> 1, tiles_per_head = hd >> 4;
+                const int head = tile / tiles_per_head, d = (tile % tiles_per_head) * 8 + (ln >> 2);
+                // rounded to bfloat16 first, as the plain product followed by the encoding kernel rounds them
+                float lo = __bfloat162float(__float2bfloat16(tot[i][ln][p]));
+                float hi = __bfloat162float(__float2bfloat16(tot[i][ln][p + 2]));
+                const bool is_v = head >= rs.nq + rs.nkv;
+                if (!is_v) {
+                    rotate_pair(lo, hi, rope_sin, rope_cos, lo, hi);
+                }
+                if (head < rs.nq) {
+                    bf16* q = reinterpret_cast<bf16*>(out) + ((size_t)m * rs.row_heads + head) * hd + d;
+                    q[0] = __float2bfloat16(lo);
+                    q[half] = __float2bfloat16(hi);
+                } else {
+                    const int seq = rs.tok_seq[m];
+                    const int slot = rs.seq_slot[seq];
+                    const int pos = rs.tok_pos[m];
+                    int idx = pos;
+                    bool keep = slot >= 0;
+                    if (keep && rs.ring_len > 0) {
+                        keep = pos >= rs.seq_end[seq] - rs.ring_len;
+                        idx = pos % rs.ring_len;
+                    }
+                    if (keep) {
+                        const int kvh = is_v ? head - rs.nq - rs.nkv : head - rs.nq;
+                        const int page = rs.page_table[(size_t)slot * rs.table_stride + idx / JANIS_PAGE];
+                        bf16* dst = (is_v ? rs.vpool : rs.kpool) +
+                                    (((size_t)page * rs.nkv + kvh) * JANIS_PAGE + idx % JANIS_PAGE) * hd + d;
+                        dst[0] = __float2bfloat16(lo);
+                        dst[half] = __float2bfloat16(hi);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
     if (epi == EPI_GATED_GELU || epi == EPI_GATED_SILU) {
         // rows g of the tile are gate rows, rows g + 8 the matching up rows
         const int I = N / 2;
@@ -239,32 +318,50 @@ static int g_gemv_small_ctas = 1;
 // tuning switch: 0 launches tall products with 8-warp CTAs too
 JANIS_EXPORT void janis_gemv_small_ctas(int on) { g_gemv_small_ctas = on ? 1 : 0; }
 
-template <int MT, int U, int CL, typename TO>
+template <int MT, int U, int CL, typename TO, bool ROPE = false>
 static int launch_one(const bf16* x, const bf16* W, TO* out, int M, int N, int K, int epi, float cap,
-                      cudaStream_t stream) {
+                      const RopeStore& rs, cudaStream_t stream) {
     const int tiles = (N + 15) / 16;
     if (CL == 1) {
         // many tiles: CTAs of 4 warps, so that more of them are resident and the last wave is short
-        if (tiles >= 1024 && g_gemv_small_ctas)
-            return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, 4, TO>, dim3(tiles), dim3(4 * 32), 0, stream, 1, x, W,
-                                 out, M, N, K, epi, cap);
-        return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, GEMV_WARPS, TO>, dim3(tiles), dim3(GEMV_WARPS * 32), 0,
-                             stream, 1, x, W, out, M, N, K, epi, cap);
+        if (tiles >= 1024 && g_gemv_small_ctas && !ROPE)
+            return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, 4, TO, false>, dim3(tiles), dim3(4 * 32), 0, stream, 1,
+                                 x, W, out, M, N, K, epi, cap, rs);
+        return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, GEMV_WARPS, TO, ROPE>, dim3(tiles), dim3(GEMV_WARPS * 32), 0,
+                             stream, 1, x, W, out, M, N, K, epi, cap, rs);
     }
-    return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, CL, GEMV_WARPS, TO>, dim3(tiles * CL), dim3(GEMV_WARPS * 32), 0,
-                         stream, CL, x, W, out, M, N, K, epi, cap);
+    return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, CL, GEMV_WARPS, TO, ROPE>, dim3(tiles * CL), dim3(GEMV_WARPS * 32),
+                         0, stream, CL, x, W, out, M, N, K, epi, cap, rs);
 }
 
 template <int MT, int U>
 static int launch_gemv(const bf16* x, const bf16* W, void* out, int out_dtype, int M, int N, int K, int epi,
                        float cap, int cluster, cudaStream_t stream) {
-#define JANIS_GEMV(CL)                                                                                          \
-    (out_dtype == JANIS_BF16 ? launch_one<MT, U, CL, bf16>(x, W, (bf16*)out, M, N, K, epi, cap, stream)          \
-                             : launch_one<MT, U, CL, float>(x, W, (float*)out, M, N, K, epi, cap, stream))
+    const RopeStore none = {};
+#define JANIS_GEMV(CL)                                                                                                \
+    (out_dtype == JANIS_BF16 ? launch_one<MT, U, CL, bf16>(x, W, (bf16*)out, M, N, K, epi, cap, none, stream)          \
+                             : launch_one<MT, U, CL, float>(x, W, (float*)out, M, N, K, epi, cap, none, stream))
     if (cluster >= 4) return JANIS_GEMV(4);
     if (cluster >= 2) return JANIS_GEMV(2);
     return JANIS_GEMV(1);
 #undef JANIS_GEMV
+}
+
+template <int MT, int U>
+static int launch_gemv_rope(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int cluster,
+                            const RopeStore& rs, cudaStream_t stream) {
+    if (cluster >= 4) return launch_one<MT, U, 4, bf16, true>(x, W, out, M, N, K, EPI_NONE, 0.f, rs, stream);
+    if (cluster >= 2) return launch_one<MT, U, 2, bf16, true>(x, W, out, M, N, K, EPI_NONE, 0.f, rs, stream);
+    return launch_one<MT, U, 1, bf16, true>(x, W, out, M, N, K, EPI_NONE, 0.f, rs, stream);
+}
+
+static int choose_cluster(int tiles, int nblk) {
+    // enough CTAs to fill the GPU a few times over, as long as every warp keeps some blocks of K.  Measured in a
+    // replayed graph at 2304 x 2048 / 4096 x 2304 / 2304 x 9216: clusters of 4 / 2 / 4 are fastest (5.1, 7.5, 11.5 us;
+    // the qkv product takes 9.2 us with 4, every one is slower with 8).
+    int cluster = 1;
+    while (cluster < 4 && tiles * cluster < 512 && nblk >= GEMV_WARPS * cluster * 2 * 2) cluster *= 2;
+    return cluster;
 }
 
 // x [M, K] bf16, W [N, K] bf16, out [M, N] (or [M, N/2] with a gated epilogue).
@@ -284,15 +381,37 @@ JANIS_EXPORT int janis_gemv_bf16(const void* x, const void* W, void* out, int ou
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
     const int tiles = (N + 15) / 16, nblk = (K + 31) / 32;
-    if (cluster == 0) {
-        // enough CTAs to fill the GPU a few times over, as long as every warp keeps some blocks of K.  Measured in a
-        // replayed graph at 2304 x 2048 / 4096 x 2304 / 2304 x 9216: clusters of 4 / 2 / 4 are fastest (5.1, 7.5, 11.5 us;
-        // the qkv product takes 9.2 us with 4, every one is slower with 8).
-        cluster = 1;
-        while (cluster < 4 && tiles * cluster < 512 && nblk >= GEMV_WARPS * cluster * 2 * 2) cluster *= 2;
-    }
+    if (cluster == 0) cluster = choose_cluster(tiles, nblk);
     if (M <= 8) return launch_gemv<1, JANIS_GEMV_U1>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     if (M <= 16) return launch_gemv<2, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     if (M <= 32) return launch_gemv<4, 2>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     return launch_gemv<8, 1>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
+}
+
+// The q/k/v projection of a decode step with the rotary encoding and the cache write in its epilogue (bfloat16,
+// at most 16 rows, the whole head rotated: rot == hd, hd a multiple of 16).  x [M, K]; W [heads * hd, K] with
+// heads = nq + 2 nkv (kpool given) or nq (kpool null: a layer that reads another layer's keys); q goes to
+// q_out [M, row_heads, hd], k and v to the cache line as janis_rope_store writes them.
+JANIS_EXPORT int janis_gemv_rope_store(const void* x, const void* W, void* q_out, int M, int K, const int* tok_pos,
+                                       const int* tok_seq, const int* seq_slot, const int* seq_end,
+                                       const float* inv_freq, int nq, int nkv, int hd, int row_heads, void* kpool,
+                                       void* vpool, const int* page_table, int table_stride, int ring_len,
+                                       cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 16) return fail("gemv_rope_store: at most 16 rows, found %d", M);
+    if (K <= 0 || K % 8) return fail("gemv_rope_store: K must be a positive multiple of 8, found %d", K);
+    if (hd <= 0 || hd % 16) return fail("gemv_rope_store: the head size must be a multiple of 16, found %d", hd);
+    if (nq <= 0 || nkv < 0 || row_heads < nq) return fail("gemv_rope_store: %d query heads in rows of %d heads", nq, row_heads);
+    if (((uintptr_t)x | (uintptr_t)W) & 15) return fail("gemv_rope_store: operands must be 16-byte aligned");
+    const int heads = kpool != nullptr ? nq + 2 * nkv : nq;
+    const int N = heads * hd;
+    RopeStore rs = {};
+    rs.tok_pos = tok_pos; rs.tok_seq = tok_seq; rs.seq_slot = seq_slot; rs.seq_end = seq_end; rs.inv_freq = inv_freq;
+    rs.kpool = (bf16*)kpool; rs.vpool = (bf16*)vpool; rs.page_table = page_table;
+    rs.table_stride = table_stride; rs.ring_len = ring_len;
+    rs.nq = nq; rs.nkv = kpool != nullptr ? nkv : 0; rs.hd = hd; rs.row_heads = row_heads;
+    const int cluster = choose_cluster(N / 16, (K + 31) / 32);
+    if (M <= 8)
+        return launch_gemv_rope<1, JANIS_GEMV_U1>((const bf16*)x, (const bf16*)W, (bf16*)q_out, M, N, K, cluster, rs, stream);
+    return launch_gemv_rope<2, 4>((const bf16*)x, (const bf16*)W, (bf16*)q_out, M, N, K, cluster, rs, stream);
 }

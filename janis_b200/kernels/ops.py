@@ -58,6 +58,7 @@ def core():
         lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
         lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
         lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
+        lib.janis_gemv_rope_store.argtypes = [P, P, P, I, I, P, P, P, P, P, I, I, I, I, P, P, P, I, I, P]
         lib.janis_gemm_tc05.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
         lib.janis_tc05_timeouts.restype = I
         lib.janis_tc05_set_stages.argtypes = [I]
@@ -296,6 +297,42 @@ def gemv_bf16(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0, cluster: in
                                     _t(out, "out", _FLOATS, (M, n_out)), _DT[out.dtype], M, N, K, epilogue,
                                     float(cap), int(cluster), _stream()))
     return out
+
+
+def gemv_rope_store(x, w, qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, nq: int, nkv: int, hd: int,
+                    kpool=None, vpool=None, page_table=None, ring_len: int = 0, store: bool = True):
+    """The q/k/v projection of up to 16 decode rows with the rotary encoding of the whole head and the cache write
+    in its epilogue: what `gemv_bf16(x, w, qkv)` followed by `rope_store(qkv, ...)` leaves in the queries' part
+    of qkv [M, heads, hd] and in the cache line, in one kernel (the keys' and values' part of qkv is not written).
+    w: [(nq + 2 nkv) hd, K], or [nq hd, K] with store=False (a layer that reads another layer's keys)."""
+    M, K = x.shape
+    heads = nq + 2 * nkv if store else nq
+    _t(x, "x", torch.bfloat16, (M, K))
+    _t(w, "w", torch.bfloat16, (heads * hd, K))
+    _t(qkv, "qkv", torch.bfloat16, (M, None, hd))
+    if qkv.shape[1] < nq:
+        raise KernelError("gemv_rope_store: the rows of qkv hold fewer heads than nq")
+    _t(tok_pos, "tok_pos", torch.int32)
+    _t(tok_seq, "tok_seq", torch.int32)
+    if tok_pos.numel() < M or tok_seq.numel() < M:
+        raise KernelError("gemv_rope_store: position tables shorter than the step")
+    _t(inv_freq, "inv_freq", torch.float32, (hd // 2,))
+    stride = 0
+    if store:
+        n_pages = kpool.shape[0]
+        _t(kpool, "kpool", torch.bfloat16, (n_pages, nkv, PAGE, hd))
+        _t(vpool, "vpool", torch.bfloat16, (n_pages, nkv, PAGE, hd))
+        _t(page_table, "page_table", torch.int32, (None, None))
+        _t(seq_slot, "seq_slot", torch.int32)
+        _t(seq_end, "seq_end", torch.int32)
+        stride = page_table.shape[1]
+    lib = core()
+    _check(lib, lib.janis_gemv_rope_store(
+        x.data_ptr(), w.data_ptr(), qkv.data_ptr(), M, K, tok_pos.data_ptr(), tok_seq.data_ptr(),
+        seq_slot.data_ptr() if store else None, seq_end.data_ptr() if store else None, inv_freq.data_ptr(),
+        nq, nkv, hd, qkv.shape[1], kpool.data_ptr() if store else None, vpool.data_ptr() if store else None,
+        page_table.data_ptr() if store else None, stride, ring_len, _stream()))
+    return qkv
 
 
 def softcap(x, cap: float):

@@ -100,8 +100,7 @@ class SoftmaxAttention(Mixer):
         # a written line that later layers read keeps its step buffer until the step ends
         name = f"attn.qkv.line{line.index}" if (own and line.has_readers and ctx.mode == "prefill") else "attn.qkv"
         qkv = ws.buf(name, (T, heads, hd), rt.dtype)
-        rt.linear(x, self.w_qkv if own else self.w_q, qkv.view(T, heads * hd))
-        self.position.encode_and_store(qkv, ctx, nq, nkv, hd, kv)
+        self.position.project_encode_store(x, self.w_qkv if own else self.w_q, qkv, ctx, nq, nkv, hd, kv)
         att = ws.buf("attn.ctx", (T, nq * hd), rt.dtype)
         if ctx.mode == "prefill":
             n_scratch = ops.attn_prefill_scratch_floats(T, ctx.n_seq, nq, hd, rt.dtype)

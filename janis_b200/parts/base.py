@@ -156,6 +156,12 @@ class PositionEncoding(Part):
     def encode_and_store(self, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, kv_line):
         raise NotImplementedError
 
+    def project_encode_store(self, x, w, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, kv_line):
+        """qkv [T, heads, hd] = x w^T, then encode_and_store.  An encoding whose kernels can do all of it at once
+        overrides this; the result must be what this order of the two leaves in the queries and in the cache."""
+        ctx.rt.linear(x, w, qkv.view(qkv.shape[0], -1))
+        return self.encode_and_store(qkv, ctx, nq, nkv, hd, kv_line)
+
 
 class Mixer(Part):
     def cache_needs(self) -> Mapping[str, Any]:

@@ -48,6 +48,21 @@ class RotaryEncoding(PositionEncoding):
                               nq, nkv, hd, kv_line.k, kv_line.v, kv_line.table, kv_line.ring_len, store=True)
 
 
+    def project_encode_store(self, x, w, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, kv_line):
+        """A decode step of up to 16 rows in bfloat16 that rotates the whole head: projection, encoding and cache
+        write are one kernel (the product's tiles pair each element with its partner half a head on)."""
+        ops = ctx.rt.ops
+        fused = (ctx.mode == "decode" and ctx.rt.dtype == torch.bfloat16 and self.rot == hd and hd % 16 == 0
+                 and x.shape[0] <= getattr(ops, "GEMV_FAST_ROWS", 0) and hasattr(ops, "gemv_rope_store"))
+        if not fused:
+            return super().project_encode_store(x, w, qkv, ctx, nq, nkv, hd, kv_line)
+        if kv_line is None or not kv_line.write:
+            return ops.gemv_rope_store(x, w, qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.seq_end, self.inv_freq,
+                                       nq, nkv, hd, store=False)
+        return ops.gemv_rope_store(x, w, qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.seq_end, self.inv_freq,
+                                   nq, nkv, hd, kv_line.k, kv_line.v, kv_line.table, kv_line.ring_len, store=True)
+
+
 class NoPosition(RotaryEncoding):
     """No encoding: keys and values are stored as projected."""
 

@@ -91,6 +91,17 @@ def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot, nq, nkv,
     return qkv
 
 
+def gemv_rope_store(x, w, qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, nq, nkv, hd, kpool=None, vpool=None,
+                    page_table=None, ring_len=0, store=True):
+    heads = nq + 2 * nkv if store else nq
+    M = x.shape[0]
+    full = (x.double() @ w.double().T).to(qkv.dtype).view(M, heads, hd)
+    rope_store(full, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, hd, nq, nkv, hd, kpool, vpool, page_table,
+               ring_len, store)
+    qkv[:, :nq] = full[:, :nq]
+    return qkv
+
+
 def gemm_f32(x, w, out, cap=0.0):
     v = x.double() @ w.double().T
     if cap > 0:

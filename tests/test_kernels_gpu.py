@@ -40,6 +40,17 @@ def close(got, want, tol, what=""):
     assert err <= tol * scale, f"{what}: max err {err:.3e} > {tol:.1e} x scale {scale:.3e}"
 
 
+def same(got, want, what=""):
+    """Bit for bit; says where and by how much if not."""
+    if torch.equal(got, want):
+        return
+    bad = (got != want).nonzero()
+    first = tuple(int(v) for v in bad[0])
+    diff = (got.double() - want.double()).abs().max().item()
+    raise AssertionError(f"{what}: {len(bad)} of {got.numel()} values differ, first at {first}: "
+                         f"{got[first].item()} vs {want[first].item()}; max difference {diff:.3e}")
+
+
 def tol_of(dtype):
     return F32_TOL if dtype == torch.float32 else BF16_TOL
 
@@ -179,6 +190,59 @@ def test_rope_store_many_tokens(dtype, nq, nkv, hd, rot, ring):
     close(qkv, qkv_ref, tol_of(dtype), "rotated q/k")
     close(k, k_ref, tol_of(dtype), "cached k")
     close(v, v_ref, tol_of(dtype), "cached v")
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("nq,nkv,hd,K,ring", [(8, 4, 256, 2304, 0), (4, 2, 64, 328, 64), (3, 1, 48, 72, 0),
+                                              (2, 2, 16, 2048, 128), (5, 1, 32, 9216, 64)])
+def test_projection_with_rotary_and_cache_write_in_one_kernel(M, nq, nkv, hd, K, ring):
+    """The fused decode kernel against the two kernels it replaces, bit for bit (it rounds the sums to bfloat16
+    before it rotates them, as they do), and against the plain statement: rows at positions on both sides of a
+    ring's wrap, a padding row, short and long K (clusters of 1, 2 and 4 CTAs), and the query-only form."""
+    d = dev()
+    pos = [(37 * i + (140 if i % 3 == 0 else 3)) % 190 for i in range(M)]
+    slots = [(-1 if (i == 2 and M > 2) else (5 * i + 3) % 16) for i in range(M)]     # every row a sequence of its own
+    tok_pos = torch.tensor(pos, dtype=torch.int32)
+    tok_seq = torch.arange(M, dtype=torch.int32)
+    seq_slot = torch.tensor(slots, dtype=torch.int32)
+    seq_end = (tok_pos + 1).int()
+    inv = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float32)
+    n_pages = 70
+    table = torch.randperm(n_pages, generator=torch.Generator().manual_seed(6))[:64].int().view(16, 4).contiguous()
+    heads = nq + 2 * nkv
+    x = rnd((M, K), torch.bfloat16, 30 + M)
+    w = (rnd((heads * hd, K), torch.bfloat16, 31) * (4.0 / K ** 0.5)).to(torch.bfloat16)
+    k0, v0 = _paged(n_pages, nkv, hd, torch.bfloat16, 32)
+    # the two kernels
+    qkv2 = torch.zeros((M, heads, hd), dtype=torch.bfloat16, device=d)
+    k2, v2 = k0.clone(), v0.clone()
+    ops().gemv_bf16(x, w, qkv2.view(M, heads * hd))
+    ops().rope_store(qkv2, tok_pos.to(d), tok_seq.to(d), seq_slot.to(d), seq_end.to(d), inv.to(d), hd, nq, nkv, hd,
+                     k2, v2, table.to(d), ring, True)
+    # the one kernel
+    qkv1 = torch.zeros((M, heads, hd), dtype=torch.bfloat16, device=d)
+    k1, v1 = k0.clone(), v0.clone()
+    ops().gemv_rope_store(x, w, qkv1, tok_pos.to(d), tok_seq.to(d), seq_slot.to(d), seq_end.to(d), inv.to(d), nq, nkv,
+                          hd, k1, v1, table.to(d), ring, True)
+    same(qkv1[:, :nq], qkv2[:, :nq], "rotated q")
+    same(k1, k2, "cached k")
+    same(v1, v2, "cached v")
+    # the plain statement
+    q_ref = torch.zeros((M, heads, hd), dtype=torch.bfloat16)
+    k_ref, v_ref = k0.cpu().clone(), v0.cpu().clone()
+    R.gemv_rope_store(x.cpu(), w.cpu(), q_ref, tok_pos, tok_seq, seq_slot, seq_end, inv, nq, nkv, hd, k_ref, v_ref,
+                      table, ring, True)
+    close(qkv1[:, :nq], q_ref[:, :nq], BF16_TOL, "rotated q")
+    close(k1, k_ref, BF16_TOL, "cached k")
+    close(v1, v_ref, BF16_TOL, "cached v")
+    # queries alone
+    wq = w[: nq * hd].contiguous()
+    q1 = torch.zeros((M, nq, hd), dtype=torch.bfloat16, device=d)
+    ops().gemv_rope_store(x, wq, q1, tok_pos.to(d), tok_seq.to(d), None, None, inv.to(d), nq, nkv, hd, store=False)
+    q2 = torch.zeros((M, nq, hd), dtype=torch.bfloat16, device=d)
+    ops().gemv_bf16(x, wq, q2.view(M, nq * hd))       # (fewer rows of W: K may be split over more CTAs than above)
+    ops().rope_store(q2, tok_pos.to(d), tok_seq.to(d), None, None, inv.to(d), hd, nq, nkv, hd, store=False)
+    same(q1, q2, "rotated q alone")
 
 
 def test_rope_angles_at_large_positions():
