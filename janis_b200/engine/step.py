@@ -72,6 +72,32 @@ def _bucket_prompt_seqs(n: int) -> int:
     return b
 
 
+def prompt_tables(entries, lens, Tb: int, Tmax: int, Smax: int) -> np.ndarray:
+    """The tables of a graphed prompt step, laid out for the largest shape: tokens, positions and sequence
+    indices (Tmax each), then slots, lengths before the step (all 0), lengths after it, first rows and wanted rows
+    (Smax each).  The tokens from the end of the real ones up to Tb are padding: token 0, position 0, sequence
+    n_seq.  Sequence n_seq and all after it have slot -1, length 0 and their first row at the end of the real
+    tokens; wanted rows beyond the real ones point at row 0."""
+    n_seq, T = len(entries), sum(lens)
+    host = np.zeros(3 * Tmax + 5 * Smax, dtype=np.int32)
+    first = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+    host[0:T] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+    host[Tmax:Tmax + T] = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+    host[2 * Tmax:2 * Tmax + T] = np.repeat(np.arange(n_seq, dtype=np.int32), lens)
+    host[2 * Tmax + T:2 * Tmax + Tb] = n_seq
+    o = 3 * Tmax
+    host[o:o + Smax] = -1                            # slots
+    host[o:o + n_seq] = [e.slot for e in entries]
+    host[o + 2 * Smax:o + 2 * Smax + n_seq] = lens   # lengths after the step
+    host[o + 3 * Smax:o + 4 * Smax] = T              # first rows
+    host[o + 3 * Smax:o + 3 * Smax + n_seq] = first
+    rows = [first[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
+    if rows:
+        rows = np.concatenate(rows)
+        host[o + 4 * Smax:o + 4 * Smax + len(rows)] = rows
+    return host
+
+
 class Stepper:
     MAX_GRAPH_BATCH = 256
     PROMPT_GRAPH_TOKENS = _PROMPT_TOKEN_BUCKETS[-1]     # longer prompt steps keep the device busy past the host
@@ -229,22 +255,9 @@ class Stepper:
         if self._prompt_logits is None or self._prompt_logits.shape[0] < Sb:
             self._prompt_graphs.clear()                 # graphs hold the address of the old buffer
             self._prompt_logits = torch.empty((Sb, self.model.vocab), dtype=torch.float32, device=dev)
-        host = np.zeros(3 * Tmax + 5 * Smax, dtype=np.int32)
-        first = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
-        host[0:T] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        host[Tmax:Tmax + T] = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
-        host[2 * Tmax:2 * Tmax + T] = np.repeat(np.arange(n_seq, dtype=np.int32), lens)
-        host[2 * Tmax + T:2 * Tmax + Tb] = n_seq
-        o = 3 * Tmax
-        host[o:o + Smax] = -1                            # slots
-        host[o:o + n_seq] = [e.slot for e in entries]
-        host[o + 2 * Smax:o + 2 * Smax + n_seq] = lens   # lengths after the step (before it: 0)
-        host[o + 3 * Smax:o + 4 * Smax] = T              # first rows
-        host[o + 3 * Smax:o + 3 * Smax + n_seq] = first
         n_want = 0 if out is None else out.shape[0]
-        if n_want:
-            host[o + 4 * Smax:o + 4 * Smax + n_want] = np.concatenate(
-                [first[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries)])
+        host = prompt_tables(entries, lens, Tb, Tmax, Smax)
+        o = 3 * Tmax
         for e, n in zip(entries, lens):
             self.cache.reserve(e.slot, n)
         self.cache.sync()
