@@ -273,7 +273,7 @@ def _pretty(config: str) -> str:
     return "Gemma2-" + name[len("gemma2-"):].upper() if name.startswith("gemma2-") else name
 
 
-def run(steps: int = 64, warmup: int = 8, batch: int = 8, context: int = 8192, config: str = "gemma2-2b",
+def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, config: str = "gemma2-2b",
         layers: int | None = None, points=(1, 64), prefill_tokens: int = 2048, e2e: bool = True,
         profile: str = "") -> dict:
     """The whole benchmark; returns the record that bench.py prints as one JSON line."""
@@ -322,7 +322,8 @@ def run(steps: int = 64, warmup: int = 8, batch: int = 8, context: int = 8192, c
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="janis bench")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256,
+                    help="timed decode steps (0.6 s at the default sizes: several clock samples, and the first and last step of the end-to-end run weigh little)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="janis_b200")
     ap.add_argument("--batch", default="8", help="sequences decoded together; a list (8,1,64) also times the others")
