@@ -288,10 +288,10 @@ def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, 
     eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=max_batch * room, max_batch=max_batch,
                                  max_context=room)
     main = measure_decode(eng, batch, context, steps, warmup, sample_clocks=True, profile=profile == "decode")
+    pre = measure_prefill(eng, prefill_tokens, profile=profile == "prefill")
     pts = {}
     for b in points:
         pts[f"decode_b{b}"] = round(measure_decode(eng, b, context, max(16, steps // 2), warmup)["tok_s"], 1)
-    pre = measure_prefill(eng, prefill_tokens, profile=profile == "prefill")
     end = measure_e2e(eng, batch, context, steps) if e2e and not profile else None
     cfg = eng.config
     rec = {
