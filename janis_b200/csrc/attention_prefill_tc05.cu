@@ -19,6 +19,8 @@
 // that it waits neither for the products nor for the other threads of its row.  The accumulator is
 // rescaled only when a row's maximum has grown by more than 2^8 since the reference the exponentials
 // use (P stays below 256, far inside bfloat16 and float range), so most tiles leave it untouched.
+// Barriers and tensor memory are set up, and the CTA's place in the step is read from the step's tables, before
+// the kernel waits for the one ahead of it in the stream; Q and the first keys are asked for right after the wait.
 // Every wait is bounded: on a timeout the CTA records it (janis_attn_tc05_timeouts), frees its tensor
 // memory and returns.  No TMA load here uses cluster multicast.
 #include <cuda.h>
@@ -175,9 +177,9 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // another may still read tile i - 1 (it cannot be behind by more: tile i - 1's exchange needs its arrival)
     __shared__ float row_max[4][SPLIT][BM];
     __shared__ float row_sum[SPLIT][BM];             // and, at the end, their sums
-    grid_dependents_launch();
-    grid_dependency_wait();
-    // which sequence, which tile of queries, which part of its keys (as in the mma.sync kernel)
+    // Which sequence, which tile of queries, which part of its keys (as in the mma.sync kernel).  The step's
+    // tables were written before the kernel ahead of this one started, so all of the set-up below (barriers,
+    // tensor memory) runs while that kernel still does; the wait comes before the first load of Q.
     const int item = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int gtile = item / parts, part = item % parts;
     int seq = -1, q0 = 0, len = 0;
@@ -205,7 +207,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
     auto bar = [&](int i) { return bar0 + 8 * i; };
 
-    if (threadIdx.x == 0) {
+    if (warp == LOADER_WARP && lane == 0) {           // the loader sets the barriers up: it is their first user
         mbar_init(bar(Q_FULL), 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(K_FULL + i), 1);
@@ -222,10 +224,22 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == LOADER_WARP) {                        // one warp allocates tensor memory
+    if (warp == ISSUER_WARP) {                        // one warp allocates tensor memory
         const uint32_t slot = (uint32_t)__cvta_generic_to_shared(&tmem_slot);
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    grid_dependents_launch();
+    grid_dependency_wait();
+    if (warp == LOADER_WARP && lane == 0) {           // Q and the first keys are on their way before the others are ready
+        mbar_expect_tx(bar(Q_FULL), Q_BYTES);
+        for (int sl = 0; sl < SLABS; ++sl) tma_load_2d(sQ + sl * Q_SLAB, &map_q, head * HD + sl * 64, first + q0, bar(Q_FULL));
+        for (int i = 0; i < 2 && i < n_tiles; ++i) {
+            mbar_expect_tx(bar(K_FULL + i), KV_TILE);
+            for (int sl = 0; sl < SLABS; ++sl)
+                tma_load_2d(sKV + i * 2 * KV_TILE + sl * KV_SLAB, &map_kv, (kv_k_head0 + kvh) * HD + sl * 64,
+                            first + k_first + i * BN, bar(K_FULL + i));
+        }
     }
     fence_before();
     __syncthreads();
@@ -239,8 +253,6 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // of P V, which frees the values: the loads follow the order in which the products finish
         // (K0 K1 V0 V1 K2 K3, then V(i + 2) after O(i) and K(i + 4) after S(i + 2), which is done by then), so
         // that a wait for values never holds back the keys that the next scores want.
-        mbar_expect_tx(bar(Q_FULL), Q_BYTES);
-        for (int sl = 0; sl < SLABS; ++sl) tma_load_2d(sQ + sl * Q_SLAB, &map_q, head * HD + sl * 64, first + q0, bar(Q_FULL));
         bool ok = true;
         auto load_k = [&](int i) {
             if (!ok || i >= n_tiles) return;
@@ -261,8 +273,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tma_load_2d(sV + sl * KV_SLAB, &map_kv, (kv_k_head0 + nkv + kvh) * HD + sl * 64, first + k_first + i * BN,
                             bar(V_FULL + s));
         };
-        load_k(0); load_k(1);
-        load_v(0); load_v(1);
+        load_v(0); load_v(1);                          // (Q, K0 and K1 were asked for above)
         load_k(2); load_k(3);
         for (int i = 0; ok && i + 2 < n_tiles; ++i) {
             load_v(i + 2);
@@ -517,7 +528,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncwarp();
     fence_before();
     __syncthreads();
-    if (warp == LOADER_WARP)
+    if (warp == ISSUER_WARP)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     if (failed && threadIdx.x == 0) atomicAdd(&g_timeouts, 1);
 }
