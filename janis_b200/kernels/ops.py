@@ -367,20 +367,6 @@ def tc05_timeouts() -> int:
     return int(core().janis_tc05_timeouts())
 
 
-_transposed: dict[int, tuple] = {}                 # id(weight) -> (weight, its transposed view)
-
-
-def _wt(w):
-    """w.t() without building the view again for every product of every step."""
-    hit = _transposed.get(id(w))
-    if hit is None or hit[0] is not w:
-        if len(_transposed) > 4096:
-            _transposed.clear()
-        hit = (w, w.t())
-        _transposed[id(w)] = hit
-    return hit[1]
-
-
 def linear_bf16(x, w, out):
     """out[M, N] = x w^T in bfloat16 with float accumulation: the skinny kernel up to 16 rows,
     the library product (cuBLAS) above."""
@@ -390,7 +376,7 @@ def linear_bf16(x, w, out):
     _t(x, "x", torch.bfloat16)
     _t(w, "w", torch.bfloat16)
     _t(out, "out", torch.bfloat16, (M, w.shape[0]))
-    torch.mm(x, _wt(w), out=out)
+    torch.mm(x, w.t(), out=out)
     return out
 
 
@@ -399,7 +385,7 @@ def matmul_bf16_to_f32(x, w, out):
     _t(x, "x", torch.bfloat16)
     _t(w, "w", torch.bfloat16)
     _t(out, "out", torch.float32, (x.shape[0], w.shape[0]))
-    torch.mm(x, _wt(w), out_dtype=torch.float32, out=out)
+    torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     return out
 
 
