@@ -936,6 +936,17 @@ JANIS_EXPORT int janis_attn_wait_timeouts() {
     return n;
 }
 
+namespace janis { int prefill_tc05_timeouts_async(int* host, cudaStream_t stream); }   // attention_prefill_tc05.cu
+
+// Both counts of this library (host[0]: the decode kernels' waits, host[1]: the tcgen05 prompt kernel's) copied into
+// pinned host memory in the order of `stream`, without waiting for it: a caller that waits for the stream anyway
+// (for its tokens) finds them there afterwards.
+JANIS_EXPORT int janis_attn_timeouts_async(int* host, cudaStream_t stream) {
+    cudaError_t e = cudaMemcpyFromSymbolAsync(host, g_wait_timeouts, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return fail("attn_timeouts_async: %s", cudaGetErrorString(e));
+    return prefill_tc05_timeouts_async(host + 1, stream);
+}
+
 // Runs the bounded wait against a barrier nothing completes (at most 4096 tries): *status becomes 1.
 JANIS_EXPORT int janis_attn_wait_probe(int tries, int* status, cudaStream_t stream) {
     if (tries < 1 || tries > 4096) return fail("wait_probe: between 1 and 4096 tries, found %d", tries);

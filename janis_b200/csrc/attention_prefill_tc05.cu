@@ -21,6 +21,8 @@
 // use (P stays below 256, far inside bfloat16 and float range), so most tiles leave it untouched.
 // Barriers and tensor memory are set up, and the CTA's place in the step is read from the step's tables, before
 // the kernel waits for the one ahead of it in the stream; Q and the first keys are asked for right after the wait.
+// A sequence's result depends on its own rows alone: keys beyond its end are masked by selection, and the rows of
+// the last box of values that lie beyond its end are cleared in shared memory before P V reads them.
 // Every wait is bounded: on a timeout the CTA records it (janis_attn_tc05_timeouts), frees its tensor
 // memory and returns.  No TMA load here uses cluster multicast.
 #include <cuda.h>
@@ -422,6 +424,24 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 }
             }
+            // The last tile of a sequence that does not end on a tile border: the box of values runs on into rows
+            // that are not this sequence's (the next sequence's, padding, whatever the buffer held).  Their
+            // columns of P are zero, but 0 x NaN is NaN in the product, so those rows of V are cleared in shared
+            // memory once the box has landed (a 128-byte swizzle permutes within a row: whole rows stay whole).
+            // Keys of such rows only reach their own columns of S, which the mask replaces.
+            {
+                const int k0 = k_first + it * BN;
+                if (k0 + BN > len) {
+                    if (!mbar_wait(bar(V_FULL + (it & 1)), (it >> 1) & 1, fail_flag)) return false;
+                    const int n_valid = len - k0;     // >= 1: the tile holds a key that a query of this tile sees
+                    unsigned char* v_ptr = smem_raw + (sKV - raw) + (it & 1) * 2 * KV_TILE + KV_TILE;
+                    const int pieces = (BN - n_valid) * 8;           // 16-byte pieces per slab
+                    for (int idx = threadIdx.x; idx < pieces * SLABS; idx += SOFTMAX_WARPS * 32) {
+                        const int sl = idx / pieces, pc = idx % pieces;
+                        *reinterpret_cast<uint4*>(v_ptr + sl * KV_SLAB + n_valid * 128 + pc * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
             // this thread's CPT keys of row r of P: pieces of 16 bytes, swizzled like the TMA tiles
 #pragma unroll
             for (int c = 0; c < CPT / 8; ++c) {
@@ -590,6 +610,11 @@ int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const 
     return launch_kernel("attn_prefill_tc05", kernel, dim3(nq, n_tiles_bound * parts), dim3(pt::THREADS), pt::SMEM_BYTES,
                          stream, 1, mq, mkv, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, kv_k_head0, scale, cap,
                          window, parts, piece, partial);
+}
+
+int prefill_tc05_timeouts_async(int* host, cudaStream_t stream) {
+    cudaError_t e = cudaMemcpyFromSymbolAsync(host, pt::g_timeouts, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+    return e == cudaSuccess ? 0 : fail("attn_timeouts_async: %s", cudaGetErrorString(e));
 }
 
 }  // namespace janis

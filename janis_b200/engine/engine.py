@@ -51,6 +51,11 @@ class Engine:
         self.sampler = Sampler(rt)
         self.stop_tokens = tuple(model.stop_tokens)
         self._closed = False
+        # counters of bounded device waits that gave up: read wherever the host waits for the device anyway
+        watch = getattr(rt.ops, "WaitWatch", None)
+        self.watch = watch() if watch is not None and torch.device(rt.device).type == "cuda" else None
+        if self.watch is not None:
+            self.check_health(quiet=True)        # what happened before this engine existed is not its business
 
     # -- the step function, for callers that drive it themselves ----------------
     def alloc_slot(self) -> int:
@@ -62,6 +67,17 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
         """See `Stepper.step`: float32 logits [wanted, vocab] on the device."""
         return self.stepper.step(entries)
+
+    def check_health(self, quiet: bool = False) -> None:
+        """Waits for the device and raises `KernelError` if a kernel gave up one of its bounded waits since the
+        last check (a CTA that gives up returns without its result, so the steps in between are not to be
+        trusted).  `generate` does this by itself wherever it reads tokens; a caller that drives `step` calls it
+        when it reads logits."""
+        if self.watch is None:
+            return
+        self.watch.request()
+        torch.cuda.current_stream().synchronize()
+        self.watch.check(quiet)
 
     # -- generation ---------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], temp: float = 0.0, top_p: float = 1.0,
@@ -136,7 +152,13 @@ class _Backend:
         entries = [StepEntry(h, p, (len(p) - 1,)) for h, p in zip(handles, prompts)]
         logits = self.e.stepper.step(entries, copy=False)
         toks = self.e.sampler.sample(logits, self.params, request_ids, [0] * len(handles), None, banned)
-        return toks.tolist()
+        watch = self.e.watch
+        if watch is not None:
+            watch.request()
+        toks = toks.tolist()          # waits for the stream: the counters of given-up waits have arrived too
+        if watch is not None:
+            watch.check()
+        return toks
 
     def decode_start(self, handles, last_tokens, request_ids, token_index, replies):
         n = len(handles)
@@ -145,23 +167,34 @@ class _Backend:
                    for i, h in enumerate(handles)]
         logits = st.step(entries, copy=False, tokens_on_device=last_tokens is None)
         ids = [r if r is not None else 0 for r in request_ids]
+        watch = self.e.watch
         if n > Stepper.MAX_GRAPH_BATCH or self._pinned is None:
-            return self.e.sampler.sample(logits, self.params, ids, token_index, replies)
+            toks = self.e.sampler.sample(logits, self.params, ids, token_index, replies)
+            if watch is not None:
+                watch.request()
+            return toks
         out = st.token_buffer(n)
         self.e.sampler.sample(logits, self.params, ids, token_index, replies, out=out)
         host = self._pinned[self._turn % len(self._pinned)]
         self._turn += 1
         host[:n].copy_(out, non_blocking=True)
+        if watch is not None:
+            watch.request()           # the counters of given-up waits travel with the tokens
         done = torch.cuda.Event()
         done.record()
         return (host, done, n)
 
     def decode_finish(self, ticket):
+        watch = self.e.watch
         if isinstance(ticket, torch.Tensor):
-            return ticket.tolist()
-        host, done, n = ticket
-        done.synchronize()            # the one wait of a step: n token ids
-        return host[:n].tolist()
+            toks = ticket.tolist()
+        else:
+            host, done, n = ticket
+            done.synchronize()        # the one wait of a step: n token ids
+            toks = host[:n].tolist()
+        if watch is not None:
+            watch.check()
+        return toks
 
 
 # ---------------------------------------------------------------------------

@@ -13,8 +13,8 @@ per (padded batch size, bound on the lengths); padding rows carry slot -1, touch
 no cache and change no other row.  Short prompt steps, whose three hundred
 launches cost the host more time than the device needs for them, are replayed
 from graphs too, one per (padded token count, padded sequence count) once a
-shape has come twice; padding tokens belong to a padding sequence of slot -1 and
-length 0 that stands behind the real ones.
+shape has come twice; padding tokens form a sequence of their own with slot -1
+that stands behind the real ones: it is computed like any other and stored nowhere.
 
 The reference's forward takes one sequence, one offset, and returns the last
 position's logits (`qwen/model.go:346-349`, `gemma/gemma.go:196-213`).
@@ -75,22 +75,27 @@ def _bucket_prompt_seqs(n: int) -> int:
 def prompt_tables(entries, lens, Tb: int, Tmax: int, Smax: int) -> np.ndarray:
     """The tables of a graphed prompt step, laid out for the largest shape: tokens, positions and sequence
     indices (Tmax each), then slots, lengths before the step (all 0), lengths after it, first rows and wanted rows
-    (Smax each).  The tokens from the end of the real ones up to Tb are padding: token 0, position 0, sequence
-    n_seq.  Sequence n_seq and all after it have slot -1, length 0 and their first row at the end of the real
-    tokens; wanted rows beyond the real ones point at row 0."""
+    (Smax each).  The tokens from the end of the real ones up to Tb are padding: token 0 at positions 0, 1, ... of
+    sequence n_seq, a sequence of its own with slot -1 and their number as its length, so that every row of the
+    step is some sequence's and every kernel writes it (it is stored nowhere and no real sequence sees it).  The
+    sequences after it have slot -1 and length 0; the first row of each is the end of the one before; wanted
+    rows beyond the real ones point at row 0."""
     n_seq, T = len(entries), sum(lens)
     host = np.zeros(3 * Tmax + 5 * Smax, dtype=np.int32)
     first = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
     host[0:T] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
     host[Tmax:Tmax + T] = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+    host[Tmax + T:Tmax + Tb] = np.arange(Tb - T, dtype=np.int32)
     host[2 * Tmax:2 * Tmax + T] = np.repeat(np.arange(n_seq, dtype=np.int32), lens)
     host[2 * Tmax + T:2 * Tmax + Tb] = n_seq
     o = 3 * Tmax
     host[o:o + Smax] = -1                            # slots
     host[o:o + n_seq] = [e.slot for e in entries]
     host[o + 2 * Smax:o + 2 * Smax + n_seq] = lens   # lengths after the step
-    host[o + 3 * Smax:o + 4 * Smax] = T              # first rows
+    host[o + 2 * Smax + n_seq] = Tb - T              # the padding tokens' sequence
+    host[o + 3 * Smax:o + 4 * Smax] = Tb             # first rows
     host[o + 3 * Smax:o + 3 * Smax + n_seq] = first
+    host[o + 3 * Smax + n_seq] = T
     rows = [first[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
     if rows:
         rows = np.concatenate(rows)
@@ -243,9 +248,9 @@ class Stepper:
 
     def _prefill_graphed(self, entries, lens, out, key) -> None:
         """A short prompt step through a CUDA graph of its padded shape.  The tables live in one static device
-        buffer laid out for the largest shape; padding tokens (token 0, position 0) belong to sequence n_seq,
-        which like the sequences after it has slot -1, length 0 and its first row at the end of the real
-        tokens; wanted rows beyond the real ones point at row 0 and their logits are dropped."""
+        buffer laid out for the largest shape; padding tokens (token 0) are sequence n_seq, which has slot -1 and
+        attends over itself alone, so every row of every buffer of the step is written; the sequences after it
+        have slot -1 and length 0; wanted rows beyond the real ones point at row 0 and their logits are dropped."""
         Tb, Sb, wanted = key
         Tmax, Smax = self.PROMPT_GRAPH_TOKENS, self.PROMPT_GRAPH_SEQS
         n_seq, T = len(entries), sum(lens)

@@ -61,6 +61,7 @@ def core():
         lib.janis_gemv_rope_store.argtypes = [P, P, P, I, I, P, P, P, P, P, I, I, I, I, P, P, P, I, I, P]
         lib.janis_gemm_tc05.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
         lib.janis_tc05_timeouts.restype = I
+        lib.janis_tc05_timeouts_async.argtypes = [P, P]
         lib.janis_tc05_set_stages.argtypes = [I]
         lib.janis_tc05_set_stages.restype = None
         lib.janis_argmax.argtypes = [P, P, I, I, P]
@@ -91,6 +92,7 @@ def attention_lib(head_dim: int):
         lib.janis_attn_set_prefill_piece.argtypes = [I]
         lib.janis_attn_set_prefill_piece.restype = None
         lib.janis_attn_tc05_timeouts.restype = I
+        lib.janis_attn_timeouts_async.argtypes = [P, P]
         lib.janis_attn_prefill_scratch.argtypes = [I, I]
         lib.janis_attn_prefill_scratch.restype = c_longlong
         lib.janis_attn_prefill_tile.restype = I
@@ -365,6 +367,46 @@ def tc05_set_stages(stages: int = 0) -> None:
 def tc05_timeouts() -> int:
     """How often a CTA of gemm_tc05 gave up waiting on a barrier (0 in a healthy run); synchronises."""
     return int(core().janis_tc05_timeouts())
+
+
+class WaitWatch:
+    """Notices when a kernel has given up one of its bounded waits (on a barrier of its copies or of its tensor-core
+    products): such a CTA returns without its result, and what the step produced is then worthless.
+
+    `request()` asks every loaded library, in the order of the current stream and without waiting, to copy its
+    counters of given-up waits into pinned host memory; `check()`, called once the host has waited for that
+    stream anyway (to read the step's tokens), raises `KernelError` if a counter has grown since the last
+    check.  Counters of libraries loaded later join at their next request."""
+
+    def __init__(self):
+        self._host = torch.zeros(64, dtype=torch.int32).pin_memory()
+        self._where: dict[str, int] = {}           # library -> index of its first counter
+        self._seen = [0] * 64
+
+    def _slot(self, name: str) -> int:              # two counters a library (the core library uses one)
+        if name not in self._where:
+            if 2 * len(self._where) + 2 > 64:
+                raise KernelError("too many attention libraries for one watch")
+            self._where[name] = 2 * len(self._where)
+        return self._where[name]
+
+    def request(self) -> None:
+        st, base = _stream(), self._host.data_ptr()
+        if _core is not None:
+            _check(_core, _core.janis_tc05_timeouts_async(base + 4 * self._slot("core"), st), 0)
+        for hd, lib in _attn.items():
+            _check(lib, lib.janis_attn_timeouts_async(base + 4 * self._slot(f"attention (head size {hd})"), st), 0)
+
+    def check(self, quiet: bool = False) -> None:
+        """Call after the stream of the last `request()` has been waited for (quiet: take note, raise nothing)."""
+        now = self._host.tolist()
+        grown = [(name, now[at + i] - self._seen[at + i]) for name, at in self._where.items() for i in range(2)
+                 if now[at + i] > self._seen[at + i]]
+        self._seen = now
+        if grown and not quiet:
+            what = ", ".join(f"{n} in {name}" for name, n in grown)
+            raise KernelError(f"a kernel gave up a bounded wait ({what}): the results of the steps since the last "
+                              "check are not to be trusted")
 
 
 def linear_bf16(x, w, out):

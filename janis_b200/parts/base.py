@@ -90,13 +90,22 @@ class Workspace:
             if cur is not None and name in self._in_graph:
                 self._retired.append(cur)         # keep its memory valid for the graphs that recorded it
                 self._in_graph.discard(name)
-            cur = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            # zeros, not whatever the allocator hands out: a kernel that reads a row nobody wrote (a tile that runs
+            # past the step's rows) must find numbers there
+            cur = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[name] = cur
         if self.frozen:
             self._in_graph.add(name)
         view = cur[:n].view(*shape)
         self._views[name] = (shape, cur, view)
         return view
+
+    def fill(self, value) -> None:
+        """Every buffer filled with `value` (tests poison the workspace with NaN between steps: a step must write
+        what it reads)."""
+        for t in self._bufs.values():
+            if t.is_floating_point():
+                t.fill_(value)
 
     def begin_capture(self) -> None:
         self.frozen = True

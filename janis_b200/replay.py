@@ -63,6 +63,8 @@ def run_trace(engine, lines: Iterable[str], out_dir: str, report: TextIO = sys.s
                 tmp = os.path.join(out_dir, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))
+            if hasattr(engine, "check_health"):
+                engine.check_health()     # a kernel that gave up a bounded wait: no logits of this run are to be trusted
         for rid in ended:
             rid = str(rid)
             if rid not in slots:

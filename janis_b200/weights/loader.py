@@ -111,17 +111,60 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & 0x7FFF_FFFF_FFFF_FFFF
 
 
+def _signed64(c: int) -> int:
+    c &= 0xFFFF_FFFF_FFFF_FFFF
+    return c - (1 << 64) if c >= (1 << 63) else c
+
+
+_GAMMA, _MUL1, _MUL2 = _signed64(0x9E3779B97F4A7C15), _signed64(0xBF58476D1CE4E5B9), _signed64(0x94D049BB133111EB)
+_CHUNK = 1 << 22                 # elements drawn at a time (the 64-bit intermediates of a whole embedding would not fit)
+
+
+def _hash64(counter: torch.Tensor) -> torch.Tensor:
+    """The splitmix64 finaliser over int64 values (two's-complement wrap-around; shifts made logical by masks)."""
+    z = counter * _GAMMA
+    z = (z ^ ((z >> 30) & 0x3_FFFF_FFFF)) * _MUL1
+    z = (z ^ ((z >> 27) & 0x1F_FFFF_FFFF)) * _MUL2
+    return z ^ ((z >> 31) & 0x1_FFFF_FFFF)
+
+
+def _bell(key: int, start: int, n: int, device) -> torch.Tensor:
+    """n values of mean 0 and variance 1, those of elements start .. start + n - 1 of the tensor `key` names:
+    the sum of twelve 16-bit fields of three hashes of the element's index, a bell curve that stands in for the
+    normal distribution (same mean and variance, kurtosis 2.9, nothing beyond 6 standard deviations).  Integer
+    arithmetic and exact float steps only, so every device computes the same bits."""
+    i = torch.arange(start, start + n, dtype=torch.int64, device=device)
+    total = torch.zeros(n, dtype=torch.int64, device=device)
+    for j in (1, 2, 3):
+        z = _hash64(i * 4 + (j + key))
+        for shift in (0, 16, 32, 48):
+            total += (z >> shift) & 0xFFFF
+    # twelve uniforms on [0, 1): mean 6 x 65535 / 65536 (subtracted exactly), variance 12 / 12 (up to 2^-32)
+    return (total - 6 * 65535).to(torch.float32) * (1.0 / 65536.0)
+
+
 def random_tensor(name: str, spec: TensorSpec, seed: int, device="cpu",
                   dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """The tensor that (seed, name) names: each tensor has a generator of its own, so
-    the values do not depend on which other tensors are drawn, nor in what order."""
-    g = torch.Generator(device=device)
-    g.manual_seed(_tensor_seed(seed, name))
+    """The tensor that (seed, name) names, the same bits on every device: a counter-based generator keyed by the
+    seed, the name and the element's index, so the values depend neither on which other tensors are drawn, nor
+    on their order, nor on where they are drawn."""
+    key = _tensor_seed(seed, name) >> 3           # room for the counters' low bits within 63 bits
+    n = 1
+    for d in spec.shape:
+        n *= int(d)
     if spec.integer:
-        return torch.randint(0, 2 ** 15, spec.shape, generator=g, device=device, dtype=torch.int32)
-    t = torch.empty(spec.shape, device=device, dtype=torch.float32)
-    t.normal_(0.0, spec.init_std, generator=g)
-    return t.to(dtype)
+        out = torch.empty(n, device=device, dtype=torch.int32)
+        for a in range(0, n, _CHUNK):
+            m = min(_CHUNK, n - a)
+            i = torch.arange(a, a + m, dtype=torch.int64, device=device)
+            out[a:a + m] = (_hash64(i * 4 + (1 + key)) & 0x7FFF).to(torch.int32)
+        return out.view(spec.shape)
+    out = torch.empty(n, device=device, dtype=dtype)
+    std = float(spec.init_std)
+    for a in range(0, n, _CHUNK):
+        m = min(_CHUNK, n - a)
+        out[a:a + m] = (_bell(key, a, m, device) * std).to(dtype)
+    return out.view(spec.shape)
 
 
 def random_tensors(expected: Mapping[str, TensorSpec], seed: int, device="cpu",

@@ -124,6 +124,75 @@ def test_padding_and_company_change_nothing(on, dtype, engines, plain_models):
         assert torch.equal(alone[20:], pair[20:]) and torch.equal(alone[20:], nine[20:])
 
 
+@pytest.mark.parametrize("on,dtype", CASES)
+@pytest.mark.parametrize("n_live", [17, 33, 64])
+def test_decode_batches_of_many_sequences(on, dtype, n_live, engines, plain_models):
+    """Decode steps of 17, 33 and 64 live sequences of unequal lengths (more rows than the skinny products
+    take: library products inside the recorded step, the activation as a kernel of its own, the tensor-core
+    product for the logits, batches padded to a multiple of 8); the shorter requests end earlier, so the
+    batch shrinks through every padded size on its way down."""
+    for key in (["B_hot", "C"] if on == "cuda" else ["B"]):
+        V = vocab_of(key)
+        g = torch.Generator().manual_seed(900 + n_live)
+        lens = torch.randint(4, 80, (n_live,), generator=g).tolist()
+        lens[0], lens[1] = 140, 3                       # one far beyond the windows, one very short
+        prompts = [max(1, n - int(torch.randint(1, 12, (1,), generator=g))) for n in lens]
+        reqs = [random_tokens(V, n, 910 + i) for i, n in enumerate(lens)]
+        eng = engines(key, dtype, on, max_tokens=n_live * 192, max_batch=n_live)
+        got = run_requests(eng, reqs, prompts)
+        for i, (gi, r) in enumerate(zip(got, reqs)):
+            assert_logits(gi, plain_logits(plain_models, key, r), dtype,
+                          f"{key} batch of {n_live}, request {i} (len {lens[i]}, prompt {prompts[i]})")
+        assert eng.cache.live_slots() == []
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_a_decode_batch_beyond_the_recorded_sizes(on, dtype, engines, plain_models):
+    """More sequences than a recorded decode step holds (256): such a step is launched kernel by kernel with
+    tables of its own."""
+    key = "A_hot" if on == "cuda" else "A_hot"
+    V = vocab_of(key)
+    n_live = 260
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(3, 9, (n_live,), generator=g).tolist()
+    lens[5] = 30
+    reqs = [random_tokens(V, n, 1300 + i) for i, n in enumerate(lens)]
+    eng = engines(key, dtype, on, max_tokens=n_live * 64, max_batch=n_live)
+    got = run_requests(eng, reqs, [n - 2 for n in lens])
+    for i, (gi, r) in enumerate(zip(got, reqs)):
+        assert_logits(gi, plain_logits(plain_models, key, r), dtype, f"{key} batch of {n_live}, request {i}")
+    assert eng.cache.live_slots() == []
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_a_prompt_step_cut_into_pieces(on, dtype, engines, plain_models):
+    """A prompt step of more tokens than `max_step_tokens` runs as pieces cut at sequence borders; logits are
+    wanted at places in every piece (and at none in one sequence), and come back in the order of the entries."""
+    from janis_b200 import StepEntry
+    key = "B_hot" if on == "cuda" else "B"
+    V = vocab_of(key)
+    lens = [30, 25, 40, 10, 70, 3, 50]                  # pieces of at most 50 tokens: 30 | 25 | 40 10 | 70 | 3 | 50
+    want = [[0, 29], [24], list(range(40)), [], [5, 69], [0, 1, 2], [49]]
+    reqs = [random_tokens(V, n + 2, 1500 + i) for i, n in enumerate(lens)]
+    eng = engines(key, dtype, on, max_tokens=2048, max_step_tokens=50)
+    slots = [eng.alloc_slot() for _ in reqs]
+    out = eng.step([StepEntry(s, r[:n], w) for s, r, n, w in zip(slots, reqs, lens, want)])
+    assert out.shape[0] == sum(len(w) for w in want)
+    o = 0
+    for i, (r, w) in enumerate(zip(reqs, want)):
+        if w:
+            assert_logits(out[o:o + len(w)], plain_logits(plain_models, key, r)[w], dtype, f"{key} cut step, request {i}")
+        o += len(w)
+    for t in range(2):                                  # and the cache holds every piece's keys
+        out = eng.step([StepEntry(s, [r[n + t]], [0]) for s, r, n in zip(slots, reqs, lens)])
+        for i, (r, n) in enumerate(zip(reqs, lens)):
+            assert_logits(out[i:i + 1], plain_logits(plain_models, key, r)[n + t:n + t + 1], dtype,
+                          f"{key} after a cut step, request {i} token {t}")
+    for s in slots:
+        eng.free_slot(s)
+    eng.cache.audit()
+
+
 @GPU
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graphs_and_plain_launches_agree(dtype, model_dirs, plain_models):
@@ -190,15 +259,18 @@ def test_short_prompt_steps_replayed_from_graphs(key, dtype, model_dirs, plain_m
     from janis_b200 import StepEntry
     eng = make_engine(model_dirs[key], dtype, "cuda", max_tokens=2048)
     V = vocab_of(key)
+    poison = lambda: eng.stepper.ws.fill(float("nan"))      # a step must write every row it reads, padding included
     batches = [(30, 75, 12), (41, 50, 33), (64, 64), (1, 100, 20), (3, 2, 1), (120,)]
     for b, lens in enumerate(batches):
         reqs = [random_tokens(V, n + 3, 400 + 10 * b + i) for i, n in enumerate(lens)]
         want = [plain_logits(plain_models, key, r) for r in reqs]
         slots = [eng.alloc_slot() for _ in reqs]
+        poison()
         out = eng.step([StepEntry(s, r[:n], [n - 1]) for s, r, n in zip(slots, reqs, lens)])
         for i, n in enumerate(lens):
             assert_logits(out[i:i + 1], want[i][n - 1:n], dtype, f"{key} batch {b} prompt {i}")
         for t in range(3):
+            poison()
             out = eng.step([StepEntry(s, [r[n + t]], [0]) for s, r, n in zip(slots, reqs, lens)])
             for i, n in enumerate(lens):
                 assert_logits(out[i:i + 1], want[i][n + t:n + t + 1], dtype, f"{key} batch {b} request {i} token {t}")

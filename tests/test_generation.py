@@ -156,11 +156,43 @@ def test_janis_generate_command(model_dirs, plain_models):
 
 
 @GPU
-def test_engine_from_a_configuration_alone():
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_engine_from_a_configuration_alone(dtype, tmp_path):
+    """Weights drawn on the device from (seed, tensor name) are the ones the random-weights folder of the same
+    seed holds (drawn on the CPU): the engine's greedy reply is the plain model's over that folder."""
     import janis_b200
-    eng = janis_b200.from_config(TINY["A"], seed=3, dtype="bfloat16", max_tokens=256)
-    out = eng.generate([[1, 2, 3]], max_tokens=4, stop=())
+    janis_b200.write_random_model(str(tmp_path), TINY["B"], seed=3)
+    plain = {"rnd": P.load_folder(str(tmp_path))}
+    eng = janis_b200.from_config(TINY["B"], seed=3, dtype=dtype, max_tokens=256)
+    prompt = random_tokens(TINY["B"]["vocab_size"], 21, 130)
+    out = eng.generate([prompt], max_tokens=4, stop=())
     assert len(out[0]) == 4
+    check_greedy(plain, "rnd", dtype, prompt, out[0])
     eng.close()
     with pytest.raises(RuntimeError, match="closed"):
         eng.generate([[1]])
+
+
+@GPU
+def test_a_given_up_wait_is_reported_by_the_engine(tmp_path):
+    """A CTA that gives up a bounded wait returns without its result.  The engine reads the libraries' counters
+    wherever it waits for tokens anyway: a count that has grown ends `generate` with an error instead of
+    tokens nobody should trust; afterwards the engine works as before.  (Head size 96: a library whose
+    counter no other test expects to be zero; the probe is a one-warp kernel whose barrier nothing completes.)"""
+    import janis_b200
+    from janis_b200.kernels import ops
+    cfg = dict(TINY["B"], head_dim=96, query_pre_attn_scalar=96)
+    eng = janis_b200.from_config(cfg, seed=4, dtype="bfloat16", max_tokens=512)
+    prompts = [random_tokens(cfg["vocab_size"], n, 140 + n) for n in (9, 30)]
+    first = eng.generate(prompts, max_tokens=5, stop=())
+    assert ops.attn_wait_probe(96, tries=32) == 1
+    with pytest.raises(ops.KernelError, match="gave up a bounded wait"):
+        eng.generate(prompts, max_tokens=5, stop=())
+    assert eng.cache.live_slots() == []
+    eng.cache.audit()
+    assert eng.generate(prompts, max_tokens=5, stop=()) == first
+    assert ops.attn_wait_probe(96, tries=32) == 1
+    with pytest.raises(ops.KernelError, match="gave up a bounded wait"):
+        eng.check_health()
+    eng.check_health()
+    eng.close()

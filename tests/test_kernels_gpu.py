@@ -491,6 +491,73 @@ def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, piece, prefill_kern
     assert ops().attn_tc05_timeouts(hd) == 0
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 64), (2, 1, 128), (8, 4, 256), (3, 1, 48), (4, 2, 16)])
+@pytest.mark.parametrize("window,cap", [(0, 30.0), (100, 0.0)])
+@pytest.mark.parametrize("from_kv_src", [False, True])
+def test_attn_prefill_ignores_rows_that_are_not_a_sequences_own(nq, nkv, hd, window, cap, from_kv_src):
+    """Rows before, between and behind the sequences hold NaN and +Inf (queries, keys and values alike): no
+    sequence's result may change.  A tile of keys or values that runs past a sequence's end is masked in the
+    scores, but a product of a zero weight with NaN is NaN, so the kernels must not let such rows into P V.
+    Lengths end inside, on and just past tile borders; the last sequence is followed by garbage up to the end
+    of the buffer.  All three prompt kernels: CUDA cores in float32 and bfloat16, mma.sync, tcgen05."""
+    lens = [5, 63, 64, 70, 129, 200, 1]
+    gaps = [3, 70, 1, 64, 130, 7, 9, 150]            # rows before sequence i; the last: behind them all
+    first, row = [], 0
+    for n, g in zip(lens, gaps):
+        row += g
+        first.append(row)
+        row += n
+    T = row + gaps[-1]
+    d = dev()
+    own = torch.zeros(T, dtype=torch.bool)
+    for f, n in zip(first, lens):
+        own[f:f + n] = True
+    scale = 1.0 / math.sqrt(hd)
+    # for the per-token CUDA-core kernel the rows of a gap are a sequence of garbage of their own
+    g_first, g_len, prev = [], [], 0
+    for f, n in zip(first + [T], lens + [0]):
+        g_first.append(prev)
+        g_len.append(f - prev)
+        prev = f + n
+    all_first = torch.tensor(first + g_first, dtype=torch.int32)
+    all_len = lens + g_len
+    tok_pos = torch.zeros(T, dtype=torch.int32)
+    tok_seq = torch.zeros(T, dtype=torch.int32)
+    for i, (f, n) in enumerate(zip(all_first.tolist(), all_len)):
+        tok_pos[f:f + n] = torch.arange(n, dtype=torch.int32)
+        tok_seq[f:f + n] = i
+    for dtype in DTYPES:
+        heads = nq if from_kv_src else nq + 2 * nkv
+        clean = rnd((T, nq + 2 * nkv, hd), dtype, 44)
+        poison = torch.where(torch.arange(T, device=d) % 2 == 0, float("nan"), float("inf")).to(dtype)
+        dirty = torch.where(own.to(d)[:, None, None], clean, poison[:, None, None].expand_as(clean)).contiguous()
+        q = dirty[:, :nq].contiguous() if from_kv_src else dirty
+        kw = dict(kv_src=dirty, kv_row_heads=nq + 2 * nkv, kv_k_head0=nq) if from_kv_src else {}
+        want = torch.zeros((T, nq * hd), dtype=torch.float64)
+        R.attn_prefill(clean.cpu(), tok_pos, tok_seq, all_first, want, nq, nkv, hd, scale, cap, window)
+        runs = [("cuda cores", dict(tensor_cores=False), 1)]
+        if dtype == torch.bfloat16:
+            runs.append(("mma.sync", dict(seq_len=torch.tensor(lens, dtype=torch.int32, device=d)), 0))
+            if hd % 64 == 0 and hd <= 256:
+                runs.append(("tcgen05", dict(seq_len=torch.tensor(lens, dtype=torch.int32, device=d)), 1))
+        try:
+            for name, extra, which in runs:
+                ops().attn_set_prefill_kernel(hd, which)
+                tensor_cores = "seq_len" in extra
+                out = torch.full((T, nq * hd), 9.0, dtype=dtype, device=d)
+                ops().attn_prefill(q, tok_pos.to(d), tok_seq.to(d),
+                                   (all_first[:len(lens)] if tensor_cores else all_first).to(d), out, nq, nkv, hd, scale,
+                                   cap, window, **kw, **extra)
+                got = out.cpu()[own]
+                assert torch.isfinite(got).all(), f"{name} {dtype}: rows of other sequences reached a result"
+                close(got, want[own], (2 * BF16_TOL if tensor_cores else tol_of(dtype)), f"{name} {dtype} beside garbage")
+                if tensor_cores:                     # rows that are nobody's are not written
+                    assert (out.cpu()[~own] == 9.0).all()
+        finally:
+            ops().attn_set_prefill_kernel(hd, 1)
+    assert ops().attn_tc05_timeouts(hd) == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attn_prefill_reads_another_layers_keys(dtype):
     nq, nkv, hd = 4, 2, 32

@@ -171,3 +171,30 @@ def test_random_weights_are_a_function_of_seed_and_name(tmp_path):
     n = f.read("model.layers.0.input_layernorm.weight").float()
     assert abs(w.std().item() - 0.02) < 0.002 and abs(n.std().item() - 0.1) < 0.03
     f.close()
+
+
+def test_random_weights_have_the_asked_spread_and_do_not_repeat():
+    """Mean 0, the standard deviation asked for, a bell (kurtosis near 3, nothing beyond 6 deviations), no
+    correlation between neighbours, between rows or between tensors, and a prefix of a longer tensor of the same
+    name equals the shorter one (a value is a function of seed, name and index alone: chunks cannot matter)."""
+    n = (1 << 22) + 12345                              # more than one chunk of the generator
+    a = random_tensor("m.weight", TensorSpec((n,), init_std=0.02), 7, dtype=torch.float32)
+    x = (a / 0.02).double()
+    assert abs(x.mean().item()) < 3e-3 and abs(x.std().item() - 1.0) < 3e-3
+    assert 2.8 < (x ** 4).mean().item() < 3.1 and x.abs().max().item() <= 6.0
+    assert abs((x[:-1] * x[1:]).mean().item()) < 3e-3 and abs((x[:-4096] * x[4096:]).mean().item()) < 3e-3
+    b = random_tensor("n.weight", TensorSpec((n,), init_std=0.02), 7, dtype=torch.float32)
+    assert abs(((b / 0.02).double() * x).mean().item()) < 3e-3
+    short = random_tensor("m.weight", TensorSpec((1000,), init_std=0.02), 7, dtype=torch.float32)
+    assert torch.equal(short, a[:1000])
+    ints = random_tensor("t.table", TensorSpec((5000,), integer=True), 7)
+    assert ints.dtype == torch.int32 and 0 <= int(ints.min()) and int(ints.max()) < 2 ** 15 and len(ints.unique()) > 4000
+
+
+@pytest.mark.gpu
+def test_random_weights_are_the_same_bits_on_every_device():
+    for spec, dt in ((TensorSpec((300, 77), init_std=0.02), torch.bfloat16), (TensorSpec((5000,), init_std=0.1), torch.float32),
+                     (TensorSpec((64, 3), integer=True), torch.bfloat16)):
+        cpu = random_tensor("model.layers.3.x.weight", spec, 11, "cpu", dt)
+        gpu = random_tensor("model.layers.3.x.weight", spec, 11, "cuda:0", dt)
+        assert gpu.is_cuda and torch.equal(cpu, gpu.cpu())
