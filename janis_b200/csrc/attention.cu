@@ -1,10 +1,11 @@
 // Softmax attention for one head size (JANIS_HEAD_DIM, fixed when this file is
 // compiled; the library is built once per head size a model needs).
 //
-//   prefill: packed sequences of unequal lengths that start at position 0; a
-//            query sees the keys of its own sequence up to itself and, with a
-//            window, only the last `window` of them.  Keys and values are read
-//            from the step's own [T, nq + 2 nkv, hd] buffer.
+//   prefill: packed sequences of unequal lengths; a query sees the keys of its
+//            own sequence up to itself and, with a window, only the last `window`
+//            of them.  Keys and values of the step's own positions are read from
+//            the step's [T, nq + 2 nkv, hd] buffer, those of positions that earlier
+//            steps stored (a prompt that comes in several steps) from the cache.
 //   decode : one query per sequence over the paged cache (a ring for windowed
 //            layers), the key range cut into chunks that separate CTAs reduce;
 //            a second kernel merges the chunks in ascending order.
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32)
 attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ kv_src, const int* __restrict__ tok_pos,
                     const int* __restrict__ tok_seq, const int* __restrict__ seq_first_row,
                     T* __restrict__ out, int n_tok, int nq, int nkv, int q_row_heads, int kv_row_heads,
-                    int kv_k_head0, float scale, float cap, int window) {
+                    int kv_k_head0, float scale, float cap, int window, CachedPrefix cached) {
     typedef Geo<T> G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * ATTN_WARPS + warp;
@@ -156,7 +157,10 @@ attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ kv_src, con
     const int nh_here = min(G::RG, rep - hg * G::RG);
     const int lig = lane % G::LPK, grp = lane / G::LPK;
     const int pos = tok_pos[t];
-    const int first = seq_first_row[tok_seq[t]];         // row of this sequence's position 0
+    const int seq = tok_seq[t];
+    const int start = cached.seq_start ? cached.seq_start[seq] : 0;   // positions below it are in the cache
+    const int slot = cached.seq_start ? cached.seq_slot[seq] : -1;
+    const int first = seq_first_row[seq] - start;        // row that position 0 would have in the step's buffer
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
 
     Lane<T> st;
@@ -170,9 +174,15 @@ attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ kv_src, con
     for (int j0 = lo; j0 <= pos; j0 += G::KPW) {
         const int j = j0 + grp;
         const bool valid = j <= pos;
-        const T* base = kv_src + (size_t)(first + (valid ? j : pos)) * row_elems;
-        st.key(base + (size_t)(kv_k_head0 + kvh) * HD, base + (size_t)(kv_k_head0 + nkv + kvh) * HD, valid, cap,
-               lig);
+        const T* base = kv_src + (size_t)(first + (valid && j >= start ? j : pos)) * row_elems;
+        const T* kp = base + (size_t)(kv_k_head0 + kvh) * HD;
+        const T* vp = base + (size_t)(kv_k_head0 + nkv + kvh) * HD;
+        if (valid && j < start && slot >= 0) {            // stored by an earlier step
+            const size_t off = cached_row(cached, slot, j, nkv, kvh, HD);
+            kp = (const T*)cached.kpool + off;
+            vp = (const T*)cached.vpool + off;
+        }
+        st.key(kp, vp, valid, cap, lig);                  // (one call for the whole warp: it shuffles)
     }
     st.merge_groups();
     if (grp != 0) return;
@@ -316,7 +326,15 @@ constexpr int pow2_ceil(int n) { return n <= 1 ? 1 : (n <= 2 ? 2 : (n <= 4 ? 4 :
 template <typename T> struct Staged {
     static constexpr int STAGES = JANIS_STAGES;
     static constexpr int LMAX = 16, BUDGET = 32;
-    static constexpr int WARPS = clamp_int(JANIS_PAGE / Geo<T, LMAX>::KPW, 1, 8);   // a pass never exceeds a page
+    static constexpr int SMEM_LIMIT = 200 * 1024;
+    // a pass never exceeds a page; head sizes whose keys split over few lanes (many keys a warp) take fewer warps,
+    // so that the stages still fit shared memory
+    static constexpr int fit_warps() {
+        int w = clamp_int(JANIS_PAGE / Geo<T, LMAX>::KPW, 1, 8);
+        while (w > 1 && STAGES * 2 * w * Geo<T, LMAX>::KPW * HD * (int)sizeof(T) > SMEM_LIMIT) w /= 2;
+        return w;
+    }
+    static constexpr int WARPS = fit_warps();
     static constexpr int KEYS_PER_PASS = WARPS * Geo<T, LMAX>::KPW;        // keys the CTA handles at a time
     static constexpr int TILE = max_int(KEYS_PER_PASS, pow2_floor(JANIS_STAGE_BUDGET / (2 * HD * (int)sizeof(T))));
     static constexpr int TILE_BYTES = TILE * HD * (int)sizeof(T);
@@ -324,7 +342,7 @@ template <typename T> struct Staged {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;
     static_assert(TILE <= JANIS_PAGE && JANIS_PAGE % TILE == 0, "a tile must divide a page");
     static_assert(TILE % KEYS_PER_PASS == 0, "a tile must be whole passes");
-    static_assert(SMEM_BYTES <= 200 * 1024, "stages do not fit shared memory");
+    static_assert(SMEM_BYTES <= SMEM_LIMIT, "stages do not fit shared memory");
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
@@ -899,25 +917,34 @@ JANIS_EXPORT long long janis_attn_decode_scratch(int n_seq, int nq, int max_chun
 // sequence are read from row (seq_first_row + j) of kv_src, a [rows, kv_row_heads, hd]
 // buffer whose key heads start at head kv_k_head0 and value heads nkv later
 // (kv_src = qkv, kv_row_heads = nq + 2 nkv, kv_k_head0 = nq for a layer's own keys).
+// With seq_start (int32 [n_seq], tokens of each sequence that earlier steps stored) the step continues sequences:
+// seq_first_row is then the row of a sequence's first token of this step, and the keys and values of positions
+// below seq_start come from the cache line (kpool, vpool, page_table, ring_len as in janis_attn_decode).
 JANIS_EXPORT int janis_attn_prefill(const void* qkv, const void* kv_src, int dtype, const int* tok_pos,
                                     const int* tok_seq, const int* seq_first_row, void* out, int n_tok, int nq,
                                     int nkv, int q_row_heads, int kv_row_heads, int kv_k_head0, float scale,
-                                    float cap, int window, cudaStream_t stream) {
+                                    float cap, int window, const int* seq_start, const int* seq_slot,
+                                    const void* kpool, const void* vpool, const int* page_table, int table_stride,
+                                    int ring_len, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attn_prefill: %d query heads do not divide over %d key heads", nq, nkv);
+    if (seq_start != nullptr && (seq_slot == nullptr || kpool == nullptr || vpool == nullptr || page_table == nullptr))
+        return fail("attn_prefill: sequences that continue need their slots and the cache line");
+    if (ring_len % JANIS_PAGE) return fail("attn_prefill: ring length %d is not a multiple of the page", ring_len);
+    const CachedPrefix cached = {seq_start, seq_slot, kpool, vpool, page_table, table_stride, ring_len};
     const int rep = nq / nkv;
     dim3 grid((n_tok + ATTN_WARPS - 1) / ATTN_WARPS, 1, 1);
     if (dtype == JANIS_F32) {
         grid.y = nkv * ((rep + Geo<float>::RG - 1) / Geo<float>::RG);
         return launch_kernel("attn_prefill", attn_prefill_kernel<float>, grid, dim3(ATTN_WARPS * 32), 0, stream, 1,
                              (const float*)qkv, (const float*)kv_src, tok_pos, tok_seq, seq_first_row, (float*)out, n_tok, nq,
-                             nkv, q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window);
+                             nkv, q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window, cached);
     }
     if (dtype == JANIS_BF16) {
         grid.y = nkv * ((rep + Geo<bf16>::RG - 1) / Geo<bf16>::RG);
         return launch_kernel("attn_prefill", attn_prefill_kernel<bf16>, grid, dim3(ATTN_WARPS * 32), 0, stream, 1,
                              (const bf16*)qkv, (const bf16*)kv_src, tok_pos, tok_seq, seq_first_row, (bf16*)out, n_tok, nq,
-                             nkv, q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window);
+                             nkv, q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window, cached);
     }
     return fail("attn_prefill: unknown dtype %d", dtype);
 }

@@ -1,7 +1,9 @@
 // Prompt attention in bfloat16 on the tensor cores (mma.sync.m16n8k16, float
 // accumulation), one head size per compiled library (JANIS_HEAD_DIM).
 //
-// Packed sequences of unequal lengths that start at position 0.  One CTA owns BM
+// Packed sequences of unequal lengths.  They start at position 0, or (template flag EXT) go on from what
+// earlier steps stored: the keys and values of those positions are then read from the paged cache line, row by
+// row, the step's own from the step's buffer.  One CTA owns BM
 // consecutive queries of one sequence and one query head: each of its warps holds 16
 // query rows, walks the key tiles of 64 that the causal mask and the window leave,
 // and keeps the running maximum, the running sum and the unnormalised output in
@@ -77,12 +79,30 @@ __device__ __forceinline__ void load_tile(uint32_t smem, const bf16* src, size_t
     }
 }
 
+// A tile of keys (or values) whose rows before position `start` come from the cache line and the others from
+// the step's buffer; rows >= n_valid are filled with zeros.  `src` points at the row that position k0 would have.
+__device__ __forceinline__ void load_tile_mixed(uint32_t smem, const bf16* src, size_t stride, int rows, int n_valid, int k0,
+                                                int start, const CachedPrefix& cached, const bf16* pool, int slot, int nkv,
+                                                int kvh) {
+    for (int idx = threadIdx.x; idx < rows * CHUNKS; idx += THREADS) {
+        const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+        const bool ok = row < n_valid;
+        const bf16* p = src + chunk * 8;
+        if (ok) p = k0 + row < start ? pool + cached_row(cached, slot, k0 + row, nkv, kvh, HD) + chunk * 8
+                                     : p + (size_t)row * stride;
+        cp_async16(tile_addr(smem, row, chunk), p, ok);
+    }
+}
+
+// EXT: sequences may go on from what earlier steps stored (`cached`); positions are then absolute, q0 and `len`
+// count the step's own tokens of the sequence, and seq_len holds the lengths after the step.
+template <bool EXT>
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__ kv_src,
                         const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
                         bf16* __restrict__ out, int nq, int nkv, int q_row_heads, int kv_row_heads,
                         int kv_k_head0, float scale, float cap, int window, int parts, int piece,
-                        float* __restrict__ partial) {
+                        float* __restrict__ partial, CachedPrefix cached) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // Which sequence, which tile of BM queries and which part of its keys is this CTA's.  Items are handed
     // out from the end of the list: the last tiles of a sequence see the most keys and should start first.
@@ -90,10 +110,13 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     const int item = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int gtile = item / parts, part = item % parts;
     int seq = -1, q0 = 0, len = 0;
-    if (!find_tile(gtile, seq_len, n_seq, seq, q0, len)) return;
+    if (!find_tile(gtile, seq_len, n_seq, seq, q0, len, EXT ? cached.seq_start : nullptr)) return;
     const int head = blockIdx.x;
     const int kvh = head / (nq / nkv);
-    const int first = seq_first_row[seq];
+    const int first = seq_first_row[seq];             // row of the sequence's first token of this step
+    const int start = EXT ? cached.seq_start[seq] : 0;         // its position
+    const int slot = EXT ? cached.seq_slot[seq] : -1;
+    const int total = start + len;                    // keys the sequence has after the step
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
 
@@ -102,7 +125,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
 
     const size_t q_stride = (size_t)q_row_heads * HD, kv_stride = (size_t)kv_row_heads * HD;
     int k_first, n_tiles;
-    key_tiles(q0, len, window, k_first, n_tiles);
+    key_tiles(q0, len, window, k_first, n_tiles, start);
     const int np = pf::parts_of(n_tiles, parts, piece);
     const bool shared_tile = np > 1;
     if (part >= np) return;
@@ -111,14 +134,22 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
         k_first += t0 * BN;
         n_tiles = t1 - t0;
     }
-    const bf16* kbase = kv_src + (size_t)first * kv_stride + (size_t)(kv_k_head0 + kvh) * HD;
+    // the row that position 0 would have in the step's buffer (before it when the sequence goes on: never read)
+    const bf16* kbase = kv_src + ((ptrdiff_t)first - start) * (ptrdiff_t)kv_stride + (size_t)(kv_k_head0 + kvh) * HD;
     const bf16* vbase = kbase + (size_t)nkv * HD;
     auto load_kv = [&](int it) {
         const int k0 = k_first + it * BN;
         const uint32_t dst = sKV + (it & 1) * 2 * KV_BYTES;
-        const int n_keys = min(BN, len - k0);
-        load_tile(dst, kbase + (size_t)k0 * kv_stride, kv_stride, BN, n_keys);
-        load_tile(dst + KV_BYTES, vbase + (size_t)k0 * kv_stride, kv_stride, BN, n_keys);
+        const int n_keys = min(BN, total - k0);
+        if (EXT && k0 < start && slot >= 0) {
+            load_tile_mixed(dst, kbase + (ptrdiff_t)k0 * (ptrdiff_t)kv_stride, kv_stride, BN, n_keys, k0, start, cached,
+                            (const bf16*)cached.kpool, slot, nkv, kvh);
+            load_tile_mixed(dst + KV_BYTES, vbase + (ptrdiff_t)k0 * (ptrdiff_t)kv_stride, kv_stride, BN, n_keys, k0, start,
+                            cached, (const bf16*)cached.vpool, slot, nkv, kvh);
+            return;
+        }
+        load_tile(dst, kbase + (ptrdiff_t)k0 * (ptrdiff_t)kv_stride, kv_stride, BN, n_keys);
+        load_tile(dst + KV_BYTES, vbase + (ptrdiff_t)k0 * (ptrdiff_t)kv_stride, kv_stride, BN, n_keys);
     };
     load_tile(sQ, q_src + (size_t)(first + q0) * q_stride + (size_t)head * HD, q_stride, BM, min(BM, len - q0));
     load_kv(0);
@@ -135,9 +166,9 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
     const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
 
-    const int row_lo = q0 + warp * 16 + g;            // this thread's two query positions
+    const int row_lo = start + q0 + warp * 16 + g;    // this thread's two query positions
     const int row_hi = row_lo + 8;
-    const int warp_first = q0 + warp * 16, warp_last = warp_first + 15;
+    const int warp_first = start + q0 + warp * 16, warp_last = warp_first + 15;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int k0 = k_first + it * BN;
@@ -169,7 +200,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
                 }
             }
             // scale, cap, mask; scores end up in units of log2(e)
-            const bool inner = k0 + BN - 1 <= warp_first && k0 + BN <= len &&
+            const bool inner = k0 + BN - 1 <= warp_first && k0 + BN <= total &&
                                (window <= 0 || k0 > warp_last - window);   // every key seen by every row
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -180,7 +211,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
                     if (!inner) {
                         const int key = k0 + j * 8 + t * 2 + (c & 1);
                         const int row = (c & 2) ? row_hi : row_lo;
-                        const bool seen = key <= row && key < len && (window <= 0 || key > row - window);
+                        const bool seen = key <= row && key < total && (window <= 0 || key > row - window);
                         v = seen ? v : -INFINITY;
                     }
                     s[j][c] = v;
@@ -252,12 +283,12 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
         return;
     }
     const float inv_lo = 1.0f / l_run[0], inv_hi = 1.0f / l_run[1];
-    bf16* out_lo = out + (size_t)(first + row_lo) * nq * HD + (size_t)head * HD + t * 2;
-    bf16* out_hi = out + (size_t)(first + row_hi) * nq * HD + (size_t)head * HD + t * 2;
+    bf16* out_lo = out + (size_t)(first + row_lo - start) * nq * HD + (size_t)head * HD + t * 2;
+    bf16* out_hi = out + (size_t)(first + row_hi - start) * nq * HD + (size_t)head * HD + t * 2;
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
-        if (row_lo < len) *reinterpret_cast<uint32_t*>(out_lo + i * 8) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
-        if (row_hi < len) *reinterpret_cast<uint32_t*>(out_hi + i * 8) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
+        if (row_lo < total) *reinterpret_cast<uint32_t*>(out_lo + i * 8) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
+        if (row_hi < total) *reinterpret_cast<uint32_t*>(out_hi + i * 8) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
     }
 }
 
@@ -271,14 +302,14 @@ constexpr int MERGE_ROWS = 8;                         // rows of the tile per CT
 __global__ void __launch_bounds__(256)
 attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restrict__ seq_first_row,
                           const int* __restrict__ seq_len, int n_seq, bf16* __restrict__ out, int nq, int window,
-                          int parts, int piece) {
+                          int parts, int piece, const int* __restrict__ seq_start) {
     const int gtile = blockIdx.x, head = blockIdx.y;
     const int r_begin = blockIdx.z * MERGE_ROWS;
     // the step's tables were written before the attention kernel started: they are read while it still runs
     int seq = -1, q0 = 0, len = 0;
-    const bool found = find_tile(gtile, seq_len, n_seq, seq, q0, len);
+    const bool found = find_tile(gtile, seq_len, n_seq, seq, q0, len, seq_start);
     int k_first = 0, n_tiles = 0;
-    if (found) key_tiles(q0, len, window, k_first, n_tiles);
+    if (found) key_tiles(q0, len, window, k_first, n_tiles, seq_start ? seq_start[seq] : 0);
     const int np = found ? parts_of(n_tiles, parts, piece) : 1;
     const int first = found ? seq_first_row[seq] : 0;
     grid_dependents_launch();
@@ -363,19 +394,32 @@ JANIS_EXPORT void janis_attn_set_prefill_kernel(int which) { g_prefill_kernel = 
 // head kv_k_head0, value heads nkv later.  n_tiles_bound >= sum over sequences of ceil(len / tile), tile =
 // janis_attn_prefill_tile().  partial: janis_attn_prefill_scratch(n_tiles_bound, nq) floats, or null (or
 // fewer floats), in which case no tile is shared.
+// With seq_start (int32 [n_seq], tokens of each sequence that earlier steps stored) the step continues sequences:
+// seq_len then holds the lengths after the step, seq_first_row the row of a sequence's first token of this step, and
+// keys and values of positions below seq_start come from the cache line (kpool, vpool, page_table, ring_len as in
+// janis_attn_decode); such a step runs on the mma.sync kernel.
 JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, int n_tok, const int* seq_first_row,
                                         const int* seq_len, int n_seq, int n_tiles_bound, void* out, int nq,
                                         int nkv, int q_row_heads, int kv_row_heads, int kv_k_head0, float scale,
                                         float cap, int window, float* partial, long long partial_floats,
-                                        cudaStream_t stream) {
+                                        const int* seq_start, const int* seq_slot, const void* kpool, const void* vpool,
+                                        const int* page_table, int table_stride, int ring_len, cudaStream_t stream) {
     if (n_seq <= 0 || n_tiles_bound <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attn_prefill_mma: %d query heads do not divide over %d key heads", nq, nkv);
-    if (((uintptr_t)q_src | (uintptr_t)kv_src | (uintptr_t)out | (uintptr_t)partial) & 15)
+    if (((uintptr_t)q_src | (uintptr_t)kv_src | (uintptr_t)out | (uintptr_t)partial | (uintptr_t)kpool | (uintptr_t)vpool) & 15)
         return fail("attn_prefill_mma: operands must be 16-byte aligned");
+    const bool ext = seq_start != nullptr;
+    if (ext && (seq_slot == nullptr || kpool == nullptr || vpool == nullptr || page_table == nullptr))
+        return fail("attn_prefill_mma: sequences that continue need their slots and the cache line");
+    if (ring_len % JANIS_PAGE) return fail("attn_prefill_mma: ring length %d is not a multiple of the page", ring_len);
+    const CachedPrefix cached = {seq_start, seq_slot, kpool, vpool, page_table, table_stride, ring_len};
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(pf::attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(pf::attn_prefill_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              pf::SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(pf::attn_prefill_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     pf::SMEM_BYTES);
         if (e != cudaSuccess) return fail("attn_prefill_mma: shared memory of %d bytes refused: %s", pf::SMEM_BYTES,
                                           cudaGetErrorString(e));
         configured = true;
@@ -391,19 +435,22 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
     const int piece = g_prefill_piece > 0 ? g_prefill_piece : (int)std::min<long long>(16, std::max<long long>(4, share + 3));
     if ((long long)n_tiles_bound * parts > 65535) return fail("attn_prefill_mma: %d tiles of queries exceed the grid", n_tiles_bound);
     int done = -1;
-    if (g_prefill_kernel == 1)
+    if (g_prefill_kernel == 1 && !ext)                // the tcgen05 kernel takes sequences that start at position 0
         done = launch_prefill_tc05(q_src, kv_src, n_tok, seq_first_row, seq_len, n_seq, n_tiles_bound, out, nq, nkv,
                                    q_row_heads, kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial,
                                    stream);
     if (done > 0) return 1;
     if (done < 0) {
+        // (a plain launch: this kernel reads its tables and operands at its top, without the dependency wait)
         dim3 grid(nq, n_tiles_bound * parts);
-        pf::attn_prefill_mma_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
+        auto kernel = ext ? pf::attn_prefill_mma_kernel<true> : pf::attn_prefill_mma_kernel<false>;
+        kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
             (const bf16*)q_src, (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
-            kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial);
+            kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial, cached);
         if (launched("attn_prefill_mma")) return 1;
     }
     if (parts == 1) return 0;
     return launch_kernel("attn_prefill_merge", pf::attn_prefill_merge_kernel, dim3(n_tiles_bound, nq, pf::BM / pf::MERGE_ROWS), dim3(256), 0, stream, 1,
-                         (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts, piece);
+                         (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts, piece,
+                         seq_start);
 }

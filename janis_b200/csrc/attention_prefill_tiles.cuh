@@ -36,10 +36,13 @@ __device__ __forceinline__ float fast_tanh(float x) {  // 1 - 2 / (e^2x + 1); ex
     return 1.0f - 2.0f * r;
 }
 
-// The sequence and the tile of BM queries that item `tile` of the step stands for (false: none).
-__device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ seq_len, int n_seq, int& seq, int& q0, int& len) {
+// The sequence and the tile of BM queries that item `tile` of the step stands for (false: none).  `len` is the
+// number of tokens the sequence brings to this step: seq_end[s], less what earlier steps stored (seq_start[s],
+// when the step continues sequences), and q0 counts from the first of them.
+__device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ seq_end, int n_seq, int& seq, int& q0, int& len,
+                                          const int* __restrict__ seq_start = nullptr) {
     for (int s = 0; s < n_seq; ++s) {
-        const int n = seq_len[s];
+        const int n = seq_end[s] - (seq_start ? seq_start[s] : 0);
         const int nt = (n + BM - 1) / BM;
         if (tile < nt) { seq = s; q0 = tile * BM; len = n; return true; }
         tile -= nt;
@@ -47,10 +50,11 @@ __device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ seq_
     return false;
 }
 
-// Key tiles [k_first / BN, ...) that a tile of queries walks: n_tiles of them from key k_first.
-__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_first, int& n_tiles) {
-    const int q_last = min(q0 + BM, len) - 1;
-    const int j_first = window > 0 ? max(0, q0 - window + 1) : 0;
+// Key tiles [k_first / BN, ...) that a tile of queries walks: n_tiles of them from key k_first (an absolute
+// position; the step's first token stands at position `start`).
+__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_first, int& n_tiles, int start = 0) {
+    const int q_last = start + min(q0 + BM, len) - 1;
+    const int j_first = window > 0 ? max(0, start + q0 - window + 1) : 0;
     k_first = (j_first / BN) * BN;
     n_tiles = (q_last - k_first) / BN + 1;
 }

@@ -115,6 +115,26 @@ inline int launch_kernel(const char* what, void (*kernel)(KArgs...), dim3 grid, 
     return 0;
 }
 
+// Where a multi-token step finds the keys and values of positions that earlier steps stored: the paged cache line
+// ([pages, kv heads, JANIS_PAGE, head size]; position p of a sequence in page table[slot][p / JANIS_PAGE], or at
+// p % ring_len for a windowed line).  seq_start == nullptr: every sequence of the step starts at position 0 and
+// nothing is read from the cache.
+struct CachedPrefix {
+    const int* seq_start;      // [n_seq] tokens of each sequence stored before this step
+    const int* seq_slot;       // [n_seq]
+    const void* kpool;
+    const void* vpool;
+    const int* page_table;
+    int table_stride;
+    int ring_len;
+};
+
+__device__ __forceinline__ size_t cached_row(const CachedPrefix& c, int slot, int pos, int nkv, int kvh, int hd) {
+    const int idx = c.ring_len > 0 ? pos % c.ring_len : pos;
+    const int page = c.page_table[(size_t)slot * c.table_stride + idx / JANIS_PAGE];
+    return (((size_t)page * nkv + kvh) * JANIS_PAGE + idx % JANIS_PAGE) * (size_t)hd;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
 

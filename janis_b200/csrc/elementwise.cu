@@ -375,6 +375,39 @@ rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ tok_pos, cons
     }
 }
 
+// ---------------------------------------------------------------------------
+// keys and values of a step's rows into the paged cache, as a kernel of its own: a step that continues
+// sequences attends first (its windowed lines still need the places that the step's own tokens will take)
+// and stores afterwards.  Same places and the same rule for rings as the encoding kernels above.  A thread
+// copies 16 bytes; units are (token, key or value head, piece).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_store_kernel(const T* __restrict__ qkv, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                const int* __restrict__ seq_slot, const int* __restrict__ seq_end, int n_tok, int nq, int nkv, int hd,
+                int row_heads, T* __restrict__ kpool, T* __restrict__ vpool, const int* __restrict__ page_table,
+                int table_stride, int ring_len) {
+    constexpr int VEC = Vec16<T>::N;
+    const int ppr = hd / VEC;                                   // pieces per head row
+    const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    grid_dependents_launch();
+    grid_dependency_wait();
+    if (u >= (long long)n_tok * 2 * nkv * ppr) return;
+    const int pc = (int)(u % ppr), head = (int)((u / ppr) % (2 * nkv)), t = (int)(u / ((long long)ppr * 2 * nkv));
+    const int pos = tok_pos[t], seq = tok_seq[t], slot = seq_slot[seq];
+    if (slot < 0) return;
+    int idx = pos;
+    if (ring_len > 0) {
+        if (pos < seq_end[seq] - ring_len) return;              // a later token of this step takes its place
+        idx = pos % ring_len;
+    }
+    const int page = page_table[(size_t)slot * table_stride + idx / JANIS_PAGE];
+    const bool is_v = head >= nkv;
+    T* dst = (is_v ? vpool : kpool) + (((size_t)page * nkv + (is_v ? head - nkv : head)) * JANIS_PAGE + idx % JANIS_PAGE) * hd;
+    const T* src = qkv + ((size_t)t * row_heads + nq + head) * hd;
+    *reinterpret_cast<uint4*>(dst + pc * VEC) = *reinterpret_cast<const uint4*>(src + pc * VEC);
+}
+
 }  // namespace janis
 
 using namespace janis;
@@ -535,6 +568,28 @@ JANIS_EXPORT int janis_rope_store(void* qkv, int dtype, const int* tok_pos, cons
                              seq_slot, seq_end, inv_freq, rot, nq, nkv, hd, row_heads, (bf16*)kpool, (bf16*)vpool,
                              page_table, table_stride, ring_len, heads, per);
     return fail("rope_store: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_kv_store(const void* qkv, int dtype, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                const int* seq_end, int T, int nq, int nkv, int hd, int row_heads, void* kpool,
+                                void* vpool, const int* page_table, int table_stride, int ring_len, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (row_heads < nq + 2 * nkv) return fail("kv_store: rows of %d heads are too short", row_heads);
+    if (ring_len % JANIS_PAGE) return fail("kv_store: ring length %d is not a multiple of the page", ring_len);
+    if (((uintptr_t)qkv | (uintptr_t)kpool | (uintptr_t)vpool) & 15) return fail("kv_store: operands must be 16-byte aligned");
+    const int vec = dtype == JANIS_F32 ? 4 : 8;
+    if (hd % vec) return fail("kv_store: head size %d is not a multiple of %d", hd, vec);
+    const long long units = (long long)T * 2 * nkv * (hd / vec);
+    const dim3 grid((unsigned)((units + 255) / 256)), block(256);
+    if (dtype == JANIS_F32)
+        return launch_kernel("kv_store", kv_store_kernel<float>, grid, block, 0, stream, 1, (const float*)qkv, tok_pos, tok_seq,
+                             seq_slot, seq_end, T, nq, nkv, hd, row_heads, (float*)kpool, (float*)vpool, page_table,
+                             table_stride, ring_len);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("kv_store", kv_store_kernel<bf16>, grid, block, 0, stream, 1, (const bf16*)qkv, tok_pos, tok_seq,
+                             seq_slot, seq_end, T, nq, nkv, hd, row_heads, (bf16*)kpool, (bf16*)vpool, page_table,
+                             table_stride, ring_len);
+    return fail("kv_store: unknown dtype %d", dtype);
 }
 
 JANIS_EXPORT const char* janis_last_error() { return error_buffer(); }

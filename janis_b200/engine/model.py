@@ -130,6 +130,8 @@ class DecoderModel:
             nxt = self.blocks[self.schedule[idx + 1].layer].first_norm if idx + 1 < len(self.schedule) else None
             line = cache.line(call.cache_line, call.write, has_readers=call.write and self.readers[call.cache_line] > 0)
             h, y = blk.forward(h, ctx, line, y_in=y, next_norm=nxt)
+        for late in ctx.shared.pop("after_step", ()):    # what parts put off until every layer has run
+            late()
         return h
 
     def logits(self, ctx: StepContext, h: torch.Tensor, rows: torch.Tensor | None, n_rows: int,

@@ -5,6 +5,10 @@ its whole prompt; lengths may differ) or a *decode step* (every sequence brings
 exactly one token).  The step runs only the tokens it is given, packed without
 padding, against what earlier steps left in the cache, and returns float32
 logits at the places asked for, in the order of the entries and of their `want`.
+Anything else (a sequence that has started and brings several tokens: a prompt
+that comes in pieces; new sequences beside ones that go on) is a *continued
+prompt step*: it runs like a prompt step, kernel by kernel, its mixers reading
+the earlier positions from the cache (`StepContext.extends`).
 
 Prompt steps with many tokens are cut at sequence borders into pieces of at
 most `max_step_tokens`; the pieces are independent, so nothing changes but the
@@ -139,16 +143,16 @@ class Stepper:
         (the entries' token values are ignored)."""
         entries = list(entries)
         mode = self._validate(entries)
-        if mode == "prefill":
-            return self._prefill(entries)
-        return self._decode(entries, copy, tokens_on_device)
+        if mode == "decode":
+            return self._decode(entries, copy, tokens_on_device)
+        return self._prefill(entries, extends=mode == "extend")
 
     def _validate(self, entries) -> str:
         if not entries:
             raise StepError("a step needs at least one sequence")
         seen = set()
         V = self.model.vocab
-        fresh = decode = 0
+        fresh = decode = more = 0
         for e in entries:
             if e.slot is None:
                 if len(e.tokens) != 1:
@@ -177,16 +181,17 @@ class Stepper:
             elif n == 1:
                 decode += 1
             else:
-                raise StepError(f"slot {e.slot}: {n} tokens onto a sequence of {have}: a sequence that has "
-                                "started goes on one token at a time")
-        if fresh and decode:
-            raise StepError("the sequences of a step either all start or all go on by one token")
+                more += 1
         if not seen:
             raise StepError("a step of padding rows alone")
+        if more or (fresh and decode):
+            if len(seen) != len(entries):
+                raise StepError("padding rows stand in decode steps only")
+            return "extend"
         return "prefill" if fresh else "decode"
 
     # ------------------------------------------------------------------
-    def _prefill(self, entries) -> torch.Tensor | None:
+    def _prefill(self, entries, extends: bool = False) -> torch.Tensor | None:
         n_want = sum(len(e.want) for e in entries)
         out = torch.empty((n_want, self.model.vocab), dtype=torch.float32, device=self.rt.device) if n_want else None
         pieces, cur, cur_tok = [], [], 0
@@ -200,15 +205,17 @@ class Stepper:
         row0 = 0
         for piece in pieces:
             r = sum(len(e.want) for e in piece)
-            self._prefill_piece(piece, out[row0:row0 + r] if r else None)
+            self._prefill_piece(piece, out[row0:row0 + r] if r else None, extends)
             row0 += r
         return out
 
-    def _prefill_piece(self, entries, out) -> None:
+    def _prefill_piece(self, entries, out, extends: bool = False) -> None:
         n_seq = len(entries)
         lens = [len(e.tokens) for e in entries]
         T = sum(lens)
-        if self.use_graphs and T <= self.PROMPT_GRAPH_TOKENS and n_seq < self.PROMPT_GRAPH_SEQS:
+        have = [self.cache.length(e.slot) for e in entries]       # tokens that earlier steps stored
+        extends = extends and any(have)
+        if self.use_graphs and not extends and T <= self.PROMPT_GRAPH_TOKENS and n_seq < self.PROMPT_GRAPH_SEQS:
             n_want = 0 if out is None else out.shape[0]
             key = (_bucket_prompt_tokens(T), _bucket_prompt_seqs(n_seq), n_want > 0)
             if n_want <= key[1]:
@@ -217,16 +224,17 @@ class Stepper:
                 self._prompt_seen.add(key)        # a shape that never comes back is not worth a capture
         first = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
         tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        tok_pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+        tok_pos = np.concatenate([np.arange(h, h + n, dtype=np.int32) for h, n in zip(have, lens)])
         tok_seq = np.repeat(np.arange(n_seq, dtype=np.int32), lens)
         slots = np.asarray([e.slot for e in entries], dtype=np.int32)
         rows = np.concatenate([first[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries)]
                               ).astype(np.int32) if out is not None else np.zeros(0, dtype=np.int32)
-        for e, n in zip(entries, lens):
+        ends = [h + n for h, n in zip(have, lens)]
+        for e, n in zip(entries, ends):
             self.cache.reserve(e.slot, n)
         self.cache.sync()
-        host = np.concatenate([tokens, tok_pos, tok_seq, slots, np.zeros(n_seq, np.int32),
-                               np.asarray(lens, np.int32), first, rows])
+        host = np.concatenate([tokens, tok_pos, tok_seq, slots, np.asarray(have, np.int32),
+                               np.asarray(ends, np.int32), first, rows])
         dev = torch.from_numpy(host).to(self.rt.device)
         o = 0
 
@@ -238,12 +246,12 @@ class Stepper:
 
         ctx = StepContext(rt=self.rt, ws=self.ws, mode="prefill", n_tok=T, n_seq=n_seq, tokens=take(T),
                           tok_pos=take(T), tok_seq=take(T), seq_slot=take(n_seq), seq_start=take(n_seq),
-                          seq_end=take(n_seq), seq_first_row=take(n_seq), len_bound=max(lens))
+                          seq_end=take(n_seq), seq_first_row=take(n_seq), len_bound=max(ends), extends=extends)
         rows_dev = take(len(rows))
         h = self.model.forward(ctx, self.cache)
         if out is not None:
             self.model.logits(ctx, h, rows_dev, len(rows), out)
-        for e, n in zip(entries, lens):
+        for e, n in zip(entries, ends):
             self.cache.advance(e.slot, n)
 
     def _prefill_graphed(self, entries, lens, out, key) -> None:

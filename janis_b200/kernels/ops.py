@@ -56,6 +56,7 @@ def core():
         lib.janis_gated_act.argtypes = [P, P, I, I, I, I, I, P]
         lib.janis_softcap.argtypes = [P, c_longlong, F, P]
         lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
+        lib.janis_kv_store.argtypes = [P, I, P, P, P, P, I, I, I, I, I, P, P, P, I, I, P]
         lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
         lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
         lib.janis_gemv_rope_store.argtypes = [P, P, P, I, I, P, P, P, P, P, I, I, I, I, P, P, P, I, I, P]
@@ -84,9 +85,10 @@ def attention_lib(head_dim: int):
         lib.janis_attn_head_dim.restype = I
         lib.janis_attn_decode_scratch.argtypes = [I, I, I]
         lib.janis_attn_decode_scratch.restype = c_longlong
-        lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P]
+        lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P, P, P, P, P, I, I, P]
         lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
-        lib.janis_attn_prefill_mma.argtypes = [P, P, I, P, P, I, I, P, I, I, I, I, I, F, F, I, P, c_longlong, P]
+        lib.janis_attn_prefill_mma.argtypes = [P, P, I, P, P, I, I, P, I, I, I, I, I, F, F, I, P, c_longlong,
+                                               P, P, P, P, P, I, I, P]
         lib.janis_attn_set_prefill_kernel.argtypes = [I]
         lib.janis_attn_set_prefill_kernel.restype = None
         lib.janis_attn_set_prefill_piece.argtypes = [I]
@@ -239,13 +241,14 @@ def gated_act(gu, out, act: int = ACT_GELU_TANH, group: int = GATE_GROUP):
 
 
 def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot: int, nq: int, nkv: int, hd: int,
-               kpool=None, vpool=None, page_table=None, ring_len: int = 0, store: bool = True):
+               kpool=None, vpool=None, page_table=None, ring_len: int = 0, store: bool = True,
+               write_cache: bool = True):
     """Rotate q and k of qkv [T, heads, hd] (heads = q, then k, then v) in place and write k and v into
     the paged cache.
 
     kpool/vpool: [pages, nkv, PAGE, hd] of one cache line; page_table int32 [slots, pages per sequence].
     With store=False the rows hold q alone and only q is rotated (a layer that reads another layer's
-    keys)."""
+    keys).  With write_cache=False q and k are rotated and nothing is stored (`kv_store` does it later)."""
     T = qkv.shape[0]
     row_heads = nq + 2 * nkv if store else nq
     _t(qkv, "qkv", _FLOATS, (T, row_heads, hd))
@@ -255,6 +258,12 @@ def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot: int, nq:
         raise KernelError("rope_store: position tables shorter than the step")
     _t(inv_freq, "inv_freq", torch.float32, (rot // 2,))
     stride = 0
+    if store and not write_cache:
+        lib = core()
+        _check(lib, lib.janis_rope_store(qkv.data_ptr(), _DT[qkv.dtype], tok_pos.data_ptr(), tok_seq.data_ptr(), None,
+                                         None, inv_freq.data_ptr(), rot, T, nq, nkv, hd, row_heads, None, None, None,
+                                         0, 0, 0, _stream()))
+        return qkv
     if store:
         n_pages = kpool.shape[0]
         _t(kpool, "kpool", qkv.dtype, (n_pages, nkv, PAGE, hd))
@@ -270,6 +279,28 @@ def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot: int, nq:
         inv_freq.data_ptr(), rot, T, nq, nkv, hd, row_heads,
         kpool.data_ptr() if store else None, vpool.data_ptr() if store else None,
         page_table.data_ptr() if store else None, stride, ring_len, 0 if store else 1, _stream()))
+    return qkv
+
+
+def kv_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, nq: int, nkv: int, hd: int, kpool, vpool, page_table,
+             ring_len: int = 0):
+    """Write the keys and values of qkv [T, nq + 2 nkv, hd] into the paged cache line as they stand (the places
+    and the rule for rings are rope_store's): the second half of `rope_store(..., write_cache=False)`."""
+    T = qkv.shape[0]
+    _t(qkv, "qkv", _FLOATS, (T, None, hd))
+    if qkv.shape[1] < nq + 2 * nkv:
+        raise KernelError("kv_store: the rows of qkv hold no keys and values")
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", qkv.dtype, (n_pages, nkv, PAGE, hd))
+    _t(vpool, "vpool", qkv.dtype, (n_pages, nkv, PAGE, hd))
+    _t(page_table, "page_table", torch.int32, (None, None))
+    if tok_pos.numel() < T or tok_seq.numel() < T:
+        raise KernelError("kv_store: position tables shorter than the step")
+    lib = core()
+    _check(lib, lib.janis_kv_store(qkv.data_ptr(), _DT[qkv.dtype], _t(tok_pos, "tok_pos", torch.int32),
+                                   _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32),
+                                   _t(seq_end, "seq_end", torch.int32), T, nq, nkv, hd, qkv.shape[1], kpool.data_ptr(),
+                                   vpool.data_ptr(), page_table.data_ptr(), page_table.shape[1], int(ring_len), _stream()))
     return qkv
 
 
@@ -446,18 +477,44 @@ def attn_prefill_scratch_floats(n_tok: int, n_seq: int, nq: int, hd: int, dtype=
     return int(lib.janis_attn_prefill_scratch((n_tok + bm - 1) // bm + n_seq, nq))
 
 
+def _cached_args(name, seq_start, seq_slot, kpool, vpool, page_table, ring_len, dtype, n_seq, nkv, hd):
+    """The arguments that say where the keys and values of earlier steps are (all null for a step whose sequences
+    start at position 0)."""
+    if seq_start is None:
+        return (None, None, None, None, None, 0, 0)
+    if kpool is None or vpool is None or page_table is None or seq_slot is None:
+        raise KernelError(f"{name}: sequences that continue need their slots and the cache line")
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", dtype, (n_pages, nkv, PAGE, hd))
+    _t(vpool, "vpool", dtype, (n_pages, nkv, PAGE, hd))
+    _t(page_table, "page_table", torch.int32, (None, None))
+    _t(seq_start, "seq_start", torch.int32)
+    _t(seq_slot, "seq_slot", torch.int32)
+    if n_seq is not None and (seq_start.numel() < n_seq or seq_slot.numel() < n_seq):
+        raise KernelError(f"{name}: sequence tables shorter than the step")
+    return (seq_start.data_ptr(), seq_slot.data_ptr(), kpool.data_ptr(), vpool.data_ptr(), page_table.data_ptr(),
+            page_table.shape[1], int(ring_len))
+
+
 def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, hd: int, scale: float, cap: float,
                  window: int, kv_src=None, kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True,
-                 scratch=None):
-    """Causal (and windowed when window > 0) attention over packed sequences that start at position 0.
+                 scratch=None, seq_start=None, seq_slot=None, kpool=None, vpool=None, page_table=None,
+                 ring_len: int = 0):
+    """Causal (and windowed when window > 0) attention over packed sequences.
     qkv: [T, nq + 2 nkv, hd], or [T, nq, hd] when keys and values come from `kv_src`, another layer's
     [T, kv_row_heads, hd] rows whose key heads start at head kv_k_head0 (values nkv heads later).
-    bfloat16 with `seq_len` (int32 [n_seq], the sequences' lengths) runs on the tensor cores; float32
-    runs the CUDA-core kernel, which is exact 32-bit."""
+    Without `seq_start` every sequence starts at position 0 and seq_first_row is the row of that position.  With
+    `seq_start` (int32 [n_seq], the tokens earlier steps stored) the step continues sequences: tok_pos are absolute
+    positions, seq_first_row is the row of a sequence's first token of this step, `seq_len` the lengths after the
+    step, and the keys and values of earlier positions are read from the cache line (kpool, vpool, page_table,
+    ring_len), which must still hold what those steps left (this step's own keys are stored afterwards).
+    bfloat16 with `seq_len` (int32 [n_seq]) runs on the tensor cores; float32 runs the CUDA-core kernel, which is
+    exact 32-bit."""
     T = qkv.shape[0]
     if qkv.dtype == torch.bfloat16 and seq_len is not None and tensor_cores:
         return _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src,
-                                 kv_row_heads, kv_k_head0, scratch)
+                                 kv_row_heads, kv_k_head0, scratch,
+                                 (seq_start, seq_slot, kpool, vpool, page_table, ring_len))
     if kv_src is None:
         _t(qkv, "qkv", _FLOATS, (T, nq + 2 * nkv, hd))
         kv_src, kv_row_heads, kv_k_head0 = qkv, nq + 2 * nkv, nq
@@ -470,17 +527,19 @@ def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, h
     if kv_k_head0 + 2 * nkv > kv_row_heads:
         raise KernelError("attn_prefill: key/value heads lie outside the rows of kv_src")
     _t(out, "out", qkv.dtype, (T, nq * hd))
+    cached = _cached_args("attn_prefill", seq_start, seq_slot, kpool, vpool, page_table, ring_len, qkv.dtype,
+                          seq_first_row.numel(), nkv, hd)
     lib = attention_lib(hd)
     _check(lib, lib.janis_attn_prefill(qkv.data_ptr(), kv_src.data_ptr(), _DT[qkv.dtype],
                                        _t(tok_pos, "tok_pos", torch.int32), _t(tok_seq, "tok_seq", torch.int32),
                                        _t(seq_first_row, "seq_first_row", torch.int32), out.data_ptr(), T, nq, nkv,
                                        q_row_heads, kv_row_heads, kv_k_head0, float(scale), float(cap),
-                                       int(window), _stream()))
+                                       int(window), *cached, _stream()))
     return out
 
 
 def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src, kv_row_heads,
-                      kv_k_head0, scratch=None):
+                      kv_k_head0, scratch=None, cached=(None,) * 5 + (0,)):
     T = qkv.shape[0]
     if kv_src is None:
         _t(qkv, "qkv", torch.bfloat16, (T, nq + 2 * nkv, hd))
@@ -496,6 +555,7 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
     n_seq = seq_len.numel()
     _t(seq_len, "seq_len", torch.int32, (n_seq,))
     _t(seq_first_row, "seq_first_row", torch.int32, (n_seq,))
+    cached = _cached_args("attn_prefill", *cached, torch.bfloat16, n_seq, nkv, hd)
     lib = attention_lib(hd)
     bm = lib.janis_attn_prefill_tile()      # queries per CTA
     tiles = (T + bm - 1) // bm + n_seq      # >= sum of ceil(len / bm)
@@ -506,7 +566,7 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
                                            seq_len.data_ptr(), n_seq, tiles, out.data_ptr(), nq, nkv,
                                            qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),
                                            int(window), _t(scratch, "scratch", torch.float32) if scratch is not None else None,
-                                           scratch.numel() if scratch is not None else 0, _stream()),
+                                           scratch.numel() if scratch is not None else 0, *cached, _stream()),
            2 if scratch is not None else 1)
     return out
 

@@ -12,7 +12,11 @@ causal only and ignores the cache offset, `gemma/gemma.go:232-240`).
 The three projections are one product over the rows q | k | v concatenated at
 load; the names on disk stay as they are.  A prompt step reads keys and values
 from the step's own buffer (a windowed layer may see a prompt longer than its
-ring holds); a decode step reads the paged cache.
+ring holds); a decode step reads the paged cache.  A step that continues
+sequences with several tokens (`ctx.extends`: a prompt that comes in pieces, as
+the reference's session feeds it, `qwen/session.go:272-303`) reads the earlier
+positions from the cache and its own from the step's buffer, and stores its
+own only afterwards: a ring still needs the places they will take.
 """
 from __future__ import annotations
 
@@ -100,21 +104,35 @@ class SoftmaxAttention(Mixer):
         # a written line that later layers read keeps its step buffer until the step ends
         name = f"attn.qkv.line{line.index}" if (own and line.has_readers and ctx.mode == "prefill") else "attn.qkv"
         qkv = ws.buf(name, (T, heads, hd), rt.dtype)
-        self.position.project_encode_store(x, self.w_qkv if own else self.w_q, qkv, ctx, nq, nkv, hd, kv)
+        extends = ctx.mode == "prefill" and ctx.extends
+        if extends:                                   # attend first, store afterwards
+            rt.linear(x, self.w_qkv if own else self.w_q, qkv.view(T, -1))
+            self.position.encode(qkv, ctx, nq, nkv, hd, own)
+        else:
+            self.position.project_encode_store(x, self.w_qkv if own else self.w_q, qkv, ctx, nq, nkv, hd, kv)
         att = ws.buf("attn.ctx", (T, nq * hd), rt.dtype)
         if ctx.mode == "prefill":
             n_scratch = ops.attn_prefill_scratch_floats(T, ctx.n_seq, nq, hd, rt.dtype)
             scratch = ws.buf("attn.prefill_partial", (n_scratch,), torch.float32) if n_scratch else None
+            before = dict(seq_start=ctx.seq_start, seq_slot=ctx.seq_slot, kpool=kv.k, vpool=kv.v, page_table=kv.table,
+                          ring_len=kv.ring_len) if extends else {}
             if own:
                 if line.has_readers:
                     ctx.shared[("kv", line.index)] = (qkv, heads, nq)
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
-                                 self.softcap, self.window, seq_len=ctx.seq_end, scratch=scratch)
+                                 self.softcap, self.window, seq_len=ctx.seq_end, scratch=scratch, **before)
             else:
                 src, src_heads, k0 = ctx.shared[("kv", line.index)]
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
                                  self.softcap, self.window, kv_src=src, kv_row_heads=src_heads, kv_k_head0=k0,
-                                 seq_len=ctx.seq_end, scratch=scratch)
+                                 seq_len=ctx.seq_end, scratch=scratch, **before)
+            if extends and own:
+                store = lambda: ops.kv_store(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.seq_end, nq, nkv, hd,
+                                             kv.k, kv.v, kv.table, kv.ring_len)
+                if line.has_readers:                  # the layers that read this line want it as the step found it
+                    ctx.shared.setdefault("after_step", []).append(store)
+                else:
+                    store()
         else:
             chunk, max_chunks = self._decode_geometry(ctx, rt.sm_count)
             scratch = ws.buf("attn.partial", (ops.attn_decode_scratch_floats(ctx.n_seq, nq, hd, max_chunks),),

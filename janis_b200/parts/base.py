@@ -14,8 +14,10 @@ sequence after sequence without padding):
 * `Norm.forward(x, ctx, out, rows=None)`; `Norm.residual_add(h, r, ctx,
   next_norm=None, out=None)`: h += norm(r) on the float32 residual stream, and
   out = next_norm(h) when asked.
-* `PositionEncoding.encode_and_store(qkv, ctx, nq, nkv, hd, kv_line)`: encode
-  queries and keys in place and write keys and values into the cache line.
+* `PositionEncoding.encode(qkv, ctx, nq, nkv, hd, with_keys)`: encode queries
+  (and keys) in place; `encode_and_store(qkv, ctx, nq, nkv, hd, kv_line)`: the
+  same and write keys and values into the cache line (by default `encode`
+  followed by the plain store; an encoding with a fused kernel overrides it).
 * `Mixer.cache_needs()` -> {name: KVNeed | StateNeed}; `Mixer.forward(x, ctx,
   line)` -> [T, hidden] in the activation dtype.  `line[name]` is the cache part
   it asked for; `line.write` is False when the schedule lets it only read.
@@ -122,7 +124,7 @@ class StepContext:
     """One step's batch as the parts see it."""
     rt: Runtime
     ws: Workspace
-    mode: str                       # "prefill": sequences start at 0; "decode": one token each
+    mode: str                       # "prefill": one or more tokens a sequence, packed; "decode": one token each
     n_tok: int
     n_seq: int
     tokens: torch.Tensor            # int32 [T]
@@ -131,8 +133,11 @@ class StepContext:
     seq_slot: torch.Tensor          # int32 [n_seq] cache slot, < 0 for padding
     seq_start: torch.Tensor         # int32 [n_seq] tokens cached before the step
     seq_end: torch.Tensor           # int32 [n_seq] tokens cached after the step
-    seq_first_row: torch.Tensor     # int32 [n_seq] row of the sequence's position 0 in the packed step
+    seq_first_row: torch.Tensor     # int32 [n_seq] row of the sequence's first token of this step in the packed step
     len_bound: int = 0              # host-side bound on max(seq_end); sizes the decode grids
+    extends: bool = False           # a "prefill" step some of whose sequences have tokens in the cache already
+                                    # (seq_start > 0): a mixer reads those from its cache line and stores this
+                                    # step's own only after it has attended
     shared: dict = field(default_factory=dict)   # scratch that parts of one step hand to each other
 
 
@@ -162,8 +167,19 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    def encode(self, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, with_keys: bool):
+        """Encode the queries of qkv [T, heads, hd] (and the keys behind them when with_keys) in place; store
+        nothing.  A step that continues sequences attends before it stores, so it needs the two apart."""
+        raise NotImplementedError(f"{type(self).__name__} has no encode(): it cannot take a step that continues "
+                                  "sequences with several tokens")
+
     def encode_and_store(self, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, kv_line):
-        raise NotImplementedError
+        own = kv_line is not None and kv_line.write
+        self.encode(qkv, ctx, nq, nkv, hd, own)
+        if own:
+            ctx.rt.ops.kv_store(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.seq_end, nq, nkv, hd, kv_line.k,
+                                kv_line.v, kv_line.table, kv_line.ring_len)
+        return qkv
 
     def project_encode_store(self, x, w, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, kv_line):
         """qkv [T, heads, hd] = x w^T, then encode_and_store.  An encoding whose kernels can do all of it at once

@@ -39,6 +39,10 @@ class RotaryEncoding(PositionEncoding):
     def load(self, store, rt: Runtime):
         self.inv_freq = torch.from_numpy(self._inv_host.copy()).to(rt.device)
 
+    def encode(self, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, with_keys: bool):
+        return ctx.rt.ops.rope_store(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.seq_end, self.inv_freq, self.rot,
+                                     nq, nkv, hd, store=with_keys, write_cache=False)
+
     def encode_and_store(self, qkv, ctx: StepContext, nq: int, nkv: int, hd: int, kv_line):
         ops = ctx.rt.ops
         if kv_line is None or not kv_line.write:

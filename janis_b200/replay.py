@@ -7,8 +7,10 @@ per line:
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
 
 `entries` gives each request's next tokens and the places among them whose logits
-are wanted; a request gets a cache slot when it first appears; the requests of a
-step either all start or all go on by one token.  `end` names requests that are
+are wanted; a request gets a cache slot when it first appears.  The usual trace
+has steps whose requests either all start or all go on by one token; a request
+that has started may also bring several tokens (a prompt that comes in pieces),
+beside others that start or go on.  `end` names requests that are
 finished after the step: their slots are given back.  For a step in which
 something is wanted, `<out>/<step>.f32` receives the logits, little-endian
 float32 [wanted, vocab], in the order of the entries and of `want`.  After every

@@ -62,7 +62,7 @@ def gated_act(gu, out, act=ACT_GELU_TANH, group=GATE_GROUP):
 
 
 def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot, nq, nkv, hd, kpool=None, vpool=None,
-               page_table=None, ring_len=0, store=True):
+               page_table=None, ring_len=0, store=True, write_cache=True):
     T = qkv.shape[0]
     half = rot // 2
     n_rot = nq + nkv if store else nq
@@ -72,8 +72,13 @@ def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot, nq, nkv,
         a, b = qkv[:, :n_rot, :half].double(), qkv[:, :n_rot, half:rot].double()
         qkv[:, :n_rot, :half] = (a * c - b * s).to(qkv.dtype)
         qkv[:, :n_rot, half:rot] = (a * s + b * c).to(qkv.dtype)
-    if not store:
+    if not store or not write_cache:
         return qkv
+    return kv_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, nq, nkv, hd, kpool, vpool, page_table, ring_len)
+
+
+def kv_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, nq, nkv, hd, kpool, vpool, page_table, ring_len=0):
+    T = qkv.shape[0]
     for t in range(T):
         seq = int(tok_seq[t])
         slot = int(seq_slot[seq])
@@ -162,17 +167,28 @@ def attn_prefill_scratch_floats(n_tok, n_seq, nq, hd, dtype=torch.bfloat16):
 
 
 def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq, nkv, hd, scale, cap, window, kv_src=None,
-                 kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True, scratch=None):
+                 kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True, scratch=None, seq_start=None,
+                 seq_slot=None, kpool=None, vpool=None, page_table=None, ring_len=0):
     T = qkv.shape[0]
     if kv_src is None:
         kv_src, kv_k_head0 = qkv, nq
     for t in range(T):
         pos = int(tok_pos[t])
-        first = int(seq_first_row[int(tok_seq[t])])
+        seq = int(tok_seq[t])
+        start = int(seq_start[seq]) if seq_start is not None else 0
+        first = int(seq_first_row[seq]) - start           # the row position 0 would have
         lo = max(0, pos - window + 1) if window > 0 else 0
-        rows = kv_src[first + lo:first + pos + 1]
-        o = _attend(qkv[t, :nq].cpu(), rows[:, kv_k_head0:kv_k_head0 + nkv].cpu(),
-                    rows[:, kv_k_head0 + nkv:kv_k_head0 + 2 * nkv].cpu(), scale, cap)
+        ks, vs = [], []
+        if lo < start:                                    # keys and values that earlier steps stored
+            slot = int(seq_slot[seq])
+            idx = [(j % ring_len if ring_len > 0 else j) for j in range(lo, start)]
+            pages = [int(page_table[slot, i // PAGE]) for i in idx]
+            ks.append(torch.stack([kpool[p, :, i % PAGE] for p, i in zip(pages, idx)]).cpu())
+            vs.append(torch.stack([vpool[p, :, i % PAGE] for p, i in zip(pages, idx)]).cpu())
+        rows = kv_src[first + max(lo, start):first + pos + 1]
+        ks.append(rows[:, kv_k_head0:kv_k_head0 + nkv].cpu())
+        vs.append(rows[:, kv_k_head0 + nkv:kv_k_head0 + 2 * nkv].cpu())
+        o = _attend(qkv[t, :nq].cpu(), torch.cat(ks), torch.cat(vs), scale, cap)
         out[t] = o.reshape(-1).to(out.dtype)
     return out
 

@@ -193,6 +193,66 @@ def test_a_prompt_step_cut_into_pieces(on, dtype, engines, plain_models):
     eng.cache.audit()
 
 
+@pytest.mark.parametrize("on,dtype", CASES)
+@pytest.mark.parametrize("chunk", [7, 64, 100])
+def test_a_prompt_that_comes_in_pieces(on, dtype, chunk, engines, plain_models):
+    """A prompt fed in steps of `chunk` tokens onto what the steps before left in the cache (the reference's
+    session feeds its prompt so, `qwen/session.go:272-303`): the logits at every position are the plain model's
+    over the whole sequence.  Pieces end inside, on and beyond a cache page, straddle the windows (8, 16, 40: a
+    piece is longer than a ring's window, and shorter), two requests of unequal lengths run side by side, the
+    shorter ends earlier, tokens one by one follow over the same cache, and the slots are used again."""
+    from janis_b200 import StepEntry
+    for key in (["A_hot", "B_hot", "C"] if on == "cuda" else ["B"]):
+        V = vocab_of(key)
+        eng = engines(key, dtype, on, max_tokens=1024)
+        for round_ in range(2):
+            lens = [230 + round_, 93]
+            reqs = [random_tokens(V, n + 3, 1700 + 10 * round_ + i) for i, n in enumerate(lens)]
+            got = [[] for _ in reqs]
+            slots = [eng.alloc_slot() for _ in reqs]
+            pos = [0, 0]
+            while any(p < n for p, n in zip(pos, lens)):
+                live = [i for i in range(len(reqs)) if pos[i] < lens[i]]
+                take = [min(chunk, lens[i] - pos[i]) for i in live]
+                out = eng.step([StepEntry(slots[i], reqs[i][pos[i]:pos[i] + t], list(range(t))) for i, t in zip(live, take)])
+                o = 0
+                for i, t in zip(live, take):
+                    got[i].append(out[o:o + t].cpu())
+                    o += t
+                    pos[i] += t
+            for t in range(3):
+                out = eng.step([StepEntry(slots[i], [reqs[i][lens[i] + t]], [0]) for i in range(len(reqs))])
+                for i in range(len(reqs)):
+                    got[i].append(out[i:i + 1].cpu())
+            for i, r in enumerate(reqs):
+                assert_logits(torch.cat(got[i]), plain_logits(plain_models, key, r), dtype,
+                              f"{key} pieces of {chunk}, round {round_}, request {i}")
+            for sl in slots:
+                eng.free_slot(sl)
+            eng.cache.audit()
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_new_sequences_beside_ones_that_go_on(on, dtype, engines, plain_models):
+    """One step that starts a sequence, continues another by several tokens and a third by one token."""
+    from janis_b200 import StepEntry
+    key = "B_hot" if on == "cuda" else "B"
+    V = vocab_of(key)
+    eng = engines(key, dtype, on, max_tokens=1024)
+    reqs = [random_tokens(V, n, 1800 + i) for i, n in enumerate((90, 50, 30))]
+    want = [plain_logits(plain_models, key, r) for r in reqs]
+    s0, s1, s2 = (eng.alloc_slot() for _ in range(3))
+    eng.step([StepEntry(s0, reqs[0][:41], []), StepEntry(s1, reqs[1][:20], [])])
+    out = eng.step([StepEntry(s0, reqs[0][41:90], list(range(49))), StepEntry(s1, [reqs[1][20]], [0]),
+                    StepEntry(s2, reqs[2], [0, 29])])
+    assert_logits(out[:49], want[0][41:90], dtype, f"{key} mixed step, continued by 49")
+    assert_logits(out[49:50], want[1][20:21], dtype, f"{key} mixed step, continued by 1")
+    assert_logits(out[50:], want[2][[0, 29]], dtype, f"{key} mixed step, new")
+    for sl in (s0, s1, s2):
+        eng.free_slot(sl)
+    eng.cache.audit()
+
+
 @GPU
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graphs_and_plain_launches_agree(dtype, model_dirs, plain_models):

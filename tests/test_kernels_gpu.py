@@ -558,6 +558,60 @@ def test_attn_prefill_ignores_rows_that_are_not_a_sequences_own(nq, nkv, hd, win
     assert ops().attn_tc05_timeouts(hd) == 0
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 16), (6, 1, 32), (2, 2, 64), (8, 4, 256), (3, 1, 80), (2, 1, 272)])
+@pytest.mark.parametrize("window,ring,cap", [(0, 0, 30.0), (40, 64, 20.0), (128, 128, 0.0), (100, 128, 50.0)])
+def test_attn_prefill_continues_from_the_cache(nq, nkv, hd, window, ring, cap):
+    """Sequences that bring several tokens onto what earlier steps stored: the earlier positions come from the
+    paged cache (a ring for windowed lines, as the steps before left it), this step's own from the step's
+    buffer.  Starts inside, on and beyond a page and a ring, a sequence that starts at 0 beside them, a step
+    longer than the window and than the ring, pages scattered, and a far cached key that must win where it is
+    visible.  CUDA-core kernel in both dtypes, mma.sync in bfloat16 (the tcgen05 kernel is not for such steps);
+    with and without shared tiles."""
+    starts = [0, 5, 64, 200, 130, 63]
+    news = [70, 9, 1, 150, 260, 129]
+    slots = [2, 0, 5, 1, 3, 4]
+    n_seq = len(starts)
+    T = sum(news)
+    pages_per_seq = (ring // R.PAGE) if ring else 8
+    n_pages = 6 * pages_per_seq + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(5))[:6 * pages_per_seq].view(6, pages_per_seq).int()
+    first = torch.tensor([0] + list(np.cumsum(news)[:-1]), dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, news)]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(n_seq), torch.tensor(news)).int()
+    seq_start, seq_slot = torch.tensor(starts, dtype=torch.int32), torch.tensor(slots, dtype=torch.int32)
+    seq_end = torch.tensor([s + n for s, n in zip(starts, news)], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    d = dev()
+    for dtype in DTYPES:
+        k, v = _paged(n_pages, nkv, hd, dtype, 60)
+        qkv = rnd((T, nq + 2 * nkv, hd), dtype, 62)
+        # position 3 of the sequence that starts at 200 (slot 1) answers head 0 of its last query, where it is seen
+        far = 3 % ring if ring else 3
+        k[perm[1, far // R.PAGE].item(), 0, far % R.PAGE] = (qkv[int(first[3]) + 149, 0] * 3.0).to(dtype)
+        want = torch.empty((T, nq * hd), dtype=torch.float64)
+        R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, scale, cap, window, seq_start=seq_start,
+                       seq_slot=seq_slot, kpool=k.cpu(), vpool=v.cpu(), page_table=perm, ring_len=ring)
+        cached = dict(seq_start=seq_start.to(d), seq_slot=seq_slot.to(d), kpool=k, vpool=v, page_table=perm.to(d), ring_len=ring)
+        out = torch.full((T, nq * hd), 9.0, dtype=dtype, device=d)
+        ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, scale, cap, window,
+                           tensor_cores=False, **cached)
+        close(out, want, tol_of(dtype), f"continued prompt, CUDA cores, {dtype}")
+        if dtype == torch.bfloat16:
+            n = ops().attn_prefill_scratch_floats(T, n_seq, nq, hd)
+            for scratch in ([torch.full((n,), float("nan"), dtype=torch.float32, device=d)] if n else []) + [None]:
+                out = torch.full((T, nq * hd), 9.0, dtype=dtype, device=d)
+                ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, scale, cap, window,
+                                   seq_len=seq_end.to(d), scratch=scratch, **cached)
+                close(out, want, 2 * BF16_TOL, f"continued prompt, mma.sync, scratch {scratch is not None}")
+        # and the store that follows such a step: the same places and ring rule as the fused encoding kernel
+        k2, v2 = k.clone(), v.clone()
+        ops().kv_store(qkv, tok_pos.to(d), tok_seq.to(d), seq_slot.to(d), seq_end.to(d), nq, nkv, hd, k2, v2, perm.to(d), ring)
+        kr, vr = k.cpu().clone(), v.cpu().clone()
+        R.kv_store(qkv.cpu(), tok_pos, tok_seq, seq_slot, seq_end, nq, nkv, hd, kr, vr, perm, ring)
+        same(k2.cpu(), kr, "kv_store keys")
+        same(v2.cpu(), vr, "kv_store values")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attn_prefill_reads_another_layers_keys(dtype):
     nq, nkv, hd = 4, 2, 32
@@ -617,6 +671,50 @@ def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, kernel):
     R.attn_decode(qkv.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, scale, cap, window,
                   ring, chunk, max_chunks)
     close(out, want, tol_of(dtype), "attn_decode")
+
+
+@pytest.mark.parametrize("hd", [144, 272, 496])
+def test_attention_at_head_sizes_between_the_usual_ones(hd):
+    """Head sizes whose 16-byte pieces do not divide evenly over a warp's lanes (the staged decode kernel then
+    takes fewer warps so that its stages fit shared memory) and sizes beyond 256 (tiles of 32 keys in the prompt
+    kernel, no tensor-core decode kernel): every kernel that takes them, both dtypes."""
+    nq, nkv = 4, 2
+    lens, slots = [70, 1, 200], [1, 2, 0]
+    n_seq, pages_per_seq = 3, 4
+    perm = torch.randperm(14, generator=torch.Generator().manual_seed(9))[:12].view(3, 4).int()
+    d = dev()
+    scale, cap = 1.0 / math.sqrt(hd), 25.0
+    seq_slot, seq_len = torch.tensor(slots, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32)
+    for dtype in DTYPES:
+        k, v = _paged(14, nkv, hd, dtype, 70)
+        q = rnd((n_seq, nq + 2 * nkv, hd), dtype, 72)
+        want = torch.empty((n_seq, nq * hd), dtype=torch.float64)
+        R.attn_decode(q.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, scale, cap, 0, 0, 64, 4)
+        scratch = torch.empty(ops().attn_decode_scratch_floats(n_seq, nq, hd, 4), dtype=torch.float32, device=d)
+        try:
+            for kernel in (2, 1, 0):
+                ops().attn_set_decode_kernel(hd, kernel)
+                out = torch.full((n_seq, nq * hd), 7.0, dtype=dtype, device=d)
+                ops().attn_decode(q, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
+                                  0, 0, 64, 4)
+                close(out, want, tol_of(dtype), f"attn_decode kernel {kernel} at head size {hd}, {dtype}")
+        finally:
+            ops().attn_set_decode_kernel(hd, 2)
+        T = sum(lens)
+        first = torch.tensor([0, 70, 71], dtype=torch.int32)
+        tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+        tok_seq = torch.repeat_interleave(torch.arange(n_seq), torch.tensor(lens)).int()
+        qkv = rnd((T, nq + 2 * nkv, hd), dtype, 74)
+        want = torch.empty((T, nq * hd), dtype=torch.float64)
+        R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, scale, cap, 50)
+        out = torch.full((T, nq * hd), 7.0, dtype=dtype, device=d)
+        ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, scale, cap, 50, tensor_cores=False)
+        close(out, want, tol_of(dtype), f"attn_prefill on CUDA cores at head size {hd}, {dtype}")
+        if dtype == torch.bfloat16:
+            out = torch.full((T, nq * hd), 7.0, dtype=dtype, device=d)
+            ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, scale, cap, 50, seq_len=seq_len.to(d))
+            close(out, want, 2 * BF16_TOL, f"attn_prefill on tensor cores at head size {hd}")
+    assert ops().attn_wait_timeouts(hd) == 0
 
 
 @pytest.mark.parametrize("window,ring", [(0, 0), (1024, 1024)])
