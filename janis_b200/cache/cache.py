@@ -226,11 +226,15 @@ class ModelCache:
                     st_lines.setdefault(need, []).append(i)
                 else:
                     raise CacheError(f"cache line {i}: unknown need {need!r} for {name!r}")
+        group_pages = {}
         for need, lines in kv_lines.items():
             n_pages = self.n_pages
             if need.window:
                 n_pages = min(n_pages, self.n_slots * (round_up(need.window, PAGE) // PAGE))
-            self.kv_groups[need] = KVGroup(need, lines, n_pages, self.n_slots, max_ctx, dtype, device)
+            group_pages[need] = n_pages
+        self._check_room(kv_lines, st_lines, group_pages, max_tokens, dtype, device)
+        for need, lines in kv_lines.items():
+            self.kv_groups[need] = KVGroup(need, lines, group_pages[need], self.n_slots, max_ctx, dtype, device)
         for need, lines in st_lines.items():
             self.state_groups[need] = StateGroup(need, lines, self.n_slots, device)
         for i, needs in enumerate(line_needs):
@@ -241,6 +245,33 @@ class ModelCache:
             self._line_parts.append(parts)
         self._free_slots = list(range(self.n_slots - 1, -1, -1))
         self._live: dict[int, int] = {}            # slot -> length
+
+    def _check_room(self, kv_lines, st_lines, group_pages, max_tokens, dtype, device) -> None:
+        """Refuse, with the sizes, a cache that the device has no room for (before anything is allocated)."""
+        item = torch.empty((), dtype=dtype).element_size()
+        sizes = []
+        for need, lines in kv_lines.items():
+            b = 2 * len(lines) * group_pages[need] * need.n_kv_heads * PAGE * need.head_dim * item
+            kind = f"window {need.window}" if need.window else "all positions"
+            sizes.append((f"{len(lines)} lines of {need.n_kv_heads} x {need.head_dim} keys and values, {kind}", b))
+        for need, lines in st_lines.items():
+            n = 1
+            for d in need.shape:
+                n *= int(d)
+            b = len(lines) * self.n_slots * n * torch.empty((), dtype=need.dtype).element_size()
+            sizes.append((f"{len(lines)} lines of state {tuple(need.shape)}", b))
+        self.planned_bytes = sum(b for _, b in sizes)
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            return
+        free, total = torch.cuda.mem_get_info(dev)
+        free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)     # what the allocator holds unused
+        if self.planned_bytes > free:
+            gib = lambda b: f"{b / 2 ** 30:.2f} GiB"
+            parts = "; ".join(f"{what}: {gib(b)}" for what, b in sizes)
+            raise CacheFull(f"a cache of {max_tokens} tokens ({self.n_pages} pages, {self.n_slots} sequences) needs "
+                            f"{gib(self.planned_bytes)} ({parts}); the device has {gib(free)} free of {gib(total)} "
+                            "(the rest holds the weights and other allocations): ask for fewer tokens")
 
     # -- slots ------------------------------------------------------------
     @property

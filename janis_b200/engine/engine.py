@@ -226,9 +226,9 @@ def open(model_dir: str, dtype="bfloat16", max_tokens: int = 8192, max_batch: in
     raw = read_config_json(model_dir)
     _, cfg, model = build_model(raw, os.path.join(model_dir, "config.json"))
     rt = _runtime(dtype, device)
-    tensors = load_tensors(model_dir, model.tensor_specs(), rt.device, model.ignorable_tensors)
-    model.load(WeightStore(tensors), rt)
-    del tensors
+    store = WeightStore(load_tensors(model_dir, model.tensor_specs(), rt.device, model.ignorable_tensors))
+    model.load(store, rt)         # parts that fuse tensors give the stored ones up as they go
+    del store
     return Engine(model, rt, max_tokens, max_batch, max_context, max_step_tokens, use_graphs)
 
 
@@ -241,9 +241,9 @@ def from_config(raw_config: dict, seed: int = 0, dtype="bfloat16", max_tokens: i
     """An engine with random weights drawn on the device from (seed, tensor name): no folder is written."""
     _, cfg, model = build_model(raw_config, "config")
     rt = _runtime(dtype, device)
-    tensors = random_tensors(model.tensor_specs(), seed, rt.device)
-    model.load(WeightStore(tensors), rt)
-    del tensors
+    store = WeightStore(random_tensors(model.tensor_specs(), seed, rt.device))
+    model.load(store, rt)
+    del store
     return Engine(model, rt, max_tokens, max_batch, max_context, max_step_tokens, use_graphs)
 
 

@@ -69,6 +69,8 @@ class SoftmaxAttention(Mixer):
                              f"(hidden {self.hidden}, heads x head size {self.n_heads * self.head_dim})")
         q, k, v = (store.get(self.names[n], rt.dtype) for n in ("q", "k", "v"))
         self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+        del q, k, v
+        store.drop(self.names["q"], self.names["k"], self.names["v"])      # the fused copy is the one that stays
         self.w_q = self.w_qkv[: self.n_heads * self.head_dim]      # a layer that only reads keys projects q alone
         self.w_o = store.get(self.names["o"], rt.dtype).contiguous()
         self.position.load(store, rt)

@@ -218,7 +218,11 @@ class WeightStore:
         self._conv: dict[tuple[str, torch.dtype], torch.Tensor] = {}
 
     def get(self, name: str, dtype: torch.dtype | None = None) -> torch.Tensor:
-        t = self._raw[name]
+        try:
+            t = self._raw[name]
+        except KeyError:
+            raise KeyError(f"tensor {name!r} is not in the store (never loaded, or given up by the part that "
+                           "fused it into a layout of its own)") from None
         if dtype is None or t.dtype == dtype:
             return t
         key = (name, dtype)
@@ -226,9 +230,13 @@ class WeightStore:
             self._conv[key] = t.to(dtype)
         return self._conv[key]
 
-    def drop(self, name: str) -> None:
-        """Forget the stored form of a tensor whose user keeps a fused or converted copy."""
-        self._raw.pop(name, None)
+    def drop(self, *names: str) -> None:
+        """Forget the stored form (and its conversions) of tensors whose only user keeps a fused copy: a model
+        must not sit in memory twice once it is loaded."""
+        for name in names:
+            self._raw.pop(name, None)
+            for key in [k for k in self._conv if k[0] == name]:
+                del self._conv[key]
 
     def names(self):
         return list(self._raw)

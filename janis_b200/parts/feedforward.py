@@ -55,6 +55,8 @@ class GatedMLP(FeedForward):
         I, H, G = self.intermediate, self.hidden, self.GROUP
         fused = torch.stack([g.view(I // G, G, H), u.view(I // G, G, H)], dim=1)   # [I/G, 2, G, H]
         self.w_gu = fused.reshape(2 * I, H).contiguous()
+        del g, u, fused
+        store.drop(self.names["gate"], self.names["up"])                   # the fused copy is the one that stays
         self.w_down = store.get(self.names["down"], rt.dtype).contiguous()
 
     def forward(self, x, ctx: StepContext):

@@ -39,7 +39,17 @@ TINY_C = dict(
     rope_theta=20000.0, sliding_window=40, query_pre_attn_scalar=48, attn_logit_softcapping=30.0,
     final_logit_softcapping=20.0, rms_norm_eps=1e-6, max_position_embeddings=768, eos_token_id=2)
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# a window that is a whole number of cache pages (as the real 4096 is): the ring is exactly the window, two pages
+# with a page-table entry each, and prompts longer than two rings and decoding across the wrap go through the
+# cache's page arithmetic, the decode geometry and the graphs' length buckets together; as many key/value heads as
+# query heads, an odd vocabulary
+TINY_D = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2", hidden_size=72, num_hidden_layers=3,
+    num_attention_heads=3, num_key_value_heads=3, head_dim=48, intermediate_size=200, vocab_size=211,
+    rope_theta=10000.0, sliding_window=128, query_pre_attn_scalar=48, attn_logit_softcapping=25.0,
+    final_logit_softcapping=12.0, rms_norm_eps=1e-6, max_position_embeddings=1024, eos_token_id=3)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 HOT_QK, HOT_EMBED = 20.0, 40.0
 
@@ -80,7 +90,7 @@ def write_tiny(model_dir: str, raw_config: dict, seed: int, hot: bool = False, n
 
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
-    """{'A', 'B', 'C', 'A_hot', 'B_hot', 'C_hot'} -> folder with config.json and model.safetensors."""
+    """{'A', 'B', 'C', 'D', 'A_hot', ...} -> folder with config.json and model.safetensors."""
     out = {}
     seed = 11
     for name, cfg in TINY.items():

@@ -6,6 +6,10 @@ code (Go, MLX 4-bit weights, batch 1, no sliding window) cannot be compiled or
 imported here (no Go toolchain), so this file rests on the formulas alone; each
 function cites the reference file and lines it restates.
 
+The tensors may live on any device: the arithmetic follows the weights it is
+given (the tests run the larger configurations on the GPU, in float64 torch
+operations, to keep the oracle quick).
+
 Everything is computed in ``dtype`` (float64 by default; float32 follows the
 reference's CPU backend) except the rotation angles, which the reference forms
 in float32 (`cpu/cpu_attn.go:16`, `:45-49`) and which are formed in float32
@@ -78,7 +82,7 @@ def layer_is_sliding(cfg, i):
 def embed(ids, table, hidden, dtype=torch.float64):
     """h = E[ids] * sqrt(hidden)  (`gemma/gemma.go:193`, `:197`; `qwen/embed.go:78-83`)."""
     scale = float(np.float32(math.sqrt(float(hidden))))  # embScale is a float32
-    return table.to(dtype)[torch.as_tensor(ids, dtype=torch.long)] * scale
+    return table.to(dtype)[torch.as_tensor(ids, dtype=torch.long, device=table.device)] * scale
 
 
 def rms_norm(x, w, eps):
@@ -100,22 +104,22 @@ def rope(x, positions, base):
                    dtype=np.float32)
     pos = np.asarray(positions, dtype=np.float32)
     theta = (pos[:, None] * np.float32(1.0) * inv[None, :]).astype(np.float32)  # [L, half], float32 product
-    c = torch.from_numpy(np.cos(theta.astype(np.float64))).to(x.dtype)
-    s = torch.from_numpy(np.sin(theta.astype(np.float64))).to(x.dtype)
+    c = torch.from_numpy(np.cos(theta.astype(np.float64))).to(x.dtype).to(x.device)
+    s = torch.from_numpy(np.sin(theta.astype(np.float64))).to(x.dtype).to(x.device)
     if x.dtype == torch.float32:  # the reference rounds cos/sin to float32
         c, s = c.float(), s.float()
     a, b = x[..., :half], x[..., half:]
     return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
 
 
-def visible(n, window):
+def visible(n, window, device="cpu"):
     """[n, n] bool: key j is seen by query i iff j <= i and, with a window, j > i - window.
 
     The reference's mask is causal only (`gemma/gemma.go:232-240`); the window is
     the architecture's: the last `window` positions, the query's own included.
     """
-    i = torch.arange(n)[:, None]
-    j = torch.arange(n)[None, :]
+    i = torch.arange(n, device=device)[:, None]
+    j = torch.arange(n, device=device)[None, :]
     ok = j <= i
     if window is not None:
         ok = ok & (j > i - window)
@@ -146,8 +150,8 @@ def attention(x, wq, wk, wv, wo, n_heads, n_kv, head_dim, rope_base, q_scalar, s
     k = rope(k, positions, rope_base)
     q = q * (1.0 / math.sqrt(float(q_scalar)))                                   # gemma.go:62, :76
     rep = n_heads // n_kv
-    ok = visible(L, window)
-    out = torch.empty(L, n_heads, head_dim, dtype=x.dtype)
+    ok = visible(L, window, x.device)
+    out = torch.empty(L, n_heads, head_dim, dtype=x.dtype, device=x.device)
     for h in range(n_heads):
         kv = h // rep                                                            # gemma.go:79-81, cpu_attn.go:72
         s = q[h] @ k[kv].T                                                       # [L, L]

@@ -144,3 +144,24 @@ def test_random_traffic_loses_nothing():
     c.audit()
     for g in c.kv_groups.values():
         assert g.pool.n_free == g.pool.n_pages and not g.held
+
+
+def test_the_planned_size_is_what_the_groups_hold():
+    needs = [{"kv": KVNeed(2, 16, 8)}, {"kv": KVNeed(2, 16)}, {"kv": KVNeed(2, 16, 8), "s": StateNeed((5,), torch.float32)}]
+    c = ModelCache(needs, 10 * 64, 512, torch.bfloat16, "cpu", max_seqs=3)
+    assert c.planned_bytes == c.bytes()
+    # windowed lines hold a ring per sequence (here one page each), the others every page
+    assert c.bytes() == 2 * 2 * 3 * 2 * 64 * 16 * 2 + 2 * 1 * 10 * 2 * 64 * 16 * 2 + 3 * 5 * 4
+
+
+@pytest.mark.gpu
+def test_a_cache_the_device_has_no_room_for_is_refused_with_its_sizes():
+    """Asked for more tokens than the device can hold, the cache says what it would need and what is free,
+    before it allocates anything (no out-of-memory error from the allocator, nothing left half built)."""
+    needs = [{"kv": KVNeed(16, 256, 4096)}, {"kv": KVNeed(16, 256)}] * 20
+    before = torch.cuda.memory_allocated()
+    with pytest.raises(CacheFull, match=r"needs \d+\.\d+ GiB .* the device has \d+\.\d+ GiB free"):
+        ModelCache(needs, 40_000_000, 8192, torch.bfloat16, "cuda:0", max_seqs=64)
+    assert torch.cuda.memory_allocated() == before
+    small = ModelCache(needs, 128, 8192, torch.bfloat16, "cuda:0", max_seqs=2)
+    assert small.bytes() == small.planned_bytes

@@ -96,6 +96,25 @@ def test_long_decoding_from_a_short_prompt(on, dtype, engines, plain_models):
 
 
 @pytest.mark.parametrize("on,dtype", CASES)
+@pytest.mark.parametrize("graphs", [True, False])
+def test_a_ring_of_whole_pages_wraps(on, dtype, graphs, engines, plain_models):
+    """A window of 128 = two cache pages, as the real window of 4096 is a whole number of pages: a prompt of 300
+    tokens (more than two rings: only its last 128 are stored), then 160 single-token steps across two wraps of
+    the ring, beside a shorter request; twice, so the second round finds the slots and pages used."""
+    if on != "cuda" and not graphs:
+        pytest.skip("the CPU statements have no graphs to switch off")
+    key = "D_hot"
+    V = vocab_of(key)
+    eng = engines(key, dtype, on, max_tokens=1024, use_graphs=graphs)
+    for round_ in range(2):
+        reqs = [random_tokens(V, 460, 600 + round_), random_tokens(V, 140, 610 + round_)]
+        got = run_requests(eng, reqs, [300, 20])
+        for i, (g, r) in enumerate(zip(got, reqs)):
+            assert_logits(g, plain_logits(plain_models, key, r), dtype, f"{key} ring of two pages, round {round_}, request {i}")
+    assert eng.cache.live_slots() == []
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
 def test_first_tokens_of_a_sequence(on, dtype, engines, plain_models):
     """A prompt of one token, then tokens 2..12 one by one, beside a request that starts with two."""
     for key in models_for(on):
