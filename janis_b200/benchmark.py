@@ -34,7 +34,8 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(_HERE)
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}      # an earlier measurement on this kind of GPU
+# an earlier measurement on this kind of GPU: copy bandwidth, the library's bfloat16 product as a burst and sustained
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
 def load_config(name_or_path: str) -> dict:
@@ -48,8 +49,8 @@ def peaks() -> tuple[dict, str]:
     try:
         with open(path) as f:
             p = json.load(f)
-        out = {"hbm_gbs": float(p["hbm_gbs"]),
-               "bf16_tflops": float(p.get("bf16_tflops_sustained") or p["bf16_tflops"])}
+        out = {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+               "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained") or p["bf16_tflops"])}
         return out, "measured"
     except (OSError, KeyError, ValueError, TypeError):
         return dict(FALLBACK_PEAKS), "fallback"
@@ -117,30 +118,32 @@ def weight_bytes(model, itemsize: int = 2) -> int:
 
 
 def cache_bytes(model, lengths, itemsize: int = 2) -> int:
-    """Bytes of keys and values that a decode step over sequences of these lengths reads."""
+    """Bytes of cache that a decode step over sequences of these lengths reads: keys and values of every position
+    a line keeps (a window of them for a windowed line), and every fixed-size state, whatever mixer asked for it."""
+    from .cache.cache import KVNeed, StateNeed
     total = 0
     for needs in model.cache_line_needs():
-        kv = needs.get("kv")
-        if kv is None:
-            continue
-        per_token = 2 * kv.n_kv_heads * kv.head_dim * itemsize
-        for n in lengths:
-            total += per_token * (min(n, kv.window) if kv.window else n)
+        for need in (needs or {}).values():
+            if isinstance(need, KVNeed):
+                per_token = 2 * need.n_kv_heads * need.head_dim * itemsize
+                total += sum(per_token * (min(n, need.window) if need.window else n) for n in lengths)
+            elif isinstance(need, StateNeed):
+                n = 1
+                for d in need.shape:
+                    n *= int(d)
+                total += len(lengths) * n * torch.empty((), dtype=need.dtype).element_size()
     return total
 
 
 def prefill_flops(model, n_tokens: int) -> float:
-    """2 M N K of every product of a prompt step of n_tokens that asks for the last logits, plus the
-    two products of attention over the visible keys."""
+    """2 M N K of every product of a prompt step of n_tokens that asks for the last logits, plus what each
+    layer's mixer says it computes beyond its products (attention: scores and weighted sums)."""
     flops = 0.0
     for name, spec in model.tensor_specs().items():
         if len(spec.shape) == 2 and "embed_tokens" not in name:
             flops += 2.0 * n_tokens * spec.shape[0] * spec.shape[1]
-    for blk in (model.blocks[c.layer] for c in model.schedule):
-        m = blk.mixer
-        w = m.window or n_tokens
-        visible = sum(min(i + 1, w) for i in range(n_tokens))
-        flops += 4.0 * m.n_heads * m.head_dim * visible
+    for call in model.schedule:
+        flops += float(model.blocks[call.layer].mixer.prompt_flops(n_tokens))
     flops += 2.0 * model.hidden * model.vocab          # the head, last position only
     return flops
 
@@ -154,77 +157,99 @@ def _tokens(vocab: int, n: int, seed: int) -> list[int]:
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
-def fill(engine, batch: int, length: int, seed: int = 0) -> list[int]:
-    """`batch` new sequences of `length` seeded random tokens each, by real prompt steps."""
+def uniform_lengths(n: int, lo: int, hi: int, seed: int) -> list[int]:
+    """n seeded lengths, uniform in [lo, hi]."""
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(lo, hi + 1, (n,), generator=g).tolist()
+
+
+def fill(engine, lengths, seed: int = 0) -> list[int]:
+    """New sequences of these lengths, of seeded random tokens, by real prompt steps."""
     from .engine.step import StepEntry
-    slots = [engine.alloc_slot() for _ in range(batch)]
-    per_step = max(1, engine.stepper.max_step_tokens // max(length, 1))
-    for i in range(0, batch, per_step):
-        part = slots[i:i + per_step]
-        engine.stepper.step([StepEntry(s, _tokens(engine.model.vocab, length, seed + i + j), ())
-                             for j, s in enumerate(part)])
+    slots = [engine.alloc_slot() for _ in lengths]
+    cur, cur_tok = [], 0
+    batches = []
+    for i, n in enumerate(lengths):
+        if cur and cur_tok + n > engine.stepper.max_step_tokens:
+            batches.append(cur)
+            cur, cur_tok = [], 0
+        cur.append(i)
+        cur_tok += n
+    batches.append(cur)
+    for part in batches:
+        engine.stepper.step([StepEntry(slots[i], _tokens(engine.model.vocab, lengths[i], seed + i), ()) for i in part])
     return slots
 
 
-def measure_decode(engine, batch: int, context: int, steps: int, warmup: int, sample_clocks: bool = False,
-                   profile: bool = False) -> dict:
-    """Decode tokens a second at `batch` sequences whose cache grows to `context` tokens by the last step.
-    `profile` opens the CUDA profiler range around the first two timed steps (for a profiler that was
-    started with its capture off); the timing of such a run means nothing."""
+def measure_decode(engine, start_lengths, steps: int, warmup: int, sample_clocks: bool = False,
+                   profile: bool = False, runs: int = 1) -> dict:
+    """Decode tokens a second over sequences that hold `start_lengths` tokens before the first warm-up step
+    (brought there by real prompt steps).  `runs` timed runs of exactly `steps` steps each, every one from the
+    same lengths; the median run is reported (the reference's method: three runs, the median,
+    `bench/mlx.py:41-46`).  `profile` opens the CUDA profiler range around the first two timed steps (for a
+    profiler that was started with its capture off); the timing of such a run means nothing."""
     from .engine.step import StepEntry
     ops = engine.rt.ops
-    start_len = context - steps - warmup
-    if start_len < 1:
-        raise ValueError("context too short for the steps asked")
-    slots = fill(engine, batch, start_len)
+    batch = len(start_lengths)
     st = engine.stepper
-    toks = st.token_buffer(batch)
-    toks.copy_(torch.tensor(_tokens(engine.model.vocab, batch, 99), dtype=torch.int32))
-    entries = [StepEntry(s, (0,), (0,)) for s in slots]
-    history = torch.zeros((steps + warmup, batch), dtype=torch.int32, device=engine.rt.device)
+    results = []
+    clock_rows = None
+    for run_no in range(max(1, runs)):
+        slots = fill(engine, start_lengths)
+        toks = st.token_buffer(batch)
+        toks.copy_(torch.tensor(_tokens(engine.model.vocab, batch, 99), dtype=torch.int32))
+        entries = [StepEntry(s, (0,), (0,)) for s in slots]
+        history = torch.zeros((steps + warmup, batch), dtype=torch.int32, device=engine.rt.device)
 
-    def one(i):
-        logits = st.step(entries, copy=False, tokens_on_device=True)
-        ops.argmax(logits, toks)                      # the next step's tokens, picked on the device
-        history[i].copy_(toks)
+        def one(i):
+            logits = st.step(entries, copy=False, tokens_on_device=True)
+            ops.argmax(logits, toks)                      # the next step's tokens, picked on the device
+            history[i].copy_(toks)
 
-    for i in range(warmup):
-        one(i)
-    torch.cuda.synchronize()
-    launches0 = ops.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clocks = ClockSampler() if sample_clocks else None
-    if clocks:
-        clocks.__enter__()
-    e0.record()
-    for i in range(steps):
-        if profile and i == 0:
-            torch.cuda.profiler.start()
-        one(warmup + i)
-        if profile and i == 1:
-            torch.cuda.synchronize()
-            torch.cuda.profiler.stop()
-    e1.record()
-    torch.cuda.synchronize()
-    if clocks:
-        clocks.__exit__()
-    ms = e0.elapsed_time(e1)
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clocks = ClockSampler() if sample_clocks else None
+        if clocks:
+            clocks.__enter__()
+        e0.record()
+        for i in range(steps):
+            if profile and i == 0 and run_no == 0:
+                torch.cuda.profiler.start()
+            one(warmup + i)
+            if profile and i == 1 and run_no == 0:
+                torch.cuda.synchronize()
+                torch.cuda.profiler.stop()
+        e1.record()
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.__exit__()
+        results.append((e0.elapsed_time(e1), clocks, int(history.cpu().sum())))
+        for s in slots:
+            engine.free_slot(s)
+    results.sort(key=lambda r: r[0])
+    ms, clocks, checksum = results[len(results) // 2]
     per_step = st.launch_counter + 1                  # kernels of one replayed step, plus argmax
-    mid = start_len + warmup + steps // 2
-    bytes_step = weight_bytes(engine.model) + cache_bytes(engine.model, [mid] * batch)
-    tokens_out = history.cpu()
-    for s in slots:
-        engine.free_slot(s)
+    mid = [n + warmup + steps // 2 for n in start_lengths]
+    bytes_step = weight_bytes(engine.model) + cache_bytes(engine.model, mid)
     return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "bytes_per_step": bytes_step,
             "gb_s": bytes_step / (ms / steps / 1e3) / 1e9, "gpu_launches": per_step * steps,
-            "clocks": clocks.summary() if clocks else None, "tokens_checksum": int(tokens_out.sum()),
-            "eager_launches": ops.launch_count() - launches0}
+            "clocks": clocks.summary() if clocks else None, "tokens_checksum": checksum,
+            "runs_ms_per_step": [round(r[0] / steps, 4) for r in results]}
 
 
 def measure_e2e(engine, batch: int, context: int, steps: int) -> dict:
     """The same through Engine.generate: token ids in from the host, token ids out to the host."""
     n_prompt = context - steps - 1
     prompts = [_tokens(engine.model.vocab, n_prompt, 1000 + i) for i in range(batch)]
+    return measure_generate(engine, prompts, steps + 1)
+
+
+def measure_generate(engine, prompts, new_tokens: int, temp: float = 0.0, top_p: float = 1.0) -> dict:
+    """Decode tokens a second of `Engine.generate` over these prompts, `new_tokens` each: the tokens after each
+    request's first, over the time from the first token heard to the end (the reference's decode rate,
+    `cmd/enginebench/main.go:172-189`), and the time to that first token."""
     t_first = [None]
     count = [0]
 
@@ -235,13 +260,14 @@ def measure_e2e(engine, batch: int, context: int, steps: int) -> dict:
         count[0] += 1
 
     # warm-up: the same call over the same lengths, so that every graph the timed call replays exists
-    engine.generate(prompts, temp=0.0, max_tokens=steps + 1, stop=())
+    engine.generate(prompts, temp=temp, top_p=top_p, max_tokens=new_tokens, stop=())
     torch.cuda.synchronize()
-    engine.generate(prompts, temp=0.0, max_tokens=steps + 1, stop=(), on_token=on_token)
+    t0 = time.perf_counter()
+    engine.generate(prompts, temp=temp, top_p=top_p, max_tokens=new_tokens, stop=(), on_token=on_token)
     torch.cuda.synchronize()
     dt = time.perf_counter() - t_first[0]
-    return {"tok_s": (count[0] - batch) / dt, "h2d_bytes_per_step": engine.stepper.h2d_bytes,
-            "d2h_bytes_per_step": 4 * batch}
+    return {"tok_s": (count[0] - len(prompts)) / dt, "h2d_bytes_per_step": engine.stepper.h2d_bytes,
+            "d2h_bytes_per_step": 4 * len(prompts), "first_token_ms": (t_first[0] - t0) * 1e3}
 
 
 def measure_prefill(engine, n_tokens: int, repeats: int = 5, warmup: int = 3, profile: bool = False) -> dict:
@@ -268,32 +294,79 @@ def measure_prefill(engine, n_tokens: int, repeats: int = 5, warmup: int = 3, pr
     return {"tok_s": n_tokens / (ms / 1e3), "ms": ms, "flops": prefill_flops(engine.model, n_tokens)}
 
 
+def fp32_check(raw: dict, bf16_engine, n_tokens: int = 256, seed: int = 0) -> dict:
+    """The logits at the end of a seeded prompt from the bfloat16 engine against a true 32-bit engine over the
+    same weights: the largest difference as a fraction of the largest logit."""
+    import janis_b200
+    from .engine.step import StepEntry
+    toks = _tokens(bf16_engine.model.vocab, n_tokens, 4242)
+    slot = bf16_engine.alloc_slot()
+    a = bf16_engine.step([StepEntry(slot, toks, (n_tokens - 1,))]).float().cpu()
+    bf16_engine.free_slot(slot)
+    ref = janis_b200.from_config(raw, seed=seed, dtype="float32", max_tokens=max(64, n_tokens), max_batch=1)
+    slot = ref.alloc_slot()
+    b = ref.step([StepEntry(slot, toks, (n_tokens - 1,))]).float().cpu()
+    ref.close()
+    return {"tokens": n_tokens, "max_err": round(float((a - b).abs().max()), 5),
+            "scale": round(float(b.abs().max()), 3), "same_argmax": bool(a.argmax() == b.argmax())}
+
+
 def _pretty(config: str) -> str:
     name = os.path.splitext(os.path.basename(config))[0]
     return "Gemma2-" + name[len("gemma2-"):].upper() if name.startswith("gemma2-") else name
 
 
+def _frac(r: dict, pk: dict) -> float:
+    return round(r["gb_s"] / pk["hbm_gbs"], 4)
+
+
 def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, config: str = "gemma2-2b",
         layers: int | None = None, points=(1, 64), prefill_tokens: int = 2048, e2e: bool = True,
-        profile: str = "") -> dict:
-    """The whole benchmark; returns the record that bench.py prints as one JSON line."""
+        profile: str = "", runs: int = 3, workloads: bool = True) -> dict:
+    """The whole benchmark; returns the record that bench.py prints as one JSON line.
+
+    The headline is the median of `runs` runs of exactly `steps` decode steps at `batch` sequences whose cache
+    reaches `context` tokens.  `points` adds decode at other batch sizes at the same context.  `workloads` adds
+    the other measurements the configurations are quoted with: decode at batch 1, 8 and 64 from prompts of
+    seeded lengths uniform in [128, 2048]; the 9B sizes generating 256 tokens each for an unequal batch of 8
+    prompts of lengths uniform in [64, 4096] through `Engine.generate`; the 27B sizes' prompt step of 2,048
+    tokens and decode at batch 1 and 16 from prompts of 1,024; each decode point with the fraction of the
+    copy bandwidth that its own lengths give it; and the bfloat16 logits of the headline model against a true
+    32-bit engine."""
     import janis_b200
     raw = load_config(config)
     full_layers = raw["num_hidden_layers"]
     if layers:
         raw = dict(raw, num_hidden_layers=int(layers))
     pk, pk_kind = peaks()
-    max_batch = max([batch, *points])
+    max_batch = max([batch, *points, *((64,) if workloads else ())])
     room = max(context, prefill_tokens)                 # the prefill measurement needs its own length to fit
     eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=max_batch * room, max_batch=max_batch,
                                  max_context=room)
-    main = measure_decode(eng, batch, context, steps, warmup, sample_clocks=True, profile=profile == "decode")
+    start = context - steps - warmup
+    if start < 1:
+        raise ValueError("context too short for the steps asked")
+    main = measure_decode(eng, [start] * batch, steps, warmup, sample_clocks=True, profile=profile == "decode",
+                          runs=1 if profile else runs)
     pre = measure_prefill(eng, prefill_tokens, profile=profile == "prefill")
     pts = {}
     for b in points:
-        pts[f"decode_b{b}"] = round(measure_decode(eng, b, context, max(16, steps // 2), warmup)["tok_s"], 1)
+        k = max(16, steps // 2)
+        r = measure_decode(eng, [context - k - warmup] * b, k, warmup)
+        pts[f"decode_b{b}"] = round(r["tok_s"], 1)
+        pts[f"decode_b{b}_frac"] = _frac(r, pk)
+    if workloads and not profile:
+        for b in (1, 8, 64):                            # prompts of seeded lengths uniform in [128, 2048]
+            r = measure_decode(eng, uniform_lengths(b, 128, 2048, 7 + b), 128, warmup, runs=3)
+            pts[f"decode_b{b}_u2048"] = round(r["tok_s"], 1)
+            pts[f"decode_b{b}_u2048_frac"] = _frac(r, pk)
     end = measure_e2e(eng, batch, context, steps) if e2e and not profile else None
+    check = fp32_check(raw, eng) if workloads and not profile else None
     cfg = eng.config
+    eng.close()
+    del eng
+    if workloads and not profile:
+        pts.update(other_sizes(pk, warmup))
     rec = {
         "metric": "decode tok/s at batch %d (%s sizes, context %d)" % (batch, _pretty(config), context),
         "value": round(main["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
@@ -304,19 +377,55 @@ def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, 
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "window": cfg.sliding_window, "global_batch": batch, "seq_len": context,
                    "context_len": context, "prefill_tokens": prefill_tokens, "weights": "random seed 0",
-                   "parallelism": "single", "l2": "each step reads weights+cache >> L2"},
-        "clocks": main["clocks"], "gpu_launches": main["gpu_launches"],
+                   "parallelism": "single", "l2": "each step reads weights+cache >> L2",
+                   "timed_runs": "median of %d" % (1 if profile else runs)},
+        "clocks": main["clocks"], "gpu_launches": main["gpu_launches"], "runs_ms_per_step": main["runs_ms_per_step"],
         "prefill": {"value": round(pre["tok_s"], 1), "tokens": prefill_tokens, "ms": round(pre["ms"], 3),
-                    "frac": round(pre["flops"] / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(pre["flops"] / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "frac_of_sustained": round(pre["flops"] / (pre["ms"] / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(main["gb_s"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(main["gb_s"] / pk["hbm_gbs"], 4), "peaks": pk_kind},
+                     "frac": _frac(main, pk), "peaks": pk_kind},
         "points": pts,
     }
     if end:
         rec["e2e"] = {"value": round(end["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": end["h2d_bytes_per_step"],
                       "d2h_bytes_per_step": end["d2h_bytes_per_step"]}
-    eng.close()
+    if check:
+        rec["fp32_check"] = check
     return rec
+
+
+def other_sizes(pk: dict, warmup: int = 8) -> dict:
+    """The measurements quoted for the larger configurations (all of their layers, random weights):
+    9B: an unequal batch of 8 prompts of seeded lengths uniform in [64, 4096], 256 tokens generated for each,
+    through `Engine.generate` (host tokens in and out); 27B: the prompt step of 2,048 tokens, and decode at batch 1
+    and 16 from prompts of 1,024 tokens."""
+    import janis_b200
+    out = {}
+    raw = load_config("gemma2-9b")
+    eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=8 * (4096 + 256 + 64), max_batch=8,
+                                 max_context=8192)
+    lens = uniform_lengths(8, 64, 4096, 5)
+    prompts = [_tokens(eng.model.vocab, n, 3000 + i) for i, n in enumerate(lens)]
+    g = measure_generate(eng, prompts, 256)
+    out["gen_9b_b8_u4096_tok_s"] = round(g["tok_s"], 1)
+    out["gen_9b_b8_u4096_first_token_ms"] = round(g["first_token_ms"], 1)
+    mid = [n + 128 for n in lens]
+    bytes_step = weight_bytes(eng.model) + cache_bytes(eng.model, mid)
+    out["gen_9b_b8_u4096_frac"] = round(bytes_step * (g["tok_s"] / 8) / 1e9 / pk["hbm_gbs"], 4)
+    eng.close()
+    del eng
+    raw = load_config("gemma2-27b")
+    eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=16 * 2048, max_batch=16, max_context=8192)
+    pre = measure_prefill(eng, 2048, repeats=3, warmup=2)
+    out["prefill_27b_tok_s"] = round(pre["tok_s"], 1)
+    out["prefill_27b_frac"] = round(pre["flops"] / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)
+    for b in (1, 16):
+        r = measure_decode(eng, [1024] * b, 64, warmup, runs=3)
+        out[f"decode_27b_b{b}_p1024"] = round(r["tok_s"], 1)
+        out[f"decode_27b_b{b}_p1024_frac"] = _frac(r, pk)
+    eng.close()
+    return out
 
 
 def main(argv=None) -> int:
@@ -333,6 +442,9 @@ def main(argv=None) -> int:
     ap.add_argument("--config", default="gemma2-2b", help="2b, 9b, 27b, gemma2-2b ... or a config.json")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="leave out the unequal-length decode points, the 9B and 27B measurements and the 32-bit check")
+    ap.add_argument("--runs", type=int, default=3, help="timed runs of the headline; the median is reported")
     ap.add_argument("--profile", choices=["decode", "prefill"], default="",
                     help="open the CUDA profiler range around two timed decode steps, or the last prompt step")
     a = ap.parse_args(argv)
@@ -353,6 +465,7 @@ def main(argv=None) -> int:
     points = tuple(batches[1:]) if len(batches) > 1 else (1, 64)
     config = a.config if (os.path.exists(a.config) or a.config.startswith("gemma2-")) else "gemma2-" + a.config
     rec = run(a.steps, max(3, a.warmup), batches[0], a.context, config, a.layers or None,
-              points=() if (a.no_points or a.profile) else points, prefill_tokens=a.prefill, profile=a.profile)
+              points=() if (a.no_points or a.profile) else points, prefill_tokens=a.prefill, profile=a.profile,
+              runs=max(1, a.runs), workloads=not (a.no_workloads or a.no_points) and config == "gemma2-2b" and not a.layers)
     print(json.dumps(rec))
     return 0

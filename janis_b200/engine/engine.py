@@ -88,7 +88,8 @@ class Engine:
                  max_new_tokens: int | None = None, stop_tokens: Iterable[int] | None = None):
         """Replies (lists of token ids) to prompts (lists of token ids), in order.
 
-        temp <= 0 is greedy; top_p outside (0, 1] means 1; max_tokens <= 0 means 512; `stop` defaults to
+        temp <= 0 is greedy; top_p outside (0, 1] means 1; max_tokens is one limit for every reply or a list
+        with one per request, <= 0 means 512; `stop` defaults to
         the model's end-of-sequence ids and a stop token is not part of the reply; `on_token(request,
         token)` hears every token as it is produced; `cancel()` is asked before every decode step.
         With return_replies=True the result is a list of `Reply` (tokens and finish_reason).

@@ -15,7 +15,7 @@ a small backend interface, so the loop can be tested with a fake one:
 
 One batch: the prompts start together in one prompt step and get their first
 token each; then decode steps over the sequences still alive.  A stop token ends
-a reply and is not part of it; a reply also ends at `max_tokens` or when the
+a reply and is not part of it; a reply also ends at `max_tokens` (one limit, or one per request) or when the
 context is full; a sequence that has ended leaves the batch and gives its place
 back at once.  Requests that do not fit into one batch are served in as many
 batches as it takes, in the order given.
@@ -70,8 +70,13 @@ def plan_batches(final_lengths: Sequence[int], max_batch: int, fits: Callable[[S
 def generate(backend, prompts: Sequence[Sequence[int]], max_tokens: int = DEFAULT_MAX_TOKENS,
              stop: Iterable[int] = (), on_token: Callable[[int, int], None] | None = None,
              cancel: Callable[[], bool] | None = None, mask_stop_on_first: bool = False) -> list[Reply]:
-    if max_tokens <= 0:
-        max_tokens = DEFAULT_MAX_TOKENS
+    # one limit for every request, or one per request; <= 0 means the default
+    if isinstance(max_tokens, (list, tuple)):
+        if len(max_tokens) != len(prompts):
+            raise GenerationError(f"{len(max_tokens)} token limits for {len(prompts)} requests")
+        limits = [int(m) if int(m) > 0 else DEFAULT_MAX_TOKENS for m in max_tokens]
+    else:
+        limits = [int(max_tokens) if int(max_tokens) > 0 else DEFAULT_MAX_TOKENS] * len(prompts)
     stop = frozenset(int(s) for s in stop)
     replies = [Reply() for _ in prompts]
     todo = []
@@ -83,7 +88,7 @@ def generate(backend, prompts: Sequence[Sequence[int]], max_tokens: int = DEFAUL
                                   f"{backend.max_context}")
         else:
             todo.append(i)
-    final = [min(len(prompts[i]) + max_tokens, backend.max_context) for i in todo]
+    final = [min(len(prompts[i]) + limits[i], backend.max_context) for i in todo]
     cancelled = False
     for batch in plan_batches(final, backend.max_batch, backend.fits):
         ids = [todo[j] for j in batch]
@@ -91,7 +96,7 @@ def generate(backend, prompts: Sequence[Sequence[int]], max_tokens: int = DEFAUL
             for i in ids:
                 replies[i].finish_reason = "cancel"
             continue
-        cancelled = _Batch(backend, ids, prompts, replies, max_tokens, stop, on_token, cancel, mask_stop_on_first).run()
+        cancelled = _Batch(backend, ids, prompts, replies, limits, stop, on_token, cancel, mask_stop_on_first).run()
     return replies
 
 
@@ -105,7 +110,7 @@ class _Batch:
     def _full_after(self, i: int, more: int) -> bool:
         """Whether reply i is at its length once `more` further tokens have been added."""
         n = len(self.replies[i].tokens) + more
-        return n >= self.max_tokens or len(self.prompts[i]) + n >= self.b.max_context
+        return n >= self.max_tokens[i] or len(self.prompts[i]) + n >= self.b.max_context
 
     def _take(self, rows, toks) -> None:
         """The tokens of one step: append or end, in row order; holes and ended replies are skipped."""

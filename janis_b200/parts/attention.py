@@ -63,6 +63,12 @@ class SoftmaxAttention(Mixer):
     def cache_needs(self):
         return {"kv": KVNeed(self.n_kv_heads, self.head_dim, self.window or None)}
 
+    def prompt_flops(self, n_tokens: int) -> float:
+        w = self.window or n_tokens
+        full = min(n_tokens, w)                           # queries 0 .. full-1 see i + 1 keys, the rest w
+        visible = full * (full + 1) // 2 + (n_tokens - full) * w
+        return 4.0 * self.n_heads * self.head_dim * visible      # q k^T and p v: 2 flops a multiply-add each
+
     def load(self, store, rt: Runtime):
         if rt.dtype == torch.bfloat16 and (self.hidden % 8 or (self.n_heads * self.head_dim) % 8):
             raise ValueError("the bfloat16 products need widths that are multiples of 8 "

@@ -192,6 +192,12 @@ class Mixer(Part):
     def cache_needs(self) -> Mapping[str, Any]:
         return {}
 
+    def prompt_flops(self, n_tokens: int) -> float:
+        """Floating-point operations of a prompt of n_tokens from position 0 beyond the products with the part's
+        weight matrices (for attention: scores and weighted sums over the keys each query sees).  Measurement
+        asks the mixer, so that it counts another mixer's work as well as attention's."""
+        return 0.0
+
     def forward(self, x, ctx: StepContext, line):
         raise NotImplementedError
 

@@ -117,7 +117,7 @@ def _signed64(c: int) -> int:
 
 
 _GAMMA, _MUL1, _MUL2 = _signed64(0x9E3779B97F4A7C15), _signed64(0xBF58476D1CE4E5B9), _signed64(0x94D049BB133111EB)
-_CHUNK = 1 << 22                 # elements drawn at a time (the 64-bit intermediates of a whole embedding would not fit)
+_CHUNK = 1 << 24                 # elements drawn at a time (the 64-bit intermediates of a whole embedding would not fit)
 
 
 def _hash64(counter: torch.Tensor) -> torch.Tensor:

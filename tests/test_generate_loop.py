@@ -201,3 +201,22 @@ def test_lookahead_and_cancel():
     out = generate(b, [[10], [20], [30]], max_tokens=10, cancel=cancel)
     assert [r.finish_reason for r in out] == ["cancel"] * 3 and out[2].tokens == []
     assert out[0].tokens == [11, 12, 13, 14] and not b.open_handles and b.in_flight == 0
+
+
+@pytest.mark.parametrize("backend", [FakeBackend, LookaheadBackend])
+def test_a_length_limit_for_each_request(backend):
+    """`max_tokens` as a list: each reply ends at its own limit (0 stands for the default), the others go on; the
+    room a batch needs is planned from each request's own limit."""
+    b = backend(max_batch=4, max_context=700)
+    out = generate(b, [[10], [20], [30], [40]], max_tokens=[2, 5, 1, 0], stop=())
+    assert [len(r.tokens) for r in out] == [2, 5, 1, 512]
+    assert out[0].tokens == [11, 12] and out[1].tokens == [21, 22, 23, 24, 25] and out[2].tokens == [31]
+    assert all(r.finish_reason == "length" for r in out)
+    assert not b.open_handles and sorted(b.closed) == [0, 1, 2, 3]
+    # planned from the limits: 1 + 30 and 1 + 3 fit a room of 40 together, 1 + 30 twice do not
+    assert plan_batches([31, 4], 4, lambda ls: sum(ls) <= 40) == [[0, 1]]
+    b = backend(max_batch=4, room=40)
+    generate(b, [[1], [2], [3]], max_tokens=[30, 3, 30], stop=())
+    assert [sorted(p[0]) for p in b.prefills] == [[0, 1], [2]]
+    with pytest.raises(GenerationError, match="3 token limits for 2 requests"):
+        generate(backend(), [[1], [2]], max_tokens=[1, 2, 3])

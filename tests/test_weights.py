@@ -177,7 +177,7 @@ def test_random_weights_have_the_asked_spread_and_do_not_repeat():
     """Mean 0, the standard deviation asked for, a bell (kurtosis near 3, nothing beyond 6 deviations), no
     correlation between neighbours, between rows or between tensors, and a prefix of a longer tensor of the same
     name equals the shorter one (a value is a function of seed, name and index alone: chunks cannot matter)."""
-    n = (1 << 22) + 12345                              # more than one chunk of the generator
+    n = (1 << 24) + 12345                              # more than one chunk of the generator
     a = random_tensor("m.weight", TensorSpec((n,), init_std=0.02), 7, dtype=torch.float32)
     x = (a / 0.02).double()
     assert abs(x.mean().item()) < 3e-3 and abs(x.std().item() - 1.0) < 3e-3
