@@ -322,7 +322,7 @@ def _frac(r: dict, pk: dict) -> float:
 
 def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, config: str = "gemma2-2b",
         layers: int | None = None, points=(1, 64), prefill_tokens: int = 2048, e2e: bool = True,
-        profile: str = "", runs: int = 3, workloads: bool = True) -> dict:
+        profile: str = "", runs: int = 3, workloads: bool = True, prompt_lengths=None) -> dict:
     """The whole benchmark; returns the record that bench.py prints as one JSON line.
 
     The headline is the median of `runs` runs of exactly `steps` decode steps at `batch` sequences whose cache
@@ -346,7 +346,9 @@ def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, 
     start = context - steps - warmup
     if start < 1:
         raise ValueError("context too short for the steps asked")
-    main = measure_decode(eng, [start] * batch, steps, warmup, sample_clocks=True, profile=profile == "decode",
+    # (prompt_lengths = (lo, hi): the headline run decodes from prompts of seeded lengths uniform in [lo, hi] instead)
+    starts = uniform_lengths(batch, prompt_lengths[0], prompt_lengths[1], 7 + batch) if prompt_lengths else [start] * batch
+    main = measure_decode(eng, starts, steps, warmup, sample_clocks=True, profile=profile == "decode",
                           runs=1 if profile else runs)
     pre = measure_prefill(eng, prefill_tokens, profile=profile == "prefill")
     pts = {}
@@ -368,7 +370,8 @@ def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, 
     if workloads and not profile:
         pts.update(other_sizes(pk, warmup))
     rec = {
-        "metric": "decode tok/s at batch %d (%s sizes, context %d)" % (batch, _pretty(config), context),
+        "metric": "decode tok/s at batch %d (%s sizes, %s)" % (
+            batch, _pretty(config), "prompts of %d to %d tokens" % tuple(prompt_lengths) if prompt_lengths else "context %d" % context),
         "value": round(main["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -445,6 +448,8 @@ def main(argv=None) -> int:
     ap.add_argument("--no-workloads", action="store_true",
                     help="leave out the unequal-length decode points, the 9B and 27B measurements and the 32-bit check")
     ap.add_argument("--runs", type=int, default=3, help="timed runs of the headline; the median is reported")
+    ap.add_argument("--prompt-lengths", default="", help="LO,HI: decode from prompts of seeded lengths uniform in [LO, HI] "
+                    "instead of sequences that all reach --context")
     ap.add_argument("--profile", choices=["decode", "prefill"], default="",
                     help="open the CUDA profiler range around two timed decode steps, or the last prompt step")
     a = ap.parse_args(argv)
@@ -466,6 +471,7 @@ def main(argv=None) -> int:
     config = a.config if (os.path.exists(a.config) or a.config.startswith("gemma2-")) else "gemma2-" + a.config
     rec = run(a.steps, max(3, a.warmup), batches[0], a.context, config, a.layers or None,
               points=() if (a.no_points or a.profile) else points, prefill_tokens=a.prefill, profile=a.profile,
-              runs=max(1, a.runs), workloads=not (a.no_workloads or a.no_points) and config == "gemma2-2b" and not a.layers)
+              runs=max(1, a.runs), workloads=not (a.no_workloads or a.no_points) and config == "gemma2-2b" and not a.layers,
+              prompt_lengths=tuple(int(v) for v in a.prompt_lengths.split(",")) if a.prompt_lengths else None)
     print(json.dumps(rec))
     return 0

@@ -49,7 +49,8 @@ extern "C" JANIS_API int janis_attn_decode_static(const void* qkv, const void* k
                                                   const int* seq_len, void* out, int n_seq, int nq, int nkv,
                                                   int q_row_heads, float scale, float cap, int window, int ring_len,
                                                   int chunk, int max_chunks, cudaStream_t stream) {
-    if (n_seq <= 0) return 0;
+    if (n_seq < 0) return janis::fail("attn_decode_static: a negative number of sequences");
+    if (n_seq == 0) return scratch_on_current_device() == nullptr ? 1 : 0;     // the set-up alone: nothing to launch
     if (nq <= 0 || max_chunks <= 0) return janis::fail("attn_decode_static: nq and max_chunks must be positive");
     const long long need = janis_attn_decode_scratch(n_seq, nq, max_chunks);
     if (need > (long long)JANIS_STATIC_SCRATCH_FLOATS)

@@ -19,8 +19,16 @@ extern "C" {
 #define JANIS_API __attribute__((visibility("default")))
 
 // Floats of scratch held inside the library for janis_attn_decode_static: 2 Mi floats,
-// 8 MiB.  The array is part of the library's image, so every GPU on which a process uses
-// this library holds these 8 MiB from the library's first use until the process exits.
+// 8 MiB.  The array is part of the image of one attention library, and there is one such
+// library per head size: a process that loads the libraries of several head sizes holds
+// 8 MiB for each of them, on every GPU on which it calls this entry point, until it exits
+// (and calls through different libraries neither share an array nor race on one).
+// When the memory is taken: the CUDA runtime loads a library's device code lazily, so the
+// 8 MiB of a GPU are committed by the first call of janis_attn_decode_static on that GPU
+// (its look-up of the array's address), not when the library is opened.  A caller that is
+// about to give the rest of the device's memory away makes that first call before it does
+// (a call with n_seq = 0 does the set-up and launches nothing); otherwise the first call
+// may fail for lack of memory.  Later calls commit nothing more.
 #define JANIS_STATIC_SCRATCH_FLOATS (2 * 1024 * 1024)
 
 // The existing entry point: the caller passes `partial`, a float scratch of at least
@@ -42,8 +50,10 @@ JANIS_API long long janis_attn_decode_scratch(int n_seq, int nq, int max_chunks)
 //    request is refused (returns non-zero, janis_last_error() says how much was asked and how
 //    much there is) and nothing is launched.
 //  * First call on a device: it looks up the array's device address (cudaGetSymbolAddress,
-//    with that device current) and remembers it per device.  Make this first call outside
-//    any stream capture; later calls only launch the two kernels.
+//    with that device current) and remembers it per device; this is also when the array's
+//    memory is committed (see above).  Make this first call outside any stream capture and
+//    before memory runs short; n_seq = 0 is accepted for it (the other arguments are then
+//    not looked at).  Later calls only launch the kernels.
 //  * The array is shared by every call and keeps what the last call left.  Nothing in it has
 //    to start at zero: each call writes every partial result that it reads afterwards, and
 //    reads no other.  Two calls whose kernels overlap on the GPU (different streams, or

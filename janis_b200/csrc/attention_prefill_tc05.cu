@@ -61,6 +61,37 @@ constexpr int LOADER_WARP = SOFTMAX_WARPS, ISSUER_WARP = SOFTMAX_WARPS + 1;
 constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr int OCOLS = HD / SPLIT;                     // accumulator columns a softmax thread looks after
 constexpr float RESCALE_STEP = 8.0f;                  // in units of log2: P stays below 2^8
+// The softmax's work per score is what bounds this kernel, most of it on the special-function unit (16 results a
+// cycle and SM, against 128 fused multiply-adds).  Two switches take work off it:
+//   JANIS_PT_TANH_APPROX: the cap's tanh as one tanh.approx (relative error 2^-11, on scores that the product with V
+//     weighs by P rounded to bfloat16, relative error 2^-9) instead of 2^x and 1/x;
+//   JANIS_PT_POLY_EX2: every second exponential of the softmax as a cubic on the fused multiply-add pipe (relative
+//     error 9e-5: the integer part goes into the exponent field, the fraction through the polynomial).
+// Measured on a B200 at head size 256 (4 x 4,096 tokens, one launch): both off 425 us, tanh.approx alone 372 us,
+// the cubic alone 444 us: the softmax warps are short of issue slots as much as of special-function results, and
+// the cubic costs seven instructions for the one it saves.  So the first is on and the second stays a switch.
+#ifndef JANIS_PT_TANH_APPROX
+#define JANIS_PT_TANH_APPROX 1
+#endif
+#ifndef JANIS_PT_POLY_EX2
+#define JANIS_PT_POLY_EX2 0
+#endif
+
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// 2^x for x <= 8 without the special-function unit; 2^x = 0 below -126 (masked scores are -inf)
+__device__ __forceinline__ float ex2_poly(float x) {
+    const float MAGIC = 12582912.0f;                  // 1.5 x 2^23: adding it leaves the nearest integer in the low bits
+    const float xc = fmaxf(x, -127.0f);
+    const float t = (xc - 0.5f) + MAGIC;              // nearest integer to x - 0.5: floor(x), or x itself at a tie
+    const float f = xc - (t - MAGIC);                 // in [0, 1]
+    const float p = fmaf(fmaf(fmaf(0.077119089663028717f, f, 0.227564394474029541f), f, 0.695146143436431885f), f, 1.0f);
+    const float r = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+    return x < -126.0f ? 0.f : r;
+}
 
 enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_DONE = 14, ROW_X = 15, N_BARS = 17 };
 
@@ -336,7 +367,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const float LOG2E = 1.4426950408889634f;
         // scores in units of log2(e): cap2 tanh(s scale / cap) = cap2 - 2 cap2 / (2^(s k_tanh) + 1), or s scale2
         const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
-        const float k_tanh = CAPPED ? scale / cap * (2.0f * LOG2E) : 0.f;
+        const float k_tanh = CAPPED ? scale / cap * (JANIS_PT_TANH_APPROX ? 1.0f : 2.0f * LOG2E) : 0.f;
         float m_ref = -INFINITY, l_run = 0.f;         // reference of the exponentials (log2 units); sum over this thread's keys
         // Two tiles are in flight in every thread: stage one of tile it + 1 (scores out of tensor memory, scale,
         // cap, masks, this thread's maximum told to the row's other threads) runs before stage two of tile it (the
@@ -360,9 +391,13 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const float s = __uint_as_float(sv[j]);
                 float v;
                 if (CAPPED) {
+#if JANIS_PT_TANH_APPROX
+                    v = fmaf(tanh_approx(s * k_tanh), cap2, -base);
+#else
                     float rc;
                     asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(rc) : "f"(pf::ex2(s * k_tanh) + 1.0f));
                     v = fmaf(rc, c1, c0);              // exact limits: 2^x = inf gives cap2, 2^x = 0 gives -cap2
+#endif
                 } else {
                     v = fmaf(s, scale2, c0);
                 }
@@ -403,7 +438,8 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             uint32_t pk[CPT / 2];
 #pragma unroll
             for (int j = 0; j < CPT; j += 2) {
-                const float p0 = pf::ex2(__uint_as_float(sv[j])), p1 = pf::ex2(__uint_as_float(sv[j + 1]));
+                const float p0 = pf::ex2(__uint_as_float(sv[j]));
+                const float p1 = JANIS_PT_POLY_EX2 ? ex2_poly(__uint_as_float(sv[j + 1])) : pf::ex2(__uint_as_float(sv[j + 1]));
                 l_run += p0 + p1;
                 pk[j / 2] = pf::pack_bf16(p0, p1);
             }
