@@ -239,11 +239,11 @@ def measure_decode(engine, start_lengths, steps: int, warmup: int, sample_clocks
             "runs_ms_per_step": [round(r[0] / steps, 4) for r in results]}
 
 
-def measure_e2e(engine, batch: int, context: int, steps: int) -> dict:
+def measure_e2e(engine, batch: int, context: int, steps: int, temp: float = 0.0, top_p: float = 1.0) -> dict:
     """The same through Engine.generate: token ids in from the host, token ids out to the host."""
     n_prompt = context - steps - 1
     prompts = [_tokens(engine.model.vocab, n_prompt, 1000 + i) for i in range(batch)]
-    return measure_generate(engine, prompts, steps + 1)
+    return measure_generate(engine, prompts, steps + 1, temp, top_p)
 
 
 def measure_generate(engine, prompts, new_tokens: int, temp: float = 0.0, top_p: float = 1.0) -> dict:
@@ -363,6 +363,8 @@ def run(steps: int = 256, warmup: int = 8, batch: int = 8, context: int = 8192, 
             pts[f"decode_b{b}_u2048"] = round(r["tok_s"], 1)
             pts[f"decode_b{b}_u2048_frac"] = _frac(r, pk)
     end = measure_e2e(eng, batch, context, steps) if e2e and not profile else None
+    if end and workloads:                                # and with sampling instead of the highest logit
+        pts["e2e_b%d_temp0.8_top_p0.95" % batch] = round(measure_e2e(eng, batch, context, steps, 0.8, 0.95)["tok_s"], 1)
     check = fp32_check(raw, eng) if workloads and not profile else None
     cfg = eng.config
     eng.close()

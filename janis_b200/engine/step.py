@@ -13,8 +13,8 @@ the earlier positions from the cache (`StepContext.extends`).
 Prompt steps with many tokens are cut at sequence borders into pieces of at
 most `max_step_tokens`; the pieces are independent, so nothing changes but the
 size of the scratch buffers.  Decode steps are replayed from CUDA graphs, one
-per (padded batch size, bound on the lengths); padding rows carry slot -1, touch
-no cache and change no other row.  Short prompt steps, whose three hundred
+per (padded batch size, bound on the lengths, mean length in eighths of that
+bound); padding rows carry slot -1, touch no cache and change no other row.  Short prompt steps, whose three hundred
 launches cost the host more time than the device needs for them, are replayed
 from graphs too, one per (padded token count, padded sequence count) once a
 shape has come twice; padding tokens form a sequence of their own with slot -1
@@ -119,7 +119,7 @@ class Stepper:
         self.ws = Workspace(rt.device)
         self.max_step_tokens = max(1, int(max_step_tokens))
         self.use_graphs = bool(use_graphs) and torch.device(rt.device).type == "cuda" and model.graph_safe
-        self._graphs: dict[tuple[int, int], tuple] = {}
+        self._graphs: dict[tuple, tuple] = {}     # (padded batch, length bound, mean length in eighths of it, even) -> graph
         self._prompt_graphs: dict[tuple, tuple] = {}   # (padded tokens, padded sequences, logits wanted) -> (graph,)
         self._prompt_seen: set[tuple] = set()          # shapes that have come once
         self._prompt_meta = None
@@ -336,6 +336,12 @@ class Stepper:
                 self.cache.reserve(e.slot, p + 1)
         self.cache.sync()
         bound = _bucket_len(max(pos) + 1)
+        # how full the batch is: the mean length over its rows (padding rows count as empty) in eighths of the bound.
+        # A launch shape that suits eight sequences at the bound wastes most of the GPU on sixty-four of which one
+        # is; the eighth is part of a recorded step's key, so a shape is replayed only for batches like its own.
+        fill = max(1, min(8, -(-8 * (sum(pos) + n_seq) // (B * bound))))
+        real = [p + 1 for e, p in zip(entries, pos) if e.slot is not None]
+        even = B == n_seq and 4 * min(real) >= 3 * max(real)
         graphs = self.use_graphs and B <= self.MAX_GRAPH_BATCH
         dev = self.rt.device
         if self._decode_meta is None:
@@ -361,9 +367,10 @@ class Stepper:
             meta = torch.from_numpy(host).to(dev)
         ctx = StepContext(rt=self.rt, ws=self.ws, mode="decode", n_tok=B, n_seq=B, tokens=meta[0, :B],
                           tok_pos=meta[1, :B], tok_seq=meta[2, :B], seq_slot=meta[3, :B], seq_start=meta[4, :B],
-                          seq_end=meta[5, :B], seq_first_row=meta[6, :B], len_bound=bound)
+                          seq_end=meta[5, :B], seq_first_row=meta[6, :B], len_bound=bound,
+                          len_mean=-(-fill * bound // 8), len_even=even)
         logits = self._decode_logits[:B]
-        key = (B, bound)
+        key = (B, bound, fill, even)
         if graphs and key in self._graphs:
             g, n_launch = self._graphs[key]
             g.replay()

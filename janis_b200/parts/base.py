@@ -135,6 +135,9 @@ class StepContext:
     seq_end: torch.Tensor           # int32 [n_seq] tokens cached after the step
     seq_first_row: torch.Tensor     # int32 [n_seq] row of the sequence's first token of this step in the packed step
     len_bound: int = 0              # host-side bound on max(seq_end); sizes the decode grids
+    len_mean: int = 0               # host-side estimate of mean(seq_end) over the step's rows, rounded up to an eighth of
+                                    # len_bound (0: unknown, take len_bound); it tunes launch shapes and changes no result
+    len_even: bool = True           # whether the sequences are about equally long (the shortest at least 3/4 of the longest)
     extends: bool = False           # a "prefill" step some of whose sequences have tokens in the cache already
                                     # (seq_start > 0): a mixer reads those from its cache line and stores this
                                     # step's own only after it has attended

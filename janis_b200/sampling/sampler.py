@@ -43,8 +43,40 @@ class SamplingParams:
 
 
 class Sampler:
+    MAX_ROWS = 4096                 # rows whose request and token numbers travel through the pinned staging ring
+
     def __init__(self, rt: Runtime):
         self.rt = rt
+        self._on_gpu = torch.device(rt.device).type == "cuda"
+        self._stage: list = []      # pinned [2, MAX_ROWS] buffers, used in turn
+        self._stage_done: list = []
+        self._turn = 0
+        self._meta = None           # their device copy: row 0 request numbers, row 1 token numbers
+
+    def _numbers(self, request_ids, token_index, R: int):
+        """(request numbers, token numbers) of the step's rows as int32 tensors on the device.  On a GPU they go
+        through pinned memory in one copy that the host does not wait for, so a sampled decode step costs the host
+        as little as a greedy one; the copy is ordered behind the kernels that read the last step's numbers."""
+        dev = self.rt.device
+        if not self._on_gpu or R > self.MAX_ROWS:
+            return (torch.tensor(list(request_ids), dtype=torch.int32, device=dev),
+                    torch.tensor(list(token_index), dtype=torch.int32, device=dev))
+        if self._meta is None:
+            self._meta = torch.zeros((2, self.MAX_ROWS), dtype=torch.int32, device=dev)
+            self._stage = [torch.zeros((2, self.MAX_ROWS), dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._stage_done = [None] * len(self._stage)
+        i = self._turn
+        self._turn = (i + 1) % len(self._stage)
+        if self._stage_done[i] is not None:
+            self._stage_done[i].synchronize()
+        host = self._stage[i].numpy()
+        host[0, :R] = request_ids
+        host[1, :R] = token_index
+        self._meta[:, :R].copy_(self._stage[i][:, :R], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._stage_done[i] = ev
+        return self._meta[0, :R], self._meta[1, :R]
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, request_ids: Sequence[int],
                token_index: Sequence[int], recent: Sequence[Sequence[int]] | None = None,
@@ -70,8 +102,7 @@ class Sampler:
         if p.temp <= 0.0:
             ops.argmax(logits, out)
             return (out, None) if return_uniform else out
-        ids = torch.tensor(list(request_ids), dtype=torch.int32, device=dev)
-        idx = torch.tensor(list(token_index), dtype=torch.int32, device=dev)
+        ids, idx = self._numbers(request_ids, token_index, R)
         u = torch.empty((R,), dtype=torch.float32, device=dev) if return_uniform else None
         ops.sample(logits, out, p.temp, p.top_p, p.seed, ids, idx, u)
         return (out, u) if return_uniform else out
