@@ -338,12 +338,267 @@ JANIS_EXPORT int janis_argmax(const float* logits, int* out, int R, int V, cudaS
     return launch_kernel("argmax", argmax_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 1, logits, out, V);
 }
 
+// ---------------------------------------------------------------------------
+// The same choice with the row's weights held in shared memory.  The kernel above reads its row from global
+// memory once per pass (some thirty-five passes with a nucleus, each thread walking a stretch of its own, which a
+// warp's loads do not coalesce) and scans in one thread: 1.9 ms for 8 rows of 256,000 logits.  Here a thread-block
+// cluster of CL CTAs shares a row: each CTA computes the weights of its stretch once (coalesced loads), keeps them
+// in shared memory, and every later pass reads shared memory only; a thread owns `per` consecutive ids (an odd
+// number: no bank conflicts), so thread order within a CTA and CTA order within the cluster are id order.  Sums
+// over threads are prefix sums by shuffles in a fixed tree, sums over CTAs are added in CTA order from slots that
+// every CTA fills in all the others' shared memory; every CTA sees the same numbers and takes the same branches.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float block_prefix(float v, float* wtot, float& total) {
+    // exclusive prefix of v in thread order and the block's total; wtot: 33 floats of shared memory
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    float incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+    if (lane == 0) excl = 0.f;
+    __syncthreads();                                  // wtot may still be read from the call before
+    if (lane == 31) wtot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const float t = lane < nwarp ? wtot[lane] : 0.f;
+        float ti = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, ti, o);
+            if (lane >= o) ti += up;
+        }
+        float te = __shfl_up_sync(0xffffffffu, ti, 1);
+        if (lane == 0) te = 0.f;
+        const float all = __shfl_sync(0xffffffffu, ti, 31);
+        wtot[lane] = te;
+        if (lane == 0) wtot[32] = all;
+    }
+    __syncthreads();
+    total = wtot[32];
+    return wtot[warp] + excl;
+}
+
+template <int CL> struct ClusterSlots {
+    float f[2][CL];                                    // two sets, used in turn: a CTA fills set k + 2 only after every
+    int i[2][CL];                                      // CTA has passed the barrier of set k + 1, i.e. has read set k
+};
+
+// every CTA's value, in CTA order: returns the sum of the CTAs before this one and the sum of all
+template <int CL>
+__device__ __forceinline__ float cluster_prefix(float mine, ClusterSlots<CL>* slots, int& turn, int rank, float& total) {
+    if (CL == 1) { total = mine; return 0.f; }
+    cg::cluster_group cluster = cg::this_cluster();
+    const int set = turn & 1;
+    ++turn;
+    if (threadIdx.x < CL) cluster.map_shared_rank(slots, threadIdx.x)->f[set][rank] = mine;
+    cluster.sync();
+    float before = 0.f, run = 0.f;
+#pragma unroll
+    for (int c = 0; c < CL; ++c) {
+        if (c == rank) before = run;
+        run += slots->f[set][c];
+    }
+    total = run;
+    return before;
+}
+
+template <int CL>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_shared_kernel(const float* __restrict__ logits, int* __restrict__ out, float* __restrict__ u_out, int V,
+                     float temp, float top_p, unsigned long long seed, const int* __restrict__ request_ids,
+                     const int* __restrict__ token_index, int seg, int per) {
+    extern __shared__ float w[];                      // this CTA's stretch of weights: per * SAMPLE_THREADS floats
+    __shared__ float wtot[33];
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ ClusterSlots<CL> slots;
+    __shared__ int chosen;
+    const int rank = CL == 1 ? 0 : (int)cg::this_cluster().block_rank();
+    const int r = blockIdx.x / CL;
+    const float* row = logits + (size_t)r * V;
+    const int base = min(V, rank * seg), n_here = min(V, base + seg) - base;      // ids [base, base + n_here)
+    const int lo = min((int)threadIdx.x * per, n_here), hi = min(lo + per, n_here); // this thread's, within the stretch
+    int turn = 0;
+    grid_dependents_launch();
+    if (CL > 1) cg::this_cluster().sync();            // a CTA's shared memory may be written by the others once it runs
+    grid_dependency_wait();
+
+    // the row's maximum and the lowest id that attains it
+    float v = -INFINITY;
+    int vi = 0x7fffffff;
+    for (int j = threadIdx.x; j < n_here; j += blockDim.x) {
+        const float x = row[base + j];
+        if (x > v) { v = x; vi = base + j; }            // ids ascend within a thread: `>` keeps the lowest
+    }
+    float mx;
+    int mi;
+    block_argmax(v, vi, sv, si, mx, mi);
+    if (CL > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (threadIdx.x < CL) {
+            ClusterSlots<CL>* remote = cluster.map_shared_rank(&slots, threadIdx.x);
+            remote->f[0][rank] = mx;
+            remote->i[0][rank] = mi;
+        }
+        ++turn;
+        cluster.sync();
+        mx = slots.f[0][0];
+        mi = slots.i[0][0];
+#pragma unroll
+        for (int c = 1; c < CL; ++c)
+            if (slots.f[0][c] > mx || (slots.f[0][c] == mx && slots.i[0][c] < mi)) { mx = slots.f[0][c]; mi = slots.i[0][c]; }
+    }
+    const float inv_t = 1.0f / temp;
+    for (int j = threadIdx.x; j < n_here; j += blockDim.x) w[j] = expf((row[base + j] - mx) * inv_t);
+    __syncthreads();
+
+    float mine = 0.f, here, total;
+    for (int j = lo; j < hi; ++j) mine += w[j];
+    block_prefix(mine, wtot, here);
+    cluster_prefix<CL>(here, &slots, turn, rank, total);
+
+    // nucleus: the largest threshold tau with mass(w >= tau) >= top_p * total
+    float tau = 0.f;
+    int ties_kept = 0x7fffffff;
+    const bool cut = top_p > 0.f && top_p < 1.f;
+    if (cut) {
+        const float need = top_p * total;
+        uint32_t blo = 0u, bhi = __float_as_uint(1.0f);   // w lies in [0, 1]; mass(w >= 0) = total >= need
+        while (blo < bhi) {                               // invariant: mass(w >= blo) >= need
+            const uint32_t mid = blo + (bhi - blo + 1) / 2;
+            const float th = __uint_as_float(mid);
+            float m = 0.f;
+            for (int j = lo; j < hi; ++j) {
+                const float x = w[j];
+                if (x >= th) m += x;
+            }
+            float m_here, mass;
+            block_prefix(m, wtot, m_here);
+            cluster_prefix<CL>(m_here, &slots, turn, rank, mass);
+            if (mass >= need) blo = mid; else bhi = mid - 1;
+        }
+        tau = __uint_as_float(blo);
+        float above = 0.f;
+        for (int j = lo; j < hi; ++j) {
+            const float x = w[j];
+            if (x > tau) above += x;
+        }
+        float above_here, mass_above;
+        block_prefix(above, wtot, above_here);
+        cluster_prefix<CL>(above_here, &slots, turn, rank, mass_above);
+        // the fewest ties, lowest ids first, that lift the mass to `need`
+        ties_kept = tau > 0.f ? (int)ceilf((need - mass_above) / tau) : 0x7fffffff;
+        if (ties_kept < 1) ties_kept = 1;
+    }
+
+    // kept mass per thread, with the rank of each tie in id order
+    float tie_before = 0.f;
+    if (cut) {
+        float tie_count = 0.f, ties_here, ties_all;
+        for (int j = lo; j < hi; ++j) tie_count += (w[j] == tau) ? 1.f : 0.f;
+        tie_before = block_prefix(tie_count, wtot, ties_here);
+        tie_before += cluster_prefix<CL>(ties_here, &slots, turn, rank, ties_all);
+    }
+    float kept = 0.f;
+    {
+        int tie_rank = (int)tie_before;
+        for (int j = lo; j < hi; ++j) {
+            const float x = w[j];
+            bool keep = true;
+            if (cut) {
+                if (x == tau) { keep = tie_rank < ties_kept; ++tie_rank; }
+                else keep = x > tau;
+            }
+            if (keep) kept += x;
+        }
+    }
+    float kept_here, kept_total;
+    float before = block_prefix(kept, wtot, kept_here);
+    before += cluster_prefix<CL>(kept_here, &slots, turn, rank, kept_total);
+
+    const float u = philox_uniform(seed, (uint32_t)request_ids[r], (uint32_t)token_index[r]);
+    const float target = u * kept_total;
+    if (threadIdx.x == 0) {
+        chosen = 0x7fffffff;
+        if (u_out && rank == 0) u_out[r] = u;
+    }
+    __syncthreads();
+    // the owner of the target walks its ids; two neighbours can both claim a target that sits on their border:
+    // the lower id is the inverse CDF's answer, so the minimum of the claims is taken
+    if (kept > 0.f && before <= target && target <= before + kept) {
+        int tie_rank = (int)tie_before;
+        float acc = before;
+        int pick = -1, last = -1;
+        for (int j = lo; j < hi; ++j) {
+            const float x = w[j];
+            bool keep = true;
+            if (cut) {
+                if (x == tau) { keep = tie_rank < ties_kept; ++tie_rank; }
+                else keep = x > tau;
+            }
+            if (!keep) continue;
+            acc += x;
+            last = base + j;
+            if (target <= acc) { pick = base + j; break; }
+        }
+        if (pick < 0) pick = last;
+        if (pick >= 0) atomicMin(&chosen, pick);
+    }
+    __syncthreads();
+    int best = chosen;
+    if (CL > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        const int set = turn & 1;
+        if (threadIdx.x < CL) cluster.map_shared_rank(&slots, threadIdx.x)->i[set][rank] = best;
+        cluster.sync();
+#pragma unroll
+        for (int c = 0; c < CL; ++c) best = min(best, slots.i[set][c]);
+        cluster.sync();                               // nobody leaves while its shared memory may still be written
+    }
+    if (rank == 0 && threadIdx.x == 0) out[r] = best != 0x7fffffff ? best : mi;
+}
+
+template <int CL>
+static int launch_sample_shared(const float* logits, int* out, float* u_out, int R, int V, float temp, float top_p,
+                                unsigned long long seed, const int* request_ids, const int* token_index, cudaStream_t stream) {
+    const int seg = ((V + CL - 1) / CL + 3) & ~3;
+    int per = (seg + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    per |= 1;                                          // odd: threads that walk their stretches hit different banks
+    const size_t smem = (size_t)per * SAMPLE_THREADS * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_shared_kernel<CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return fail("sample: shared memory refused: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    return launch_kernel("sample", sample_shared_kernel<CL>, dim3(R * CL), dim3(SAMPLE_THREADS), smem, stream, CL, logits, out,
+                         u_out, V, temp, top_p, seed, request_ids, token_index, seg, per);
+}
+
+static int g_sample_kernel = 1;     // 1: weights in shared memory where the vocabulary fits a cluster's; 0: the global-memory kernel
+
+// Which kernel janis_sample launches (for tests: both make the same choice up to the rounding of their sums).
+JANIS_EXPORT void janis_set_sample_kernel(int which) { g_sample_kernel = which ? 1 : 0; }
+
 JANIS_EXPORT int janis_sample(const float* logits, int* out, float* u_out, int R, int V, float temp, float top_p,
                               unsigned long long seed, const int* request_ids, const int* token_index,
                               cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return fail("sample: empty vocabulary");
     if (!(temp > 0.f)) return fail("sample: temperature must be positive (greedy is argmax), found %g", temp);
+    if (g_sample_kernel == 1) {
+        const int fits = 45 * SAMPLE_THREADS;          // floats of shared memory a CTA gives to its stretch (180 KB)
+#define JANIS_SAMPLE(CL) \
+    return launch_sample_shared<CL>(logits, out, u_out, R, V, temp, top_p, seed, request_ids, token_index, stream)
+        if (V <= fits) JANIS_SAMPLE(1);
+        if (V <= 2 * fits - 8) JANIS_SAMPLE(2);
+        if (V <= 4 * fits - 16) JANIS_SAMPLE(4);
+        if (V <= 8 * fits - 32) JANIS_SAMPLE(8);
+#undef JANIS_SAMPLE
+    }
     return launch_kernel("sample", sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 1, logits, out, u_out, V, temp,
                          top_p, seed, request_ids, token_index);
 }

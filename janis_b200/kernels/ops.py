@@ -67,6 +67,8 @@ def core():
         lib.janis_tc05_set_stages.restype = None
         lib.janis_argmax.argtypes = [P, P, I, I, P]
         lib.janis_sample.argtypes = [P, P, P, I, I, F, F, c_ulonglong, P, P, P]
+        lib.janis_set_sample_kernel.argtypes = [I]
+        lib.janis_set_sample_kernel.restype = None
         lib.janis_repeat_penalty.argtypes = [P, P, I, I, I, F, P]
         lib.janis_mask_tokens.argtypes = [P, P, I, I, I, P]
         lib.janis_set_overlap.argtypes = [I]
@@ -667,6 +669,13 @@ def sample(logits, out, temp: float, top_p: float, seed: int, request_ids, token
                                  _t(request_ids, "request_ids", torch.int32, (R,)),
                                  _t(token_index, "token_index", torch.int32, (R,)), _stream()))
     return out
+
+
+def set_sample_kernel(which: int = 1) -> None:
+    """Choose the kernel behind `sample`: 1 = the row's weights held in the shared memory of a cluster of up to 8
+    CTAs (vocabularies up to about 368,000; the default), 0 = every pass over global memory (any vocabulary).
+    For tests."""
+    core().janis_set_sample_kernel(int(which))
 
 
 def repeat_penalty(logits, recent, penalty: float):

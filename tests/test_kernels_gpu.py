@@ -847,10 +847,20 @@ def test_argmax_lowest_id_wins(Rn, V):
     assert out[0].item() == V // 2
 
 
-@pytest.mark.parametrize("V", [50, 384, 5000, 256000])
+@pytest.fixture(params=[1, 0], ids=["shared", "global"])
+def sample_kernel(request):
+    """Both sampling kernels: the row's weights in the shared memory of a cluster, and every pass over global memory."""
+    ops().set_sample_kernel(request.param)
+    yield request.param
+    ops().set_sample_kernel(1)
+
+
+# 50 to 5,000: one CTA a row; 46,081 and 70,001: clusters of 2 (an odd vocabulary: stretches that are not
+# multiples of 4); 150,000: 4; 256,000: 8; 400,000: too large for a cluster's shared memory, the other kernel
+@pytest.mark.parametrize("V", [50, 384, 5000, 46081, 70001, 150000, 256000, 400000])
 @pytest.mark.parametrize("temp,top_p", [(1.0, 1.0), (0.6, 0.95), (0.3, 0.5), (1.0, 0.05)])
-def test_sample_matches_the_host_sampler(V, temp, top_p):
-    Rn = 6
+def test_sample_matches_the_host_sampler(V, temp, top_p, sample_kernel):
+    Rn = 6 if V <= 256000 else 2
     spread = [0.5, 2.0, 8.0][V % 3]
     logits = rnd((Rn, V), torch.float32, 36, std=spread)
     d = dev()
@@ -865,7 +875,7 @@ def test_sample_matches_the_host_sampler(V, temp, top_p):
         assert out[r].item() == R.sample_row(logits[r].cpu(), temp, top_p, u_ref), f"row {r}"
 
 
-def test_sample_with_ties_at_the_nucleus_edge():
+def test_sample_with_ties_at_the_nucleus_edge(sample_kernel):
     V = 40
     logits = torch.zeros((1, V), dtype=torch.float32, device=dev())     # all equal: the nucleus is the first ids
     d = dev()
@@ -878,7 +888,26 @@ def test_sample_with_ties_at_the_nucleus_edge():
     assert seen == set(range(10))
 
 
-def test_sample_does_not_depend_on_the_batch():
+def test_sample_with_ties_across_the_ctas_of_a_cluster():
+    """All logits equal over a vocabulary that a cluster of 8 shares: the nucleus is the lowest tenth of the ids,
+    whichever CTA holds them, and every one of them can be drawn."""
+    V = 256000
+    d = dev()
+    logits = torch.zeros((64, V), dtype=torch.float32, device=d)
+    out = torch.empty((64,), dtype=torch.int32, device=d)
+    ops().sample(logits, out, 1.0, 0.1, 7, torch.arange(64, dtype=torch.int32, device=d),
+                 torch.zeros(64, dtype=torch.int32, device=d))
+    got = out.cpu()
+    assert int(got.min()) >= 0 and int(got.max()) < 25601 and len(set(got.tolist())) > 50
+    assert int(got.max()) > 12800                      # and from all over that tenth (64 draws: the upper half is met)
+    # top_p = 0.5: the kept ids span four CTAs' stretches (32,000 ids each)
+    ops().sample(logits, out, 1.0, 0.5, 8, torch.arange(64, dtype=torch.int32, device=d),
+                 torch.zeros(64, dtype=torch.int32, device=d))
+    got = out.cpu()
+    assert int(got.max()) < 128001 and len({int(t) // 32000 for t in got.tolist()}) == 4
+
+
+def test_sample_does_not_depend_on_the_batch(sample_kernel):
     V = 1000
     logits = rnd((4, V), torch.float32, 37, std=3.0)
     d = dev()

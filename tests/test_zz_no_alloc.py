@@ -120,22 +120,26 @@ def test_the_set_up_call_and_the_largest_request_that_fits():
     # n_seq = 0: the set-up alone (this is the call a server makes before it gives its memory away)
     assert lib.janis_attn_decode_static(None, None, None, 0, None, 0, None, None, None, 0, 4, 2, 8, 1.0, 0.0, 0, 0, 64, 1,
                                         torch.cuda.current_stream().cuda_stream) == 0
-    c = _case(5, torch.float32, lens=[130], slots=[1], nq=4, nkv=2)
-    out = torch.zeros((1, 4 * HD), dtype=torch.float32, device="cuda:0")
-    most = STATIC_SCRATCH_FLOATS // (4 * (HD + 2))          # chunks whose partial results just fit the array
-    assert (most + 1) * 4 * (HD + 2) > STATIC_SCRATCH_FLOATS >= most * 4 * (HD + 2)
-    # the launch is sized by max_chunks; the sequence is short, so all but three chunks find nothing to do
-    rc = lib.janis_attn_decode_static(
-        c["qkv"].data_ptr(), c["k"].data_ptr(), c["v"].data_ptr(), 0, c["table"].data_ptr(), c["table"].shape[1],
-        c["seq_slot"].data_ptr(), c["seq_len"].data_ptr(), out.data_ptr(), 1, 4, 2, 8, 1.0 / math.sqrt(HD), 25.0, 0, 0,
-        64, most, torch.cuda.current_stream().cuda_stream)
+    lens, slots = [130, 5, 64, 70, 1, 200, 129, 33], [1, 0, 3, 2, 5, 4, 7, 6]
+    c = _case(5, torch.float32, lens=lens, slots=slots, nq=4, nkv=2, n_pages=40, pages_per_seq=4)
+    n_seq = len(lens)
+    out = torch.zeros((n_seq, 4 * HD), dtype=torch.float32, device="cuda:0")
+    most = STATIC_SCRATCH_FLOATS // (n_seq * 4 * (HD + 2))      # chunks whose partial results just fit the array
+    assert (most + 1) * n_seq * 4 * (HD + 2) > STATIC_SCRATCH_FLOATS >= most * n_seq * 4 * (HD + 2) and most <= 8192
+    # the launch is sized by max_chunks; the sequences are short, so all but a few chunks find nothing to do
+    args = (c["qkv"].data_ptr(), c["k"].data_ptr(), c["v"].data_ptr(), 0, c["table"].data_ptr(), c["table"].shape[1],
+            c["seq_slot"].data_ptr(), c["seq_len"].data_ptr(), out.data_ptr(), n_seq, 4, 2, 8, 1.0 / math.sqrt(HD), 25.0, 0, 0, 64)
+    rc = lib.janis_attn_decode_static(*args, most, torch.cuda.current_stream().cuda_stream)
     assert rc == 0, lib.janis_last_error().decode()
     torch.cuda.synchronize()
     from tests import kernel_refs
-    plain = torch.empty((1, 4 * HD), dtype=torch.float64)
+    plain = torch.empty((n_seq, 4 * HD), dtype=torch.float64)
     kernel_refs.attn_decode(c["qkv"].cpu(), c["k"].cpu(), c["v"].cpu(), c["table"].cpu(), c["seq_slot"].cpu(),
                             c["seq_len"].cpu(), None, plain, 4, 2, HD, 1.0 / math.sqrt(HD), 25.0, 0, 0, 64, most)
     assert (out.double().cpu() - plain).abs().max().item() <= 2e-5 * plain.abs().max().item()
+    # one chunk more does not fit
+    assert lib.janis_attn_decode_static(*args, most + 1, torch.cuda.current_stream().cuda_stream) != 0
+    assert "static scratch holds" in lib.janis_last_error().decode()
 
 
 def test_static_scratch_refuses_what_does_not_fit():
