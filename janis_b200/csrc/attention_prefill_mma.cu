@@ -110,7 +110,11 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q_src, const bf16* __restrict__
     const int item = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int gtile = item / parts, part = item % parts;
     int seq = -1, q0 = 0, len = 0;
-    if (!find_tile(gtile, seq_len, n_seq, seq, q0, len, EXT ? cached.seq_start : nullptr)) return;
+    grid_dependents_launch();
+    // (the step's tables were written before the step's first kernel: the tile is found before the wait)
+    const bool found = find_tile(gtile, seq_len, n_seq, seq, q0, len, EXT ? cached.seq_start : nullptr);
+    grid_dependency_wait();
+    if (!found) return;
     const int head = blockIdx.x;
     const int kvh = head / (nq / nkv);
     const int first = seq_first_row[seq];             // row of the sequence's first token of this step
@@ -441,13 +445,12 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
                                    stream);
     if (done > 0) return 1;
     if (done < 0) {
-        // (a plain launch: this kernel reads its tables and operands at its top, without the dependency wait)
         dim3 grid(nq, n_tiles_bound * parts);
         auto kernel = ext ? pf::attn_prefill_mma_kernel<true> : pf::attn_prefill_mma_kernel<false>;
-        kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
-            (const bf16*)q_src, (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
-            kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial, cached);
-        if (launched("attn_prefill_mma")) return 1;
+        if (launch_kernel("attn_prefill_mma", kernel, grid, dim3(pf::THREADS), pf::SMEM_BYTES, stream, 1, (const bf16*)q_src,
+                          (const bf16*)kv_src, seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, q_row_heads,
+                          kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial, cached))
+            return 1;
     }
     if (parts == 1) return 0;
     return launch_kernel("attn_prefill_merge", pf::attn_prefill_merge_kernel, dim3(n_tiles_bound, nq, pf::BM / pf::MERGE_ROWS), dim3(256), 0, stream, 1,

@@ -17,6 +17,8 @@ gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ W, float*
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
+    grid_dependents_launch();
+    grid_dependency_wait();                           // x is the kernel before's result
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -73,6 +75,5 @@ JANIS_EXPORT int janis_gemm_f32(const float* x, const float* W, float* out, int 
     if (K <= 0) return fail("gemm_f32: K must be positive, found %d", K);
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return fail("gemm_f32: too many rows (%d)", M);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, W, out, M, N, K, cap);
-    return launched("gemm_f32");
+    return launch_kernel("gemm_f32", gemm_f32_kernel, grid, dim3(256), 0, stream, 1, x, W, out, M, N, K, cap);
 }
