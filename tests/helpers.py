@@ -77,3 +77,25 @@ def run_requests(engine, requests, prompt_lens, max_live=None):
                 pos[i] += 1
         engine.cache.audit()
     return [torch.cat(g) for g in got]
+
+
+def run_in_pieces(engine, requests, chunk):
+    """Feed each request in steps of `chunk` tokens onto what the steps before left in the cache, the requests
+    side by side (a shorter one ends earlier); logits at every position: list of [len_i, vocab] tensors (CPU)."""
+    from janis_b200 import StepEntry
+    slots = [engine.alloc_slot() for _ in requests]
+    got = [[] for _ in requests]
+    pos = [0] * len(requests)
+    while any(p < len(r) for p, r in zip(pos, requests)):
+        live = [i for i, r in enumerate(requests) if pos[i] < len(r)]
+        take = [min(chunk, len(requests[i]) - pos[i]) for i in live]
+        out = engine.step([StepEntry(slots[i], requests[i][pos[i]:pos[i] + t], list(range(t))) for i, t in zip(live, take)])
+        o = 0
+        for i, t in zip(live, take):
+            got[i].append(out[o:o + t].cpu())
+            o += t
+            pos[i] += t
+    for s in slots:
+        engine.free_slot(s)
+    engine.cache.audit()
+    return [torch.cat(g) for g in got]
