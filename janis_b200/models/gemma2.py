@@ -15,7 +15,6 @@ import numpy as np
 from ..config.gemma2 import SLIDING, Gemma2Config
 from ..engine.model import DecoderModel, LayerCall
 from ..parts import registry as parts
-from ..parts.embedding import Embedding, LMHead
 from ..registry import register_architecture
 
 
@@ -47,10 +46,12 @@ def build_gemma2(cfg: Gemma2Config) -> DecoderModel:
     table = "model.embed_tokens.weight"
     return DecoderModel(
         cfg,
-        embedding=Embedding(cfg.vocab_size, H, table, scale=float(np.float32(math.sqrt(float(H))))),
+        embedding=parts.make("embedding", "scaled_table", vocab=cfg.vocab_size, hidden=H, table_name=table,
+                             scale=float(np.float32(math.sqrt(float(H))))),
         blocks=blocks,
         final_norm=norm("model.norm.weight"),
-        head=LMHead(cfg.vocab_size, H, table, softcap=cfg.final_logit_softcapping),
+        head=parts.make("head", "capped_linear", vocab=cfg.vocab_size, hidden=H, table_name=table,
+                        softcap=cfg.final_logit_softcapping),
         schedule=[LayerCall(i, i) for i in range(cfg.num_hidden_layers)],
         ignorable_tensors=("lm_head.weight", "*.rotary_emb.inv_freq"),
         stop_tokens=cfg.eos_token_id,

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from typing import Any, Callable
 
-FAMILIES = ("mixer", "feed_forward", "norm", "position", "block")
+FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
 
 _KINDS: dict[str, dict[str, Callable[..., Any]]] = {f: {} for f in FAMILIES}
 
@@ -40,6 +40,7 @@ def make(family: str, kind: str, **params):
 def _register_builtin() -> None:
     from .attention import SoftmaxAttention
     from .block import PreNormBlock, SandwichBlock
+    from .embedding import Embedding, LMHead
     from .feedforward import GatedMLP
     from .norm import RMSNorm
     from .position import NoPosition, RotaryEncoding
@@ -51,6 +52,8 @@ def _register_builtin() -> None:
     register("position", "none", NoPosition)
     register("block", "sandwich", SandwichBlock)
     register("block", "pre_norm", PreNormBlock)
+    register("embedding", "scaled_table", Embedding)       # rows of a table times a constant (1 for most models)
+    register("head", "capped_linear", LMHead)              # y W^T, tied to the embedding's table or not, then an optional cap
 
 
 _register_builtin()

@@ -225,6 +225,31 @@ class RunningMean(Mixer):
         return (y @ self.w.T).to(ctx.rt.dtype)
 
 
+class RunningMeanInGraphs(RunningMean):
+    """The same mixer written so that a step can be recorded into a CUDA graph: no indexing by a mask (which
+    synchronises), no host-side shapes that depend on the data.  Sequences meet the state through a 0/1 matrix
+    [sequences, slots]; a padding sequence (slot -1) has a row of zeros there: it reads a state of zeros, stores
+    nothing and changes no other row, which is what a recorded step asks of every part."""
+
+    graph_safe = True
+
+    def forward(self, x, ctx, line):
+        state = line["sum"].data                                   # [slots, hidden]
+        T, S = ctx.n_tok, ctx.n_seq
+        seq = ctx.tok_seq[:T].long()
+        slot = ctx.seq_slot[:S].long()
+        own = (slot[:, None] == torch.arange(state.shape[0], device=slot.device)[None, :]).float()     # [S, slots]
+        xf = x.float()
+        member = (seq[None, :] == torch.arange(S, device=seq.device)[:, None]).float()                 # [S, T]
+        rows = torch.arange(T, device=seq.device)
+        earlier = (rows[None, :] <= rows[:, None]).float() * member[seq]                                # [T, T]: same sequence, not later
+        total = earlier @ xf + (own @ state)[seq]
+        if line.write:
+            state += own.T @ (member @ xf)                         # every sequence's sum of this step onto its slot
+        y = total / (ctx.tok_pos[:T].float() + 1.0)[:, None]
+        return (y @ self.w.T).to(ctx.rt.dtype)
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     hidden: int
@@ -347,6 +372,57 @@ def test_a_toy_architecture_with_a_stateful_mixer(on, dtype, toy_registered):
     out = eng.generate([[1, 2, 3], [4]], max_tokens=5, stop=())
     assert [len(o) for o in out] == [5, 5]
     eng.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_stateful_mixer_inside_recorded_steps(dtype):
+    """Fixed-size state meets CUDA graphs: the toy architecture with the graph-safe form of its stateful mixer runs its
+    decode steps (with padding rows) and its short prompt steps (with padding tokens and sequences) from recorded
+    graphs, and gives what it gives launched kernel by kernel, and what the plain model gives."""
+    parts.register("mixer", "test_running_mean", RunningMeanInGraphs, replace=True)
+    janis_b200.register_architecture("ToyForCausalLM", ToyConfig, build_toy, replace=True)
+    try:
+        rt = runtime("cuda", dtype)
+        outs = []
+        host = None
+        for graphs in (True, False):
+            arch, cfg, model = janis_b200.build_model(TOY)
+            assert model.graph_safe
+            host = random_tensors(model.tensor_specs(), 21, "cpu")
+            model.load(WeightStore({k: v.to(rt.device) for k, v in host.items()}), rt)
+            eng = Engine(model, rt, max_tokens=16 * 64, max_batch=5, use_graphs=graphs)
+            assert eng.stepper.use_graphs is graphs
+            reqs = [random_tokens(50, n, 230 + n) for n in (7, 1, 20, 70, 12)]
+            got = None
+            for _ in range(3):              # the same shapes three times: launched, recorded, replayed; slots and state used again
+                got = run_requests(eng, reqs, [3, 1, 20, 40, 2], max_live=5)
+            # prompt steps that ask for the last logits only are recorded once their padded shape has come twice
+            from janis_b200 import StepEntry
+            last = None
+            for _ in range(3):
+                slots = [eng.alloc_slot() for _ in reqs[:3]]
+                last = eng.step([StepEntry(sl, r, [len(r) - 1]) for sl, r in zip(slots, reqs[:3])]).cpu()
+                for sl in slots:
+                    eng.free_slot(sl)
+            if graphs:
+                assert eng.stepper._graphs and eng.stepper._prompt_graphs
+            outs.append(got + [last])
+            eng.close()
+        w = {k: v.double() for k, v in host.items()}
+        ends = torch.stack([toy_plain(cfg, w, r)[-1] for r in reqs[:3]])
+        for g, how in ((outs[0][-1], "recorded"), (outs[1][-1], "launched")):
+            err = (g.double() - ends).abs().max().item()
+            assert err <= (1e-4 if dtype == torch.float32 else 3e-2) * ends.abs().max().item(), f"toy prompt step, {how}: {err:.3e}"
+        for i, (a, b, r) in enumerate(zip(outs[0][:-1], outs[1][:-1], reqs)):
+            want = toy_plain(cfg, w, r)
+            scale = want.abs().max().item()
+            for g, how in ((a, "recorded"), (b, "launched")):
+                err = (g.double() - want).abs().max().item()
+                assert err <= (1e-4 if dtype == torch.float32 else 3e-2) * scale, f"toy request {i}, {how}: {err:.3e} / {scale:.3e}"
+    finally:
+        parts.unregister("mixer", "test_running_mean")
+        janis_b200.unregister_architecture("ToyForCausalLM")
 
 
 # ---------------------------------------------------------------------------
