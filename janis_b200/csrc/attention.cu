@@ -511,9 +511,14 @@ __device__ __forceinline__ void fill_heads(bf16* out, int s, int nq, int nkv, in
         out[((size_t)s * nq + h0 + idx / HD) * HD + idx % HD] = __float2bfloat16_rn(v);
 }
 
+// NS stages: three give a CTA a deeper pipeline, two leave room for three CTAs an SM instead of two.  With more CTAs
+// than two an SM can hold, more CTAs in flight pay more than depth (64 sequences of unequal lengths: 63.6 -> 56.5 us a
+// layer with two stages; 8 sequences of 8,100 keys: 49.5 -> 47.8 us); with fewer CTAs than that, depth does (one
+// sequence: 523 against 545 tok/s); four stages and one CTA an SM are far slower (98 us).  The launch chooses.
+template <int NS>
 struct MmaDecode {
     static constexpr int WARPS = 4;
-    static constexpr int STAGES = JANIS_STAGES;
+    static constexpr int STAGES = NS;
     static constexpr int TILE = HD <= 128 ? 64 : 32;                 // keys per stage
     static constexpr int NT = TILE / 32;                              // 8-key column tiles per warp and stage
     static constexpr int TILE_BYTES = TILE * HD * 2;
@@ -529,13 +534,13 @@ struct MmaDecode {
 
 // DIRECT: the launch has one chunk per sequence and the kernel writes the result itself (`out`); otherwise it
 // leaves a partial per chunk for the merge kernel.
-template <int RB, bool DIRECT>
-__global__ void __launch_bounds__(MmaDecode::WARPS * 32)
+template <int RB, bool DIRECT, int NS>
+__global__ void __launch_bounds__(MmaDecode<NS>::WARPS * 32)
 attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
                        const int* __restrict__ page_table, int table_stride, const int* __restrict__ seq_slot,
                        const int* __restrict__ seq_len, float* __restrict__ partial, int nq, int nkv, int q_row_heads,
                        float scale, float cap, int window, int ring_len, int chunk, bf16* __restrict__ out) {
-    typedef MmaDecode S;
+    typedef MmaDecode<NS> S;
     extern __shared__ __align__(128) unsigned char stage_mem[];
     __shared__ __align__(8) unsigned long long full[S::STAGES];
     const int s = blockIdx.z;
@@ -981,31 +986,68 @@ JANIS_EXPORT int janis_attn_wait_probe(int tries, int* status, cudaStream_t stre
     return launched("wait_probe");
 }
 
-template <int RB>
-static int launch_decode_mma_rb(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table,
+template <int RB, int NS>
+static int launch_decode_mma_ns(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table,
                                 int table_stride, const int* seq_slot, const int* seq_len, float* partial, int n_seq, int nq,
                                 int nkv, int q_row_heads, float scale, float cap, int window, int ring_len, int chunk,
                                 int max_chunks, bf16* out, cudaStream_t stream) {
+    typedef MmaDecode<NS> S;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             MmaDecode::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, false, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             S::SMEM_BYTES);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     MmaDecode::SMEM_BYTES);
-        if (e != cudaSuccess) return fail("attn_decode: shared memory of %d bytes refused: %s", MmaDecode::SMEM_BYTES,
+            e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, true, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     S::SMEM_BYTES);
+        if (e != cudaSuccess) return fail("attn_decode: shared memory of %d bytes refused: %s", S::SMEM_BYTES,
                                           cudaGetErrorString(e));
         configured = true;
     }
     const int rep = nq / nkv;
     dim3 grid(max_chunks, nkv * ((rep + RB - 1) / RB), n_seq);
     if (out != nullptr)
-        return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, true>, grid, dim3(MmaDecode::WARPS * 32),
-                             MmaDecode::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
+        return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, true, NS>, grid, dim3(S::WARPS * 32),
+                             S::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
                              partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, out);
-    return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, false>, grid, dim3(MmaDecode::WARPS * 32),
-                         MmaDecode::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
+    return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, false, NS>, grid, dim3(S::WARPS * 32),
+                         S::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
                          partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, out);
+}
+
+static int decode_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+static int g_mma_stages = 0;        // 0: chosen per launch from the number of CTAs; 2 or 3: fixed (tests and tuning)
+
+// Fixes the stages of the tensor-core decode kernel (2 or 3; 0: chosen from the launch's size again).
+JANIS_EXPORT void janis_attn_set_decode_stages(int stages) { g_mma_stages = stages == 2 || stages == 3 ? stages : 0; }
+
+// How many stages a launch of this many CTAs gets: two (three CTAs an SM) when it has more CTAs than two an SM would
+// hold at once, else three.  The host sizes its chunks by the same rule.
+JANIS_EXPORT int janis_attn_decode_stages(long long n_ctas) {
+    if (g_mma_stages) return g_mma_stages;
+    return n_ctas > 2LL * decode_sm_count() ? 2 : 3;
+}
+
+template <int RB>
+static int launch_decode_mma_rb(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table,
+                                int table_stride, const int* seq_slot, const int* seq_len, float* partial, int n_seq, int nq,
+                                int nkv, int q_row_heads, float scale, float cap, int window, int ring_len, int chunk,
+                                int max_chunks, bf16* out, cudaStream_t stream) {
+    const int rep = nq / nkv;
+    const long long n_ctas = (long long)max_chunks * nkv * ((rep + RB - 1) / RB) * n_seq;
+    if (janis_attn_decode_stages(n_ctas) == 2)
+        return launch_decode_mma_ns<RB, 2>(qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, n_seq, nq, nkv,
+                                           q_row_heads, scale, cap, window, ring_len, chunk, max_chunks, out, stream);
+    return launch_decode_mma_ns<RB, 3>(qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, n_seq, nq, nkv,
+                                       q_row_heads, scale, cap, window, ring_len, chunk, max_chunks, out, stream);
 }
 
 static int launch_decode_mma(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table, int table_stride,
@@ -1029,7 +1071,7 @@ static int launch_decode(const T* qkv, const T* kpool, const T* vpool, const int
                          int q_row_heads, float scale, float cap, int window, int ring_len, int chunk, int max_chunks,
                          cudaStream_t stream) {
     const int rep = nq / nkv;
-    if (g_decode_kernel == 2 && sizeof(T) == 2 && MmaDecode::OK) {
+    if (g_decode_kernel == 2 && sizeof(T) == 2 && MmaDecode<2>::OK) {
         // a launch of one chunk per sequence writes the result itself: no partials, no merge
         bf16* direct = max_chunks == 1 ? (bf16*)out : nullptr;
         if (launch_decode_mma((const bf16*)qkv, (const bf16*)kpool, (const bf16*)vpool, page_table, table_stride, seq_slot,

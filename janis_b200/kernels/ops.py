@@ -102,6 +102,10 @@ def attention_lib(head_dim: int):
         lib.janis_attn_prefill_tile.restype = I
         lib.janis_attn_set_decode_kernel.argtypes = [I]
         lib.janis_attn_set_decode_kernel.restype = None
+        lib.janis_attn_decode_stages.argtypes = [c_longlong]
+        lib.janis_attn_decode_stages.restype = I
+        lib.janis_attn_set_decode_stages.argtypes = [I]
+        lib.janis_attn_set_decode_stages.restype = None
         lib.janis_attn_wait_timeouts.restype = I
         lib.janis_attn_wait_probe.argtypes = [I, P, P]
         lib.janis_attn_set_overlap.argtypes = [I]
@@ -596,6 +600,20 @@ def attn_set_decode_kernel(hd: int, which: int = 2) -> None:
     runs), 0 = straight from global memory into registers."""
     attention_lib(hd).janis_attn_set_decode_kernel(int(which))
     _decode_kernel[hd] = int(which)
+
+
+def attn_decode_resident(hd: int, dtype, n_ctas: int, sm_count: int) -> int:
+    """CTAs of a decode-attention launch of n_ctas CTAs that the GPU holds at once: the bfloat16 tensor-core kernel
+    runs with two stages and three CTAs an SM when a launch has more CTAs than two an SM would hold, else with three
+    stages and two CTAs an SM; the other kernels hold two."""
+    if dtype == torch.bfloat16 and hd <= 256 and _decode_kernel.get(hd, 2) == 2:
+        return (3 if attention_lib(hd).janis_attn_decode_stages(int(n_ctas)) == 2 else 2) * sm_count
+    return 2 * sm_count
+
+
+def attn_set_decode_stages(hd: int, stages: int = 0) -> None:
+    """Fix the stages of the bfloat16 tensor-core decode kernel (2 or 3; 0: chosen per launch, the default).  For tests."""
+    attention_lib(hd).janis_attn_set_decode_stages(int(stages))
 
 
 def attn_wait_timeouts(hd: int) -> int:

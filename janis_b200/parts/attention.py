@@ -85,7 +85,7 @@ class SoftmaxAttention(Mixer):
     def _decode_geometry(self, ctx: StepContext, sm_count: int):
         """(chunk, most chunks a sequence has): how the keys of a decode step are cut up for the CTAs.
 
-        A CTA per (sequence, key/value head, chunk); two CTAs fit an SM.  In tiles of 32 keys a CTA costs the tiles
+        A CTA per (sequence, key/value head, chunk); two or three CTAs fit an SM.  In tiles of 32 keys a CTA costs the tiles
         of its chunk plus a fixed share for starting its pipeline and for the merge.  Long chunks amortise the fixed
         share, short ones fill the SMs and even the load out.  The host knows the step's lengths by their bound,
         their mean (in eighths of the bound) and whether they are about equal; all three are part of a recorded
@@ -95,12 +95,16 @@ class SoftmaxAttention(Mixer):
         bound = max(ctx.len_bound, 1)
         span = min(bound, self.window) if self.window else bound
         pairs = ctx.n_seq * self.n_kv_heads
-        resident = 2 * sm_count
+        held = getattr(ctx.rt.ops, "attn_decode_resident", None)       # CTAs of a launch that the GPU holds at once
         mean = min(ctx.len_mean or bound, bound)
         seen = min(mean, self.window) if self.window else mean          # keys a sequence of mean length attends over
         extra = 1 if self.window and seen >= self.window else 0         # a window seldom starts on a chunk's border
         best = None
         for chunk in range(64, 2049, 64):
+            launched = (bound + chunk - 1) // chunk
+            if self.window:
+                launched = min(launched, (self.window + chunk - 1) // chunk + 1)
+            resident = held(self.head_dim, ctx.rt.dtype, pairs * launched, sm_count) if held else 2 * sm_count
             if ctx.len_even:
                 # CTAs of equal length run in waves
                 n_chunks = (seen + chunk - 1) // chunk + extra

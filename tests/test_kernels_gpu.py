@@ -660,17 +660,21 @@ def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, kernel):
     scale, cap = 1.0 / math.sqrt(hd), 30.0
     if kernel == 2 and dtype != torch.bfloat16:
         pytest.skip("the tensor-core decode kernel is bfloat16 only")
-    ops().attn_set_decode_kernel(hd, kernel)
-    try:
-        ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
-                          window, ring, chunk, max_chunks)
-    finally:
-        ops().attn_set_decode_kernel(hd, 2)
-    assert ops().attn_wait_timeouts(hd) == 0
     want = torch.empty((n_seq, nq * hd), dtype=torch.float64)
     R.attn_decode(qkv.cpu(), k.cpu(), v.cpu(), perm, seq_slot, seq_len, None, want, nq, nkv, hd, scale, cap, window,
                   ring, chunk, max_chunks)
-    close(out, want, tol_of(dtype), "attn_decode")
+    ops().attn_set_decode_kernel(hd, kernel)
+    try:
+        for stages in ((2, 3) if kernel == 2 else (0,)):        # the tensor-core kernel with both depths of its pipeline
+            ops().attn_set_decode_stages(hd, stages)
+            out.fill_(7.0)
+            ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
+                              window, ring, chunk, max_chunks)
+            close(out, want, tol_of(dtype), f"attn_decode (stages {stages})")
+    finally:
+        ops().attn_set_decode_kernel(hd, 2)
+        ops().attn_set_decode_stages(hd, 0)
+    assert ops().attn_wait_timeouts(hd) == 0
 
 
 @pytest.mark.parametrize("hd", [144, 272, 496])
