@@ -874,6 +874,39 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const int* 
         }
         return;
     }
+    if (n_chunks <= 64) {
+        // 33 to 64 chunks: the same with two chunks a lane (c and c + 32), still without a block barrier
+        const bool m0 = lane < n_chunks, m1 = lane + 32 < n_chunks;
+        const float mc0 = m0 ? p[(size_t)lane * (HD + 2)] : -INFINITY;
+        const float lc0 = m0 ? p[(size_t)lane * (HD + 2) + 1] : 0.f;
+        const float mc1 = m1 ? p[(size_t)(lane + 32) * (HD + 2)] : -INFINITY;
+        const float lc1 = m1 ? p[(size_t)(lane + 32) * (HD + 2) + 1] : 0.f;
+        const float mx = warp_max(fmaxf(mc0, mc1));
+        const float w_lo = mc0 == -INFINITY ? 0.f : expf(mc0 - mx), w_hi = mc1 == -INFINITY ? 0.f : expf(mc1 - mx);
+        float l = 0.f;                           // in chunk order, the same in every thread
+        for (int c = 0; c < 32; ++c) l += __shfl_sync(0xffffffffu, lc0 * w_lo, c);
+        for (int c = 32; c < n_chunks; ++c) l += __shfl_sync(0xffffffffu, lc1 * w_hi, c - 32);
+        const float inv = 1.0f / l;
+        for (int d0 = 0; d0 < HD; d0 += blockDim.x) {
+            const int d = d0 + threadIdx.x;
+            float a0 = 0.f, a1 = 0.f;
+            int c = 0;
+            for (; c + 2 <= n_chunks; c += 2) {          // (c is even: c and c + 1 lie in the same half)
+                const float w0 = __shfl_sync(0xffffffffu, c < 32 ? w_lo : w_hi, c & 31);
+                const float w1 = __shfl_sync(0xffffffffu, c < 32 ? w_lo : w_hi, (c + 1) & 31);
+                if (d < HD) {
+                    a0 += p[(size_t)c * (HD + 2) + 2 + d] * w0;
+                    a1 += p[(size_t)(c + 1) * (HD + 2) + 2 + d] * w1;
+                }
+            }
+            if (c < n_chunks) {
+                const float w0 = __shfl_sync(0xffffffffu, c < 32 ? w_lo : w_hi, c & 31);
+                if (d < HD) a0 += p[(size_t)c * (HD + 2) + 2 + d] * w0;
+            }
+            if (d < HD) o[d] = from_float<T>((a0 + a1) * inv);
+        }
+        return;
+    }
     // the maximum over chunks (any order gives the same value)
     float mx = -INFINITY;
     for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) mx = fmaxf(mx, p[(size_t)c * (HD + 2)]);

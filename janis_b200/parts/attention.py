@@ -118,8 +118,8 @@ class SoftmaxAttention(Mixer):
                 cost = min(chunk, span) // 32 + 4 + (share if n_ctas > resident else share / 2) + (span / chunk + extra) / 8
             if chunk < bound:
                 cost += 6          # more than one chunk a sequence: partial results and a merge kernel
-            if (min(bound, span) + chunk - 1) // chunk + (1 if self.window and span >= self.window else 0) > 32:
-                cost += 8          # beyond 32 chunks the merge forms its weights block-wide, not per warp: twice the time
+            if (min(bound, span) + chunk - 1) // chunk + (1 if self.window and span >= self.window else 0) > 64:
+                cost += 8          # beyond 64 chunks the merge forms its weights block-wide, not per warp: twice the time
             if best is None or cost < best[0]:
                 best = (cost, chunk)
         chunk = best[1]

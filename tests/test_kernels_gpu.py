@@ -722,9 +722,11 @@ def test_attention_at_head_sizes_between_the_usual_ones(hd):
 
 
 @pytest.mark.parametrize("window,ring", [(0, 0), (1024, 1024)])
-def test_attn_decode_over_thousands_of_keys(window, ring):
-    """Long sequences: many tiles per chunk, many chunks, pages far apart, a far key that must win."""
-    nq, nkv, hd, chunk = 4, 2, 128, 704
+@pytest.mark.parametrize("chunk", [704, 128, 64])
+def test_attn_decode_over_thousands_of_keys(window, ring, chunk):
+    """Long sequences: many tiles per chunk, many chunks (8, 40 and 79 of them: the merge kernel's three ways of
+    forming its weights), pages far apart, a far key that must win."""
+    nq, nkv, hd = 4, 2, 128
     lens = [5000, 3, 2049]
     slots = [1, 2, 0]
     pages_per_seq = 80 if ring == 0 else ring // R.PAGE
