@@ -140,6 +140,51 @@ def test_trace_run_as_a_user_runs_it(dtype, model_dirs, plain_models, tmp_path):
         assert_logits(torch.cat(got[f"r{i}"]), plain_logits(plain_models, key, r), dtype, f"trace request {i}")
 
 
+def test_replay_of_a_trace_over_the_cpu_statements_and_its_refusals(model_dirs, plain_models, tmp_path):
+    """`run_trace` itself, in this process, over the engine on the plain kernel statements: the records it reads,
+    the slots it takes and gives back, the files and the lines it writes, and what it refuses."""
+    import io
+    from janis_b200.replay import TraceError, run_trace
+    key = "B"
+    V = TINY["B"]["vocab_size"]
+    lens = [12, 5, 37, 1, 9]
+    reqs = [random_tokens(V, n, 140 + n) for n in lens]
+    steps, _ = _trace(reqs, [max(1, n - 4) for n in lens], batch_of=2)
+    eng = make_engine(model_dirs[key], "float32", "refs", max_tokens=4 * 64, max_batch=2)
+    out, said = tmp_path / "out", io.StringIO()
+    lines = [json.dumps(s) for s in steps]
+    lines.insert(1, "   ")                                             # an empty line is no step
+    assert run_trace(eng, lines, str(out), said) == len(steps)
+    assert said.getvalue().split() == [w for s in steps for w in ("done", str(s["step"]))]
+    got = {f"r{i}": [] for i in range(len(reqs))}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        path = out / f"{s['step']}.f32"
+        assert path.exists() == (wanted > 0)
+        if not wanted:
+            continue
+        arr = np.fromfile(path, dtype="<f4").reshape(-1, V)
+        assert arr.shape[0] == wanted
+        o = 0
+        for e in s["entries"]:
+            got[e["id"]].append(torch.from_numpy(arr[o:o + len(e["want"])].copy()))
+            o += len(e["want"])
+    for i, r in enumerate(reqs):
+        assert_logits(torch.cat(got[f"r{i}"]), plain_logits(plain_models, key, r), "float32", f"trace request {i}")
+    assert eng.cache.live_slots() == [] and not list(out.glob(".*tmp"))
+    # a step that wants nothing writes no file; a request that ends without having started, and a line that is
+    # no record, are refused with the line's number
+    quiet = [json.dumps({"step": 999, "entries": [{"id": "q", "tokens": [1, 2, 3], "want": []}], "end": ["q"]})]
+    assert run_trace(eng, quiet, str(out), io.StringIO()) == 1 and not (out / "999.f32").exists()
+    with pytest.raises(TraceError, match="line 1.*'zz'.*never started"):
+        run_trace(eng, [json.dumps({"step": 0, "entries": [], "end": ["zz"]})], str(out), io.StringIO())
+    with pytest.raises(TraceError, match="line 2: not a step record"):
+        run_trace(eng, [quiet[0], "{\"step\": 1"], str(out), io.StringIO())
+    assert eng.cache.live_slots() == []
+    eng.cache.audit()
+    eng.close()
+
+
 @GPU
 def test_janis_generate_command(model_dirs, plain_models):
     key = "B"
