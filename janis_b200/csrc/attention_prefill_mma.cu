@@ -24,6 +24,12 @@
 // queries into pieces of at most `piece` tiles (no more than `parts` = 4 pieces): each piece is one CTA's, which
 // writes its maximum, sum and unnormalised output to scratch, and a second kernel adds the pieces.
 #include <algorithm>
+#include <functional>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <tuple>
+#include <vector>
 
 #include "attention_prefill_tiles.cuh"
 
@@ -388,6 +394,79 @@ static int g_prefill_piece = 0;     // key tiles per piece of a shared tile of q
 // Fixes the size of the pieces that shared tiles of queries are cut into (0: automatic again).
 JANIS_EXPORT void janis_attn_set_prefill_piece(int piece) { g_prefill_piece = piece > 0 ? piece : 0; }
 
+// How long a step takes whose shared tiles are cut into pieces of `piece` key tiles, in microseconds, by a model
+// of four numbers fitted to a B200 at head size 256 (150 timings of 1 to 7 prompts of 300 to 4,096 tokens and
+// pieces of 4 to 140 tiles, 4 % off on average): a CTA costs `cta` before and after its tiles (9.9 us for the tcgen05
+// kernel: its launch, Q and the first keys, the two tiles the softmax runs behind, the way out), `tile` per key
+// tile, 1.9 us more when it leaves a partial result, and the merge 0.8 us and 0.39 us per round of partial rows.
+// CTAs go to the SM that is free first, in the order of their launch.  The step's lengths are on the device: the
+// model takes n_seq sequences of equal length.
+static double prefill_model_us(int n_seq, int len, int nq, int window, int parts, int piece, int sms, double cta,
+                               double tile, int* longest) {
+    std::vector<std::pair<int, bool>> items;          // key tiles, leaves a partial result; in tile order
+    long long split_parts = 0;
+    *longest = 0;
+    for (int q0 = 0; q0 < len; q0 += pf::BM) {
+        const int q_last = std::min(q0 + pf::BM, len) - 1;
+        const int j_first = window > 0 ? std::max(0, q0 - window + 1) : 0;
+        const int n = (q_last - j_first / pf::BN * pf::BN) / pf::BN + 1;
+        *longest = std::max(*longest, n);
+        const int np = pf::parts_of(n, parts, piece);
+        for (int p = 0; p < np; ++p) items.push_back({(int)((long long)n * (p + 1) / np - (long long)n * p / np), np > 1});
+        if (np > 1) split_parts += np;
+    }
+    std::priority_queue<double, std::vector<double>, std::greater<double>> free_at;
+    for (int i = 0; i < sms; ++i) free_at.push(0.0);
+    double end = 0.0;
+    for (int s = n_seq - 1; s >= 0; --s)              // the last tile of the last sequence is launched first
+        for (int i = (int)items.size() - 1; i >= 0; --i)
+            for (int h = 0; h < nq; ++h) {
+                const double t = free_at.top() + cta + tile * items[i].first + (items[i].second ? 1.9 : 0.0);
+                free_at.pop();
+                free_at.push(t);
+                end = std::max(end, t);
+            }
+    if (split_parts) end += 0.8 + 0.39 * (double)(split_parts * n_seq * nq) / sms;
+    return end;
+}
+
+// The piece that the model likes best for a step (the largest among equals: fewer partial results), remembered per
+// shape of step.  A piece as long as the longest tile's keys means that nothing is shared.
+static int prefill_piece_for(int n_tok, int n_seq, int nq, int window, int parts, bool tc05, int* longest) {
+    static std::map<std::tuple<int, int, int, int, int, bool>, std::pair<int, int>> known;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_tuple(n_tok, n_seq, nq, window, parts, tc05);
+    auto it = known.find(key);
+    if (it == known.end()) {
+        const int len = (n_tok + n_seq - 1) / n_seq, sms = sm_count();
+        // per key tile: the softmax's share does not depend on the head size, the products' does; the mma.sync
+        // kernel took 2.7 times as long per tile at head size 256 and has less to do around its tiles
+        const double tile = tc05 ? 1.0 + 0.43 * pf::HD / 256.0 : 3.9 * pf::HD / 256.0, cta = tc05 ? 9.9 : 6.0;
+        int most = 0, best = 4;
+        double best_us = prefill_model_us(n_seq, len, nq, window, parts, 4, sms, cta, tile, &most);
+        for (int piece = 5; piece <= most; piece += piece < 16 ? 1 : piece < 64 ? 2 : 8) {
+            int unused;
+            const double us = prefill_model_us(n_seq, len, nq, window, parts, piece, sms, cta, tile, &unused);
+            if (us <= best_us) { best_us = us; best = piece; }
+        }
+        if (most > 4) {                                // and nothing shared at all
+            int unused;
+            if (prefill_model_us(n_seq, len, nq, window, 1, most, sms, cta, tile, &unused) <= best_us) best = most;
+        }
+        it = known.emplace(key, std::make_pair(best, most)).first;
+    }
+    *longest = it->second.second;
+    return it->second.first;
+}
+
+// What the step of these sizes would be cut into (for tests and measurements): the piece, in key tiles.
+JANIS_EXPORT int janis_attn_prefill_piece(int n_tok, int n_seq, int n_tiles_bound, int nq, int window, int tc05) {
+    if (n_seq <= 0 || n_tok <= 0) return 0;
+    int longest = 0;
+    return prefill_piece_for(n_tok, n_seq, nq, window, janis_attn_prefill_parts(n_tiles_bound, nq), tc05 != 0, &longest);
+}
+
 static int g_prefill_kernel = 1;    // 1: tcgen05 where the head size allows it, else mma.sync; 0: mma.sync always
 
 // Which kernel janis_attn_prefill_mma launches (both give the same results up to rounding).
@@ -430,13 +509,18 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
     }
     int parts = janis_attn_prefill_parts(n_tiles_bound, nq);
     if (partial == nullptr || partial_floats < janis_attn_prefill_scratch(n_tiles_bound, nq)) parts = 1;
-    // The pieces that a tile of queries is cut into grow with an SM's even share of the step's key tiles (the
-    // step's lengths are on the device: the estimate takes sequences of equal length).  A CTA costs about as much
-    // as 3 key tiles before and after its tiles, and a piece more is a row of scratch more to merge: measured on
-    // prompts of 512 to 4,096 tokens, pieces of the share plus 3, at most 16, were the fastest or close to it.
-    const long long avg_key_tiles = (long long)n_tok / n_seq / (2 * pf::BN) + 1;
-    const long long share = (long long)n_tiles_bound * nq * avg_key_tiles / sm_count();
-    const int piece = g_prefill_piece > 0 ? g_prefill_piece : (int)std::min<long long>(16, std::max<long long>(4, share + 3));
+    // The pieces that shared tiles of queries are cut into: what a model of the step's time likes best.  When that
+    // is "none shared", the step is launched without the places of the parts and without the merge.
+    const bool tc05 = g_prefill_kernel == 1 && !ext && pf::TC05_HEAD;
+    int piece = g_prefill_piece;
+    if (piece <= 0 && parts > 1) {
+        int longest = 0;
+        piece = prefill_piece_for(n_tok, n_seq, nq, window, parts, tc05, &longest);
+        // (the sequences' real lengths may differ from the model's: a tile of queries of a step that starts its
+        // sequences never has more key tiles than the step has tokens)
+        if (!ext && piece >= longest && piece >= n_tok / pf::BN + 1) parts = 1;
+    }
+    if (piece <= 0) piece = 4;
     if ((long long)n_tiles_bound * parts > 65535) return fail("attn_prefill_mma: %d tiles of queries exceed the grid", n_tiles_bound);
     int done = -1;
     if (g_prefill_kernel == 1 && !ext)                // the tcgen05 kernel takes sequences that start at position 0

@@ -40,7 +40,7 @@ using pf::BM;
 using pf::BN;
 using pf::HD;
 
-constexpr bool SUPPORTED = HD % 64 == 0 && HD <= 256;
+constexpr bool SUPPORTED = pf::TC05_HEAD;
 constexpr int SLABS = SUPPORTED ? HD / 64 : 1;        // slabs of 64 features: one 128-byte swizzle row each
 constexpr int Q_SLAB = BM * 128;                      // bytes
 constexpr int KV_SLAB = BN * 128;

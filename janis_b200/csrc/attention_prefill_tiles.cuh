@@ -17,6 +17,7 @@ constexpr int BN = HD <= 256 ? 64 : 32;               // keys per tile
 constexpr int WARPS = HD <= 256 ? 8 : 4;              // 16 query rows each (mma.sync kernel)
 constexpr int BM = WARPS * 16;                        // queries per tile
 constexpr int PART_ROW = HD + 2;                      // floats of a partial row: maximum, sum, output
+constexpr bool TC05_HEAD = HD % 64 == 0 && HD <= 256; // head sizes that the tcgen05 kernel takes
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);

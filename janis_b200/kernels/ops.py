@@ -95,6 +95,8 @@ def attention_lib(head_dim: int):
         lib.janis_attn_set_prefill_kernel.restype = None
         lib.janis_attn_set_prefill_piece.argtypes = [I]
         lib.janis_attn_set_prefill_piece.restype = None
+        lib.janis_attn_prefill_piece.argtypes = [I, I, I, I, I, I]
+        lib.janis_attn_prefill_piece.restype = I
         lib.janis_attn_tc05_timeouts.restype = I
         lib.janis_attn_timeouts_async.argtypes = [P, P]
         lib.janis_attn_prefill_scratch.argtypes = [I, I]
@@ -587,6 +589,13 @@ def attn_set_prefill_piece(hd: int, piece: int = 0) -> None:
     """Fix how many key tiles a piece of a shared tile of queries holds in the bfloat16 prompt kernels of the
     head size's library (0: chosen from the step's size, the default).  For tests and tuning."""
     attention_lib(hd).janis_attn_set_prefill_piece(int(piece))
+
+
+def attn_prefill_piece(hd: int, n_tok: int, n_seq: int, nq: int, window: int = 0, tc05: bool = True) -> int:
+    """The piece (in key tiles) that a prompt step of these sizes would cut its shared tiles of queries into."""
+    lib = attention_lib(hd)
+    bm = int(lib.janis_attn_prefill_tile())
+    return int(lib.janis_attn_prefill_piece(n_tok, n_seq, (n_tok + bm - 1) // bm + n_seq, nq, window, 1 if tc05 else 0))
 
 
 def attn_tc05_timeouts(hd: int) -> int:

@@ -456,11 +456,11 @@ def test_attn_prefill_of_a_few_tokens(nq, nkv, hd, lens, prefill_kernel):
 
 @pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 2, 64), (3, 1, 80), (2, 2, 128)])
 @pytest.mark.parametrize("window,cap", [(0, 0.0), (100, 30.0), (300, 50.0)])
-@pytest.mark.parametrize("piece", [0, 1, 3])
+@pytest.mark.parametrize("piece", [0, 1, 3, 4])
 def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, piece, prefill_kernel):
     """Few tiles of queries: the long ones are cut into pieces for two to four CTAs that meet through scratch.
-    Sequences long enough for tiles with many key tiles (2 to 11 of them: with pieces of 1, 3 and the automatic 4
-    every number of pieces occurs, in equal and unequal cuts), a window that leaves some tiles unshared, a far
+    Sequences long enough for tiles with many key tiles (2 to 11 of them: with pieces of 1, 3 and 4 every number
+    of pieces occurs, in equal and unequal cuts; 0 is the library's own choice), a window that leaves some tiles unshared, a far
     key that must win, and the same call without scratch."""
     if prefill_kernel == 1 and (hd % 64 or hd > 256):
         pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
@@ -489,6 +489,20 @@ def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, piece, prefill_kern
     close(outs[0], want, 2 * BF16_TOL, "attn_prefill with shared tiles")
     close(outs[1], want, 2 * BF16_TOL, "attn_prefill without scratch")
     assert ops().attn_tc05_timeouts(hd) == 0
+
+
+def test_attn_prefill_pieces_follow_the_steps_size():
+    """The library's choice of piece for shared tiles of queries, from its model of the step's time: short prompts
+    are cut finely (few CTAs otherwise), one of 2,048 tokens into pieces of about one and a half times an SM's
+    even share, and a step that fills the SMs unshared is not cut at all (a piece as long as its longest tile)."""
+    o = ops()
+    assert 4 <= o.attn_prefill_piece(256, 1024, 1, 8) <= 8
+    assert 18 <= o.attn_prefill_piece(256, 2048, 1, 8) <= 26
+    assert o.attn_prefill_piece(256, 4096, 1, 8) == 64
+    assert o.attn_prefill_piece(256, 2100, 3, 8) == 11                 # three of 700: 11 key tiles at most, none shared
+    assert o.attn_prefill_piece(256, 4096, 1, 8, window=1024) <= 18    # a window bounds the keys of a tile
+    for hd, tc05 in ((128, True), (80, False)):
+        assert 4 <= o.attn_prefill_piece(hd, 1536, 1, 4, tc05=tc05) <= 24
 
 
 @pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 64), (2, 1, 128), (8, 4, 256), (3, 1, 48), (4, 2, 16)])
