@@ -407,9 +407,8 @@ static double prefill_model_us(int n_seq, int len, int nq, int window, int parts
     long long split_parts = 0;
     *longest = 0;
     for (int q0 = 0; q0 < len; q0 += pf::BM) {
-        const int q_last = std::min(q0 + pf::BM, len) - 1;
-        const int j_first = window > 0 ? std::max(0, q0 - window + 1) : 0;
-        const int n = (q_last - j_first / pf::BN * pf::BN) / pf::BN + 1;
+        int k_first, n;
+        pf::key_tiles(q0, len, window, k_first, n);
         *longest = std::max(*longest, n);
         const int np = pf::parts_of(n, parts, piece);
         for (int p = 0; p < np; ++p) items.push_back({(int)((long long)n * (p + 1) / np - (long long)n * p / np), np > 1});
@@ -431,21 +430,35 @@ static double prefill_model_us(int n_seq, int len, int nq, int window, int parts
 }
 
 // The piece that the model likes best for a step (the largest among equals: fewer partial results), remembered per
-// shape of step.  A piece as long as the longest tile's keys means that nothing is shared.
+// shape of step with the lengths rounded up to whole tiles of queries, so that few shapes are ever asked about.  The
+// candidates are multiples of an SM's even share of the key tiles (the best lay between 1.25 and 2 of it wherever it
+// was measured), a few small pieces, and "nothing shared": a piece as long as the longest tile's keys.
 static int prefill_piece_for(int n_tok, int n_seq, int nq, int window, int parts, bool tc05, int* longest) {
     static std::map<std::tuple<int, int, int, int, int, bool>, std::pair<int, int>> known;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
-    const auto key = std::make_tuple(n_tok, n_seq, nq, window, parts, tc05);
+    const int len = ((n_tok + n_seq - 1) / n_seq + pf::BM - 1) / pf::BM * pf::BM;
+    const auto key = std::make_tuple(len, n_seq, nq, window > 0 && window < len ? window : 0, parts, tc05);
     auto it = known.find(key);
     if (it == known.end()) {
-        const int len = (n_tok + n_seq - 1) / n_seq, sms = sm_count();
+        const int sms = sm_count();
         // per key tile: the softmax's share does not depend on the head size, the products' does; the mma.sync
         // kernel took 2.7 times as long per tile at head size 256 and has less to do around its tiles
         const double tile = tc05 ? 1.0 + 0.43 * pf::HD / 256.0 : 3.9 * pf::HD / 256.0, cta = tc05 ? 9.9 : 6.0;
         int most = 0, best = 4;
         double best_us = prefill_model_us(n_seq, len, nq, window, parts, 4, sms, cta, tile, &most);
-        for (int piece = 5; piece <= most; piece += piece < 16 ? 1 : piece < 64 ? 2 : 8) {
+        long long key_tiles = 0;
+        for (int q0 = 0; q0 < len; q0 += pf::BM) {
+            int k_first, n;
+            pf::key_tiles(q0, len, window, k_first, n);
+            key_tiles += n;
+        }
+        const double share = (double)key_tiles * n_seq * nq / sms;
+        std::vector<int> tries = {5, 6, 8};
+        for (double m : {1.0, 1.25, 1.5, 1.75, 2.0, 2.5, 3.0}) tries.push_back((int)(m * share + 0.5));
+        std::sort(tries.begin(), tries.end());
+        for (int piece : tries) {
+            if (piece <= 4 || piece >= most) continue;
             int unused;
             const double us = prefill_model_us(n_seq, len, nq, window, parts, piece, sms, cta, tile, &unused);
             if (us <= best_us) { best_us = us; best = piece; }
@@ -454,6 +467,7 @@ static int prefill_piece_for(int n_tok, int n_seq, int nq, int window, int parts
             int unused;
             if (prefill_model_us(n_seq, len, nq, window, 1, most, sms, cta, tile, &unused) <= best_us) best = most;
         }
+        if (known.size() > 4096) known.clear();
         it = known.emplace(key, std::make_pair(best, most)).first;
     }
     *longest = it->second.second;
@@ -466,6 +480,9 @@ JANIS_EXPORT int janis_attn_prefill_piece(int n_tok, int n_seq, int n_tiles_boun
     int longest = 0;
     return prefill_piece_for(n_tok, n_seq, nq, window, janis_attn_prefill_parts(n_tiles_bound, nq), tc05 != 0, &longest);
 }
+
+static int g_prefill_kernels = 0;   // kernels that the last call of janis_attn_prefill_mma launched
+JANIS_EXPORT int janis_attn_prefill_kernels() { return g_prefill_kernels; }
 
 static int g_prefill_kernel = 1;    // 1: tcgen05 where the head size allows it, else mma.sync; 0: mma.sync always
 
@@ -521,6 +538,9 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
         if (!ext && piece >= longest && piece >= n_tok / pf::BN + 1) parts = 1;
     }
     if (piece <= 0) piece = 4;
+    // No tile of queries has more key tiles than the step has tokens (when its sequences start with it): places for
+    // parts that no tile can have would be CTAs that only come and go, and a CTA of this size takes 2 to 3 us to do so.
+    if (!ext && parts > 1) parts = std::max(1, std::min(parts, (n_tok / pf::BN + 1 + piece - 1) / piece));
     if ((long long)n_tiles_bound * parts > 65535) return fail("attn_prefill_mma: %d tiles of queries exceed the grid", n_tiles_bound);
     int done = -1;
     if (g_prefill_kernel == 1 && !ext)                // the tcgen05 kernel takes sequences that start at position 0
@@ -536,6 +556,7 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
                           kv_row_heads, kv_k_head0, scale, cap, window, parts, piece, partial, cached))
             return 1;
     }
+    g_prefill_kernels = parts == 1 ? 1 : 2;
     if (parts == 1) return 0;
     return launch_kernel("attn_prefill_merge", pf::attn_prefill_merge_kernel, dim3(n_tiles_bound, nq, pf::BM / pf::MERGE_ROWS), dim3(256), 0, stream, 1,
                          (const float*)partial, seq_first_row, seq_len, n_seq, (bf16*)out, nq, window, parts, piece,

@@ -53,7 +53,7 @@ __device__ __forceinline__ bool find_tile(int tile, const int* __restrict__ seq_
 
 // Key tiles [k_first / BN, ...) that a tile of queries walks: n_tiles of them from key k_first (an absolute
 // position; the step's first token stands at position `start`).
-__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_first, int& n_tiles, int start = 0) {
+__host__ __device__ __forceinline__ void key_tiles(int q0, int len, int window, int& k_first, int& n_tiles, int start = 0) {
     const int q_last = start + min(q0 + BM, len) - 1;
     const int j_first = window > 0 ? max(0, start + q0 - window + 1) : 0;
     k_first = (j_first / BN) * BN;

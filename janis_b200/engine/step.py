@@ -246,7 +246,8 @@ class Stepper:
 
         ctx = StepContext(rt=self.rt, ws=self.ws, mode="prefill", n_tok=T, n_seq=n_seq, tokens=take(T),
                           tok_pos=take(T), tok_seq=take(T), seq_slot=take(n_seq), seq_start=take(n_seq),
-                          seq_end=take(n_seq), seq_first_row=take(n_seq), len_bound=max(ends), extends=extends)
+                          seq_end=take(n_seq), seq_first_row=take(n_seq), len_bound=max(ends), extends=extends,
+                          step_lens=tuple(lens))
         rows_dev = take(len(rows))
         h = self.model.forward(ctx, self.cache)
         if out is not None:

@@ -95,6 +95,8 @@ def attention_lib(head_dim: int):
         lib.janis_attn_set_prefill_kernel.restype = None
         lib.janis_attn_set_prefill_piece.argtypes = [I]
         lib.janis_attn_set_prefill_piece.restype = None
+        lib.janis_attn_prefill_kernels.argtypes = []
+        lib.janis_attn_prefill_kernels.restype = I
         lib.janis_attn_prefill_piece.argtypes = [I, I, I, I, I, I]
         lib.janis_attn_prefill_piece.restype = I
         lib.janis_attn_tc05_timeouts.restype = I
@@ -507,7 +509,7 @@ def _cached_args(name, seq_start, seq_slot, kpool, vpool, page_table, ring_len, 
 def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, hd: int, scale: float, cap: float,
                  window: int, kv_src=None, kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True,
                  scratch=None, seq_start=None, seq_slot=None, kpool=None, vpool=None, page_table=None,
-                 ring_len: int = 0):
+                 ring_len: int = 0, host_lens=None):
     """Causal (and windowed when window > 0) attention over packed sequences.
     qkv: [T, nq + 2 nkv, hd], or [T, nq, hd] when keys and values come from `kv_src`, another layer's
     [T, kv_row_heads, hd] rows whose key heads start at head kv_k_head0 (values nkv heads later).
@@ -516,13 +518,15 @@ def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, h
     positions, seq_first_row is the row of a sequence's first token of this step, `seq_len` the lengths after the
     step, and the keys and values of earlier positions are read from the cache line (kpool, vpool, page_table,
     ring_len), which must still hold what those steps left (this step's own keys are stored afterwards).
+    `host_lens`: the tokens each sequence brings to this step, if the host knows them (a step replayed from a graph
+    with other lengths does not): the grid then has no places to spare.
     bfloat16 with `seq_len` (int32 [n_seq]) runs on the tensor cores; float32 runs the CUDA-core kernel, which is
     exact 32-bit."""
     T = qkv.shape[0]
     if qkv.dtype == torch.bfloat16 and seq_len is not None and tensor_cores:
         return _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src,
                                  kv_row_heads, kv_k_head0, scratch,
-                                 (seq_start, seq_slot, kpool, vpool, page_table, ring_len))
+                                 (seq_start, seq_slot, kpool, vpool, page_table, ring_len), host_lens)
     if kv_src is None:
         _t(qkv, "qkv", _FLOATS, (T, nq + 2 * nkv, hd))
         kv_src, kv_row_heads, kv_k_head0 = qkv, nq + 2 * nkv, nq
@@ -547,7 +551,7 @@ def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq: int, nkv: int, h
 
 
 def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap, window, kv_src, kv_row_heads,
-                      kv_k_head0, scratch=None, cached=(None,) * 5 + (0,)):
+                      kv_k_head0, scratch=None, cached=(None,) * 5 + (0,), host_lens=None):
     T = qkv.shape[0]
     if kv_src is None:
         _t(qkv, "qkv", torch.bfloat16, (T, nq + 2 * nkv, hd))
@@ -566,7 +570,12 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
     cached = _cached_args("attn_prefill", *cached, torch.bfloat16, n_seq, nkv, hd)
     lib = attention_lib(hd)
     bm = lib.janis_attn_prefill_tile()      # queries per CTA
-    tiles = (T + bm - 1) // bm + n_seq      # >= sum of ceil(len / bm)
+    if host_lens is not None:               # the tokens each sequence brings, when the host knows them: no places to spare
+        if len(host_lens) != n_seq or sum(host_lens) > T:
+            raise KernelError(f"attn_prefill: host_lens {list(host_lens)} do not fit {n_seq} sequences of {T} tokens")
+        tiles = sum((int(n) + bm - 1) // bm for n in host_lens)
+    else:
+        tiles = (T + bm - 1) // bm + n_seq  # >= sum of ceil(len / bm)
     need = int(lib.janis_attn_prefill_scratch(tiles, nq))
     if scratch is not None and (need == 0 or scratch.numel() < need):
         scratch = None
@@ -574,8 +583,9 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
                                            seq_len.data_ptr(), n_seq, tiles, out.data_ptr(), nq, nkv,
                                            qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),
                                            int(window), _t(scratch, "scratch", torch.float32) if scratch is not None else None,
-                                           scratch.numel() if scratch is not None else 0, *cached, _stream()),
-           2 if scratch is not None else 1)
+                                           scratch.numel() if scratch is not None else 0, *cached, _stream()))
+    global _launches
+    _launches += int(lib.janis_attn_prefill_kernels()) - 1     # the merge, when tiles were shared
     return out
 
 

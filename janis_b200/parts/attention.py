@@ -153,12 +153,13 @@ class SoftmaxAttention(Mixer):
                 if line.has_readers:
                     ctx.shared[("kv", line.index)] = (qkv, heads, nq)
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
-                                 self.softcap, self.window, seq_len=ctx.seq_end, scratch=scratch, **before)
+                                 self.softcap, self.window, seq_len=ctx.seq_end, scratch=scratch, host_lens=ctx.step_lens,
+                                 **before)
             else:
                 src, src_heads, k0 = ctx.shared[("kv", line.index)]
                 ops.attn_prefill(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_first_row, att, nq, nkv, hd, self.scale,
                                  self.softcap, self.window, kv_src=src, kv_row_heads=src_heads, kv_k_head0=k0,
-                                 seq_len=ctx.seq_end, scratch=scratch, **before)
+                                 seq_len=ctx.seq_end, scratch=scratch, host_lens=ctx.step_lens, **before)
             if extends and own:
                 store = lambda: ops.kv_store(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.seq_end, nq, nkv, hd,
                                              kv.k, kv.v, kv.table, kv.ring_len)

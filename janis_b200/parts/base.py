@@ -138,6 +138,8 @@ class StepContext:
     len_mean: int = 0               # host-side estimate of mean(seq_end) over the step's rows, rounded up to an eighth of
                                     # len_bound (0: unknown, take len_bound); it tunes launch shapes and changes no result
     len_even: bool = True           # whether the sequences are about equally long (the shortest at least 3/4 of the longest)
+    step_lens: tuple | None = None  # host-side: the tokens each sequence brings to a "prefill" step, when the step's tables
+                                    # hold just these (None in a step recorded for other lengths too); launch shapes only
     extends: bool = False           # a "prefill" step some of whose sequences have tokens in the cache already
                                     # (seq_start > 0): a mixer reads those from its cache line and stores this
                                     # step's own only after it has attended

@@ -168,7 +168,7 @@ def attn_prefill_scratch_floats(n_tok, n_seq, nq, hd, dtype=torch.bfloat16):
 
 def attn_prefill(qkv, tok_pos, tok_seq, seq_first_row, out, nq, nkv, hd, scale, cap, window, kv_src=None,
                  kv_row_heads=None, kv_k_head0=None, seq_len=None, tensor_cores=True, scratch=None, seq_start=None,
-                 seq_slot=None, kpool=None, vpool=None, page_table=None, ring_len=0):
+                 seq_slot=None, kpool=None, vpool=None, page_table=None, ring_len=0, host_lens=None):
     T = qkv.shape[0]
     if kv_src is None:
         kv_src, kv_k_head0 = qkv, nq
