@@ -27,6 +27,7 @@
 // memory and returns.  No TMA load here uses cluster multicast.
 #include <cuda.h>
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -589,6 +590,506 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (failed && threadIdx.x == 0) atomicAdd(&g_timeouts, 1);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same work by CTAs that stay: one CTA an SM takes item after item (a tile of queries of one head, or a part of
+// one) from a counter, so that what a CTA costs besides its tiles is paid once, not per tile of queries: the launch
+// of a CTA of this size and its way out (2 to 3 us), Q and the first keys (asked for while the item before is still
+// at its last tiles), the products' start.  What stays per item is the way out of its result.  An item's place is
+// told to the three roles through two slots in shared memory; the rings of keys and values, the two score buffers,
+// P and the accumulator carry on from item to item (their barriers count tiles across items).  The result leaves
+// through the ring stage of the item's last tile (bfloat16: one stage holds a tile of queries), which is the stage
+// of the next item's second tile: the loader brings the next item's first tile meanwhile and waits for the way out
+// before the second; a partial result (float) takes both stages, and the loader waits before the first.
+// ---------------------------------------------------------------------------------------------------------------
+struct Item {
+    int seq, q0, len, first, k_first, n_tiles, head, gtile, part, np;   // n_tiles < 0: there is no further item
+};
+
+enum { ITEM_FULL = N_BARS, ITEM_EMPTY = N_BARS + 2, Q_EMPTY = N_BARS + 4, EPI_DONE = N_BARS + 5, N_BARS_ITEMS = N_BARS + 6 };
+
+// A launch's counters: the next item, and the CTAs that have left (the last one puts both back to 0).  Launches
+// take the slots in turn, so that launches in flight together (other streams) do not share one; SCHED_SLOTS of
+// them at once is the limit of that.
+constexpr int SCHED_SLOTS = 64;
+__device__ int g_sched[SCHED_SLOTS][2];
+
+// find_tile by a whole warp: 32 sequences a round
+__device__ __forceinline__ bool find_tile_warp(int tile, const int* __restrict__ seq_len, int n_seq, int lane, int& seq,
+                                               int& q0, int& len) {
+    int before = 0;
+    for (int s0 = 0; s0 < n_seq; s0 += 32) {
+        const int n = s0 + lane < n_seq ? seq_len[s0 + lane] : 0;
+        const int nt = (n + BM - 1) / BM;
+        int incl = nt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += v;
+        }
+        const int lo = before + incl - nt;
+        const unsigned hit = __ballot_sync(0xffffffffu, tile >= lo && tile < lo + nt);
+        if (hit) {
+            const int src = __ffs(hit) - 1;
+            seq = s0 + src;
+            q0 = (tile - __shfl_sync(0xffffffffu, lo, src)) * BM;
+            len = __shfl_sync(0xffffffffu, n, src);
+            return true;
+        }
+        before += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    return false;
+}
+
+template <bool CAPPED>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                               const int* __restrict__ seq_first_row, const int* __restrict__ seq_len, int n_seq,
+                               bf16* __restrict__ out, int nq, int nkv, int kv_k_head0, float scale, float cap, int window,
+                               int parts, int piece, float* __restrict__ partial, int n_places, int sched_slot) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[N_BARS_ITEMS];
+    int* sched = g_sched[sched_slot];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+    __shared__ float row_max[4][SPLIT][BM];
+    __shared__ float row_sum[SPLIT][BM];
+    __shared__ Item items[2];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sQ = (raw + 1023) & ~1023u;
+    const uint32_t sKV = sQ + Q_BYTES;
+    const uint32_t sP = sKV + STAGES * 2 * KV_TILE;
+    unsigned char* p_ptr = smem_raw + (sP - raw);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+    auto bar = [&](int i) { return bar0 + 8 * i; };
+    const volatile int* fail_flag = &failed;
+
+    if (warp == LOADER_WARP && lane == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        mbar_init(bar(Q_EMPTY), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(K_FULL + i), 1);
+            mbar_init(bar(K_EMPTY + i), 1);
+            mbar_init(bar(V_FULL + i), 1);
+            mbar_init(bar(V_EMPTY + i), 1);
+            mbar_init(bar(S_FULL + i), 1);
+            mbar_init(bar(S_EMPTY + i), SOFTMAX_WARPS);
+            mbar_init(bar(ROW_X + i), SOFTMAX_WARPS);
+            mbar_init(bar(ITEM_FULL + i), 1);
+            mbar_init(bar(ITEM_EMPTY + i), SOFTMAX_WARPS + 1);
+        }
+        mbar_init(bar(P_FULL), SOFTMAX_WARPS);
+        mbar_init(bar(O_DONE), 1);
+        mbar_init(bar(EPI_DONE), SOFTMAX_WARPS);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == ISSUER_WARP) {
+        const uint32_t slot = (uint32_t)__cvta_generic_to_shared(&tmem_slot);
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    grid_dependents_launch();
+
+    // The next item from the counter, by the whole loader warp (the step's tables were written before the kernel
+    // ahead of this one started, and the counter is this kernel's own: the items are found before the wait).
+    const int total = n_places * nq;
+    auto fetch = [&]() -> Item {
+        Item it;
+        it.n_tiles = -1;
+        it.seq = it.q0 = it.len = it.first = it.k_first = it.head = it.gtile = it.part = it.np = 0;
+        for (;;) {
+            int idx = 0;
+            if (lane == 0) idx = atomicAdd(&sched[0], 1);
+            idx = __shfl_sync(0xffffffffu, idx, 0);
+            if (idx >= total) return it;
+            const int place = n_places - 1 - idx / nq;     // heads vary fastest; the last tile of queries comes first
+            const int gtile = place / parts, part = place % parts;
+            int seq = 0, q0 = 0, len = 0;
+            if (!find_tile_warp(gtile, seq_len, n_seq, lane, seq, q0, len)) continue;
+            int k_first, n_tiles;
+            pf::key_tiles(q0, len, window, k_first, n_tiles);
+            const int np = pf::parts_of(n_tiles, parts, piece);
+            if (part >= np) continue;
+            if (np > 1) {
+                const int t0 = (int)((long long)n_tiles * part / np), t1 = (int)((long long)n_tiles * (part + 1) / np);
+                k_first += t0 * BN;
+                n_tiles = t1 - t0;
+            }
+            it.seq = seq; it.q0 = q0; it.len = len; it.first = seq_first_row[seq]; it.k_first = k_first;
+            it.n_tiles = n_tiles; it.head = idx % nq; it.gtile = gtile; it.part = part; it.np = np;
+            return it;
+        }
+    };
+    // item number k goes into slot k & 1 once the roles have taken item k - 2 out of it
+    auto publish = [&](int k, const Item& it) -> bool {
+        if (k >= 2 && !mbar_wait(bar(ITEM_EMPTY + (k & 1)), ((k >> 1) - 1) & 1, fail_flag)) return false;
+        items[k & 1] = it;
+        mbar_arrive(bar(ITEM_FULL + (k & 1)));
+        return true;
+    };
+    Item cur;
+    cur.n_tiles = -1;
+    if (warp == LOADER_WARP) {
+        cur = fetch();
+        if (lane == 0) publish(0, cur);
+    }
+    grid_dependency_wait();
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t tO = tmem, tS = tmem + HD;
+    const int group = nq / nkv;
+
+    if (warp == LOADER_WARP) {
+        // ---- loader
+        bool ok = true;
+        int g = 0, prev_np = 1;                      // tiles before this item; parts of the item before
+        for (int k = 0; cur.n_tiles >= 0; ++k) {
+            const int n = cur.n_tiles, kvh = cur.head / group;
+            if (lane == 0) {
+                // (Q is free: the item before was taken only after its last scores, below)
+                mbar_expect_tx(bar(Q_FULL), Q_BYTES);
+                for (int sl = 0; sl < SLABS; ++sl)
+                    tma_load_2d(sQ + sl * Q_SLAB, &map_q, cur.head * HD + sl * 64, cur.first + cur.q0, bar(Q_FULL));
+                auto load_k = [&](int i) {
+                    if (!ok || i >= n) return;
+                    const int gi = g + i, s = gi & 1;
+                    if (gi >= 2 && !mbar_wait(bar(K_EMPTY + s), ((gi >> 1) - 1) & 1, fail_flag)) { ok = false; return; }
+                    const uint32_t sK = sKV + s * 2 * KV_TILE;
+                    mbar_expect_tx(bar(K_FULL + s), KV_TILE);
+                    for (int sl = 0; sl < SLABS; ++sl)
+                        tma_load_2d(sK + sl * KV_SLAB, &map_kv, (kv_k_head0 + kvh) * HD + sl * 64,
+                                    cur.first + cur.k_first + i * BN, bar(K_FULL + s));
+                };
+                auto load_v = [&](int i) {
+                    if (!ok || i >= n) return;
+                    const int gi = g + i, s = gi & 1;
+                    if (gi >= 2 && !mbar_wait(bar(V_EMPTY + s), ((gi >> 1) - 1) & 1, fail_flag)) { ok = false; return; }
+                    const uint32_t sV = sKV + s * 2 * KV_TILE + KV_TILE;
+                    mbar_expect_tx(bar(V_FULL + s), KV_TILE);
+                    for (int sl = 0; sl < SLABS; ++sl)
+                        tma_load_2d(sV + sl * KV_SLAB, &map_kv, (kv_k_head0 + nkv + kvh) * HD + sl * 64,
+                                    cur.first + cur.k_first + i * BN, bar(V_FULL + s));
+                };
+                // the item before leaves through the stage of this item's second tile (both stages, if it leaves a
+                // partial result): every item's way out is waited for once, in order
+                auto way_out = [&]() {
+                    if (ok && k > 0) ok = mbar_wait(bar(EPI_DONE), (k - 1) & 1, fail_flag);
+                };
+                if (prev_np > 1) way_out();
+                load_k(0); load_v(0);
+                if (prev_np <= 1) way_out();
+                load_k(1); load_v(1);
+                load_k(2); load_k(3);
+                for (int i = 0; ok && i + 2 < n; ++i) {
+                    load_v(i + 2);
+                    load_k(i + 4);
+                }
+                // The next item is taken late, when this item's last scores are done (two tiles and the way out are
+                // left): a CTA that took its next item early would hold it while other CTAs have nothing to do.
+                if (ok) ok = mbar_wait(bar(Q_EMPTY), k & 1, fail_flag);
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            const Item nxt = fetch();
+            if (lane == 0) ok = publish(k + 1, nxt);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            g += n;
+            prev_np = cur.np;
+            cur = nxt;
+        }
+        if (!ok && lane == 0) atomicExch(&failed, 1);
+    } else if (warp == ISSUER_WARP && lane == 0) {
+        // ---- the thread that issues the products
+        const uint32_t idesc_s = instr_desc(BM, BN, false), idesc_o = instr_desc(BM, HD, true);
+        bool ok = true;
+        int g = 0;
+        for (int k = 0; ok; ++k) {
+            ok = mbar_wait(bar(ITEM_FULL + (k & 1)), (k >> 1) & 1, fail_flag);
+            if (!ok) break;
+            const int n = items[k & 1].n_tiles;
+            mbar_arrive(bar(ITEM_EMPTY + (k & 1)));
+            if (n < 0) break;
+            auto scores = [&](int i) -> bool {        // S[(g + i) & 1] = Q K(i)^T
+                const int gi = g + i, b = gi & 1;
+                if (i == 0 && !mbar_wait(bar(Q_FULL), k & 1, fail_flag)) return false;
+                if (!mbar_wait(bar(K_FULL + b), (gi >> 1) & 1, fail_flag)) return false;
+                if (gi >= 2 && !mbar_wait(bar(S_EMPTY + b), ((gi >> 1) - 1) & 1, fail_flag)) return false;
+                fence_after();
+                const uint32_t sK = sKV + b * 2 * KV_TILE;
+                for (int sl = 0; sl < SLABS; ++sl)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma(tS + 64 * b, smem_desc(sQ + sl * Q_SLAB + kk * 32), smem_desc(sK + sl * KV_SLAB + kk * 32),
+                             idesc_s, (sl > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(bar(S_FULL + b));
+                umma_commit(bar(K_EMPTY + b));
+                if (i == n - 1) umma_commit(bar(Q_EMPTY));     // the item's last scores: Q may be overwritten
+                return true;
+            };
+            ok = scores(0);
+            if (ok && n > 1) ok = scores(1);
+            for (int it = 0; ok && it < n; ++it) {
+                if (it + 2 < n) {
+                    ok = scores(it + 2);
+                    if (!ok) break;
+                }
+                const int gi = g + it, b = gi & 1;
+                ok = mbar_wait(bar(P_FULL), gi & 1, fail_flag) && mbar_wait(bar(V_FULL + b), (gi >> 1) & 1, fail_flag);
+                if (!ok) break;
+                fence_after();
+                const uint32_t sV = sKV + b * 2 * KV_TILE + KV_TILE;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma(tO, smem_desc(sP + kk * 32), smem_desc(sV + kk * 2048, KV_SLAB), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(bar(V_EMPTY + b));
+                umma_commit(bar(O_DONE));
+            }
+            g += n;
+        }
+        if (!ok) atomicExch(&failed, 1);
+    } else if (warp < SOFTMAX_WARPS) {
+        // ---- softmax (see the kernel above; the barriers of tiles count on from item to item)
+        const int quarter = warp & 3, h = warp >> 2;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const float LOG2E = 1.4426950408889634f;
+        const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
+        const float k_tanh = CAPPED ? scale / cap * (JANIS_PT_TANH_APPROX ? 1.0f : 2.0f * LOG2E) : 0.f;
+        bool ok = true;
+        int g = 0, gx = 0;                           // tiles, and exchanges through ROW_X, before this item
+        for (int k = 0; ok; ++k) {
+            ok = mbar_wait(bar(ITEM_FULL + (k & 1)), (k >> 1) & 1, fail_flag);
+            if (!ok) break;
+            const Item me = items[k & 1];
+            warp_arrive(bar(ITEM_EMPTY + (k & 1)), lane);
+            if (me.n_tiles < 0) break;
+            const int n_tiles = me.n_tiles, q0 = me.q0, len = me.len, k_first = me.k_first;
+            const int row_pos = q0 + r;
+            const bool shared_tile = me.np > 1;
+            float m_ref = -INFINITY, l_run = 0.f;
+            auto stage_one = [&](int it, uint32_t (&sv)[CPT], float& base) -> bool {
+                const int gi = g + it, x = gx + it, b = gi & 1, k0 = k_first + it * BN;
+                if (!mbar_wait(bar(S_FULL + b), (gi >> 1) & 1, fail_flag)) return false;
+                fence_after();
+                tmem_ld16(tS + 64 * b + CPT * h + lane_base, sv);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                fence_before();
+                warp_arrive(bar(S_EMPTY + b), lane);
+                base = m_ref == -INFINITY ? 0.f : m_ref;
+                const float c0 = CAPPED ? cap2 - base : -base, c1 = -2.0f * cap2;
+                const bool inner = k0 + BN - 1 <= q0 && k0 + BN <= len && (window <= 0 || k0 > q0 + BM - 1 - window);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    const float s = __uint_as_float(sv[j]);
+                    float v;
+                    if (CAPPED) {
+#if JANIS_PT_TANH_APPROX
+                        v = fmaf(tanh_approx(s * k_tanh), cap2, -base);
+#else
+                        float rc;
+                        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(rc) : "f"(pf::ex2(s * k_tanh) + 1.0f));
+                        v = fmaf(rc, c1, c0);
+#endif
+                    } else {
+                        v = fmaf(s, scale2, c0);
+                    }
+                    if (!inner) {
+                        const int key = k0 + CPT * h + j;
+                        const bool seen = key <= row_pos && key < len && (window <= 0 || key > row_pos - window);
+                        v = seen ? v : -INFINITY;
+                    }
+                    sv[j] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+                row_max[x & 3][h][r] = mx + base;
+                warp_arrive(bar(ROW_X + (x & 1)), lane);
+                return true;
+            };
+            auto stage_two = [&](int it, uint32_t (&sv)[CPT], float base) -> bool {
+                const int gi = g + it, x = gx + it, b = gi & 1;
+                if (!mbar_wait(bar(ROW_X + (x & 1)), (x >> 1) & 1, fail_flag)) return false;
+                float mx = row_max[x & 3][0][r];
+#pragma unroll
+                for (int hh = 1; hh < SPLIT; ++hh) mx = fmaxf(mx, row_max[x & 3][hh][r]);
+                float factor = 1.0f;
+                const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx != -INFINITY);
+                if (grow) {
+                    factor = pf::ex2(m_ref - mx);
+                    m_ref = mx;
+                }
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                l_run *= factor;
+                if (base != m_use) {
+                    const float shift = base - m_use;
+#pragma unroll
+                    for (int j = 0; j < CPT; ++j) sv[j] = __float_as_uint(__uint_as_float(sv[j]) + shift);
+                }
+                uint32_t pk[CPT / 2];
+#pragma unroll
+                for (int j = 0; j < CPT; j += 2) {
+                    const float p0 = pf::ex2(__uint_as_float(sv[j]));
+                    const float p1 = JANIS_PT_POLY_EX2 ? ex2_poly(__uint_as_float(sv[j + 1])) : pf::ex2(__uint_as_float(sv[j + 1]));
+                    l_run += p0 + p1;
+                    pk[j / 2] = pf::pack_bf16(p0, p1);
+                }
+                // P's buffer and the accumulator are free once the products of the tile before have finished (an
+                // item's first tile follows the wait for the last products of the item before, below)
+                if (it > 0) {
+                    if (!mbar_wait(bar(O_DONE), (gi - 1) & 1, fail_flag)) return false;
+                    fence_after();
+                    if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+                        for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
+                            uint32_t o[16];
+                            tmem_ld16(tO + c + lane_base, o);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+                            tmem_st16(tO + c + lane_base, o);
+                        }
+                        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                    }
+                }
+                {   // rows of the last box of values beyond the sequence's end are cleared (see the kernel above)
+                    const int k0 = k_first + it * BN;
+                    if (k0 + BN > len) {
+                        if (!mbar_wait(bar(V_FULL + b), (gi >> 1) & 1, fail_flag)) return false;
+                        const int n_valid = len - k0;
+                        unsigned char* v_ptr = smem_raw + (sKV - raw) + b * 2 * KV_TILE + KV_TILE;
+                        const int pieces = (BN - n_valid) * 8;
+                        for (int idx = threadIdx.x; idx < pieces * SLABS; idx += SOFTMAX_WARPS * 32) {
+                            const int sl = idx / pieces, pc = idx % pieces;
+                            *reinterpret_cast<uint4*>(v_ptr + sl * KV_SLAB + n_valid * 128 + pc * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < CPT / 8; ++c) {
+                    const int pc = (CPT / 8) * h + c;
+                    *reinterpret_cast<uint4*>(p_ptr + r * 128 + ((pc ^ (r & 7)) << 4)) =
+                        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                fence_before();
+                warp_arrive(bar(P_FULL), lane);
+                return true;
+            };
+            uint32_t sv[CPT], sv_next[CPT];
+            float base = 0.f, base_next = 0.f;
+            ok = stage_one(0, sv, base);
+            for (int it = 0; ok && it < n_tiles; ++it) {
+                if (it + 1 < n_tiles) ok = stage_one(it + 1, sv_next, base_next);
+                ok = ok && stage_two(it, sv, base);
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) sv[j] = sv_next[j];
+                base = base_next;
+            }
+            if (ok) ok = mbar_wait(bar(O_DONE), (g + n_tiles - 1) & 1, fail_flag);
+            if (ok) {
+                const int x = gx + n_tiles;
+                row_sum[h][r] = l_run;
+                warp_arrive(bar(ROW_X + (x & 1)), lane);
+                ok = mbar_wait(bar(ROW_X + (x & 1)), (x >> 1) & 1, fail_flag);
+            }
+            // the way out: through the stage of the item's last tile (a partial result: through both stages)
+            unsigned char* stage = smem_raw + (sKV - raw) + (shared_tile ? 0 : ((g + n_tiles - 1) & 1) * 2 * KV_TILE);
+            if (ok) {
+                fence_after();
+                float l_row = 0.f;
+#pragma unroll
+                for (int hh = 0; hh < SPLIT; ++hh) l_row += row_sum[hh][r];
+                if (shared_tile) {
+                    if (h == 0) {
+                        float* prow = partial + ((((size_t)me.gtile * nq + me.head) * parts + me.part) * BM + r) * pf::PART_ROW;
+                        prow[0] = m_ref;
+                        prow[1] = l_row;
+                    }
+#pragma unroll 1
+                    for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
+                        uint32_t o[16];
+                        tmem_ld16(tO + c + lane_base, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<uint4*>(stage + (size_t)r * (HD * 4) + ((((c + j) >> 2) ^ (r & 7)) << 4)) =
+                                make_uint4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                    }
+                } else {
+                    const float inv = 1.0f / l_row;
+#pragma unroll 1
+                    for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
+                        uint32_t o[16];
+                        tmem_ld16(tO + c + lane_base, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; j += 8) {
+                            uint4 w;
+                            w.x = pf::pack_bf16(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+                            w.y = pf::pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+                            w.z = pf::pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+                            w.w = pf::pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+                            *reinterpret_cast<uint4*>(stage + (size_t)r * (HD * 2) + ((((c + j) >> 3) ^ (r & 7)) << 4)) = w;
+                        }
+                    }
+                }
+                fence_before();                       // the accumulator has been read: the next item's products may overwrite it
+                const int x = gx + n_tiles + 1;
+                warp_arrive(bar(ROW_X + (x & 1)), lane);
+                ok = mbar_wait(bar(ROW_X + (x & 1)), (x >> 1) & 1, fail_flag);
+            }
+            if (ok) {
+                const int rows = min(BM, len - q0);
+                if (shared_tile) {
+                    constexpr int PIECES = HD / 4;
+                    float* pbase = partial + (((size_t)me.gtile * nq + me.head) * parts + me.part) * BM * pf::PART_ROW;
+                    for (int idx = threadIdx.x; idx < rows * PIECES; idx += SOFTMAX_WARPS * 32) {
+                        const int rr = idx / PIECES, pc = idx % PIECES;
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage + (size_t)rr * (HD * 4) + ((pc ^ (rr & 7)) << 4));
+                        float* dst = pbase + (size_t)rr * pf::PART_ROW + 2 + pc * 4;
+                        *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+                        *reinterpret_cast<uint2*>(dst + 2) = make_uint2(v.z, v.w);
+                    }
+                } else {
+                    constexpr int PIECES = HD / 8;
+                    bf16* obase = out + (size_t)(me.first + q0) * nq * HD + (size_t)me.head * HD;
+                    for (int idx = threadIdx.x; idx < rows * PIECES; idx += SOFTMAX_WARPS * 32) {
+                        const int rr = idx / PIECES, pc = idx % PIECES;
+                        *reinterpret_cast<uint4*>(obase + (size_t)rr * nq * HD + pc * 8) =
+                            *reinterpret_cast<const uint4*>(stage + (size_t)rr * (HD * 2) + ((pc ^ (rr & 7)) << 4));
+                    }
+                }
+                // the stage has been read (generic proxy) before the loader's bulk copies (async proxy) overwrite it
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                warp_arrive(bar(EPI_DONE), lane);
+            }
+            g += n_tiles;
+            gx += n_tiles + 2;
+        }
+        if (!ok) atomicExch(&failed, 1);
+    }
+    __syncwarp();
+    fence_before();
+    __syncthreads();
+    if (warp == ISSUER_WARP)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (threadIdx.x == 0) {
+        if (failed) atomicAdd(&g_timeouts, 1);
+        // the last CTA to leave puts the counters back for the next launch
+        __threadfence();
+        if (atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) {
+            sched[0] = 0;
+            sched[1] = 0;
+            __threadfence();
+        }
+    }
+}
+
 // ---- host side: tensor maps over the packed rows
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -622,6 +1123,23 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int 
 
 }  // namespace pt
 
+// Which form of the kernel a step runs: 0 a CTA per tile of queries and head, 2 CTAs that stay and take item after
+// item, 1 (default) by the step's size: the CTAs that stay save the coming and going of a CTA (about 3 us an item) and
+// lose a little where a CTA gets one item or two (they ask for their next item late, so that none holds work that
+// another could do).  Measured per layer at 8 heads of 256: 4 prompts of 4,096 tokens 374 -> 351 us, one of 8,192
+// 346 -> 340, 40 of 100 tokens 31.8 -> 24.1; one of 2,048 43.0 -> 45.5, one of 1,024 21.5 -> 23.2.
+static int g_tc05_items = 1;
+
+static int tc05_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
 int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const int* seq_first_row, const int* seq_len,
                         int n_seq, int n_tiles_bound, void* out, int nq, int nkv, int q_row_heads, int kv_row_heads,
                         int kv_k_head0, float scale, float cap, int window, int parts, int piece, float* partial,
@@ -641,6 +1159,30 @@ int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const 
         if (e != cudaSuccess) return fail("attn_prefill_tc05: shared memory of %d bytes refused: %s", pt::SMEM_BYTES,
                                           cudaGetErrorString(e));
         configured = true;
+    }
+    const bool many = (long long)n_tiles_bound * parts * nq >= 2LL * tc05_sm_count();
+    if (g_tc05_items == 2 || (g_tc05_items == 1 && many)) {
+        static bool items_configured = false;
+        if (!items_configured) {
+            cudaError_t e = cudaFuncSetAttribute(pt::attn_prefill_tc05_items_kernel<true>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, pt::SMEM_BYTES);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(pt::attn_prefill_tc05_items_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, pt::SMEM_BYTES);
+            if (e != cudaSuccess) return fail("attn_prefill_tc05: shared memory of %d bytes refused: %s", pt::SMEM_BYTES,
+                                              cudaGetErrorString(e));
+            items_configured = true;
+        }
+        static int next_slot = 0;
+        const int slot = next_slot;
+        next_slot = (next_slot + 1) % pt::SCHED_SLOTS;
+        const int n_places = n_tiles_bound * parts;
+        const long long total = (long long)n_places * nq;
+        const int ctas = (int)std::min<long long>(total, tc05_sm_count());
+        auto items = cap > 0.f ? pt::attn_prefill_tc05_items_kernel<true> : pt::attn_prefill_tc05_items_kernel<false>;
+        return launch_kernel("attn_prefill_tc05", items, dim3(ctas), dim3(pt::THREADS), pt::SMEM_BYTES, stream, 1, mq, mkv,
+                             seq_first_row, seq_len, n_seq, (bf16*)out, nq, nkv, kv_k_head0, scale, cap, window, parts,
+                             piece, partial, n_places, slot);
     }
     auto kernel = cap > 0.f ? pt::attn_prefill_tc05_kernel<true> : pt::attn_prefill_tc05_kernel<false>;
     return launch_kernel("attn_prefill_tc05", kernel, dim3(nq, n_tiles_bound * parts), dim3(pt::THREADS), pt::SMEM_BYTES,
@@ -662,3 +1204,7 @@ JANIS_EXPORT int janis_attn_tc05_timeouts() {
     if (cudaMemcpyFromSymbol(&n, janis::pt::g_timeouts, sizeof(int)) != cudaSuccess) return -1;
     return n;
 }
+
+// Which form of the tcgen05 prompt kernel runs: 0 = a CTA per tile of queries and head, 2 = CTAs that stay and take
+// item after item, 1 = chosen by the step's size (the default).  All give the same results.
+JANIS_EXPORT void janis_attn_set_prefill_items(int how) { janis::g_tc05_items = how < 0 || how > 2 ? 1 : how; }

@@ -95,6 +95,8 @@ def attention_lib(head_dim: int):
         lib.janis_attn_set_prefill_kernel.restype = None
         lib.janis_attn_set_prefill_piece.argtypes = [I]
         lib.janis_attn_set_prefill_piece.restype = None
+        lib.janis_attn_set_prefill_items.argtypes = [I]
+        lib.janis_attn_set_prefill_items.restype = None
         lib.janis_attn_prefill_kernels.argtypes = []
         lib.janis_attn_prefill_kernels.restype = I
         lib.janis_attn_prefill_piece.argtypes = [I, I, I, I, I, I]
@@ -591,8 +593,12 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
 
 def attn_set_prefill_kernel(hd: int, which: int = 1) -> None:
     """Choose the bfloat16 prompt kernel of the head size's library: 1 = tcgen05 with the accumulators in
-    tensor memory where the head size allows it (a multiple of 64 up to 256; the default), 0 = mma.sync."""
-    attention_lib(hd).janis_attn_set_prefill_kernel(int(which))
+    tensor memory where the head size allows it (a multiple of 64 up to 256; the default), in the form that suits
+    the step's size; 2 = always a CTA per tile of queries and head; 3 = always CTAs that stay and take one tile of
+    queries after another; 0 = mma.sync."""
+    lib = attention_lib(hd)
+    lib.janis_attn_set_prefill_kernel(1 if which else 0)
+    lib.janis_attn_set_prefill_items({2: 0, 3: 2}.get(which, 1))
 
 
 def attn_set_prefill_piece(hd: int, piece: int = 0) -> None:

@@ -394,9 +394,10 @@ def test_attn_prefill(dtype, nq, nkv, hd, window, cap):
     close(out, want, tol_of(dtype), "attn_prefill")
 
 
-@pytest.fixture(params=[1, 0], ids=["tcgen05", "mma_sync"])
+@pytest.fixture(params=[3, 2, 0], ids=["tcgen05_ctas_that_stay", "tcgen05_cta_per_tile", "mma_sync"])
 def prefill_kernel(request):
-    """Both bfloat16 prompt kernels (head sizes the tcgen05 kernel does not take run mma.sync either way)."""
+    """The bfloat16 prompt kernels: tcgen05 in both its forms (CTAs that stay and take item after item; a CTA per
+    tile of queries and head) and mma.sync (head sizes the tcgen05 kernel does not take run mma.sync either way)."""
     yield request.param
     for hd in list(ops()._attn):                # the libraries that are loaded: back to their default
         ops().attn_set_prefill_kernel(hd, 1)
@@ -408,7 +409,7 @@ def prefill_kernel(request):
 def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap, prefill_kernel):
     """The bfloat16 tensor-core kernels: tiles of 128 queries and 64 keys, so lengths around 64 and 128,
     a window that cuts inside and across tiles, and a far key that must win."""
-    if prefill_kernel == 1 and (hd % 64 or hd > 256):
+    if prefill_kernel and (hd % 64 or hd > 256):
         pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
     ops().attn_set_prefill_kernel(hd, prefill_kernel)
     lens = [1, 63, 64, 65, 200, 129]
@@ -436,7 +437,7 @@ def test_attn_prefill_tensor_cores(nq, nkv, hd, window, cap, prefill_kernel):
 @pytest.mark.parametrize("lens", [[1], [5], [3, 2], [64], [127, 1]])
 def test_attn_prefill_of_a_few_tokens(nq, nkv, hd, lens, prefill_kernel):
     """Steps much shorter than a tile of queries or keys (the TMA boxes reach past the end of the rows)."""
-    if prefill_kernel == 1 and (hd % 64 or hd > 256):
+    if prefill_kernel and (hd % 64 or hd > 256):
         pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
     ops().attn_set_prefill_kernel(hd, prefill_kernel)
     T = sum(lens)
@@ -462,7 +463,7 @@ def test_attn_prefill_shared_tiles(nq, nkv, hd, window, cap, piece, prefill_kern
     Sequences long enough for tiles with many key tiles (2 to 11 of them: with pieces of 1, 3 and 4 every number
     of pieces occurs, in equal and unequal cuts; 0 is the library's own choice), a window that leaves some tiles unshared, a far
     key that must win, the same call without scratch, and with the lengths given to the host as well."""
-    if prefill_kernel == 1 and (hd % 64 or hd > 256):
+    if prefill_kernel and (hd % 64 or hd > 256):
         pytest.skip("the tcgen05 kernel takes head sizes that are a multiple of 64 up to 256")
     ops().attn_set_prefill_kernel(hd, prefill_kernel)
     ops().attn_set_prefill_piece(hd, piece)
@@ -554,7 +555,8 @@ def test_attn_prefill_ignores_rows_that_are_not_a_sequences_own(nq, nkv, hd, win
         if dtype == torch.bfloat16:
             runs.append(("mma.sync", dict(seq_len=torch.tensor(lens, dtype=torch.int32, device=d)), 0))
             if hd % 64 == 0 and hd <= 256:
-                runs.append(("tcgen05", dict(seq_len=torch.tensor(lens, dtype=torch.int32, device=d)), 1))
+                runs.append(("tcgen05, CTAs that stay", dict(seq_len=torch.tensor(lens, dtype=torch.int32, device=d)), 3))
+                runs.append(("tcgen05, a CTA per tile", dict(seq_len=torch.tensor(lens, dtype=torch.int32, device=d)), 2))
         try:
             for name, extra, which in runs:
                 ops().attn_set_prefill_kernel(hd, which)
@@ -793,6 +795,34 @@ def test_attn_prefill_with_scores_that_climb(hd, slope, prefill_kernel):
     want = torch.empty((T, nq * hd), dtype=torch.float64)
     R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, 1.0 / math.sqrt(hd), 0.0, 0)
     close(out, want, 2 * BF16_TOL, "attn_prefill with climbing scores")
+    assert ops().attn_tc05_timeouts(hd) == 0
+
+
+@pytest.mark.parametrize("hd,window,cap", [(256, 0, 50.0), (64, 150, 0.0), (128, 70, 30.0)])
+def test_attn_prefill_of_many_sequences(hd, window, cap, prefill_kernel):
+    """Forty sequences of 1 to 400 tokens at 8 heads: several hundred tiles of queries, so the CTAs that stay take
+    four or five items each, one after another through the same rings and score buffers (tiles of 1 to 7 key
+    tiles, in any order of parity), and the search for a tile's sequence runs over more than 32 sequences."""
+    nq, nkv = 8, 4
+    ops().attn_set_prefill_kernel(hd, prefill_kernel)
+    rng = np.random.default_rng(61)
+    lens = [int(n) for n in rng.integers(1, 401, size=40)]
+    lens[7], lens[33] = 128, 257                                  # a tile border, and one token over it
+    T = sum(lens)
+    first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int()
+    tok_seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).int()
+    qkv = rnd((T, nq + 2 * nkv, hd), torch.bfloat16, 67)
+    d = dev()
+    scale = 1.0 / math.sqrt(hd)
+    for known in (None, lens):
+        out = torch.full((T, nq * hd), 9.0, dtype=torch.bfloat16, device=d)
+        ops().attn_prefill(qkv, tok_pos.to(d), tok_seq.to(d), first.to(d), out, nq, nkv, hd, scale, cap, window,
+                           seq_len=torch.tensor(lens, dtype=torch.int32, device=d), host_lens=known)
+        if known is None:
+            want = torch.empty((T, nq * hd), dtype=torch.float64)
+            R.attn_prefill(qkv.cpu(), tok_pos, tok_seq, first, want, nq, nkv, hd, scale, cap, window)
+        close(out, want, 2 * BF16_TOL, "attn_prefill of forty sequences")
     assert ops().attn_tc05_timeouts(hd) == 0
 
 
