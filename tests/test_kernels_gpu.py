@@ -880,6 +880,21 @@ def test_attn_decode_marks_an_undersized_launch():
     ops().attn_decode(qkv.bfloat16(), k.bfloat16(), v.bfloat16(), table, torch.tensor([0], dtype=torch.int32, device=d),
                       torch.tensor([200], dtype=torch.int32, device=d), scratch, outb, nq, nkv, hd, 1.0, 0.0, 0, 0, 64, 1)
     assert torch.isnan(outb.float()).all()
+    # and with chunks to merge: two chunks where four are needed, beside a sequence that fits; then a launch of the
+    # right size over the same scratch
+    lens = torch.tensor([200, 100], dtype=torch.int32, device=d)
+    table2 = torch.arange(8, dtype=torch.int32).view(2, 4).to(d)
+    q2 = rnd((2, nq + 2 * nkv, hd), torch.bfloat16, 36)
+    kb, vb = k.bfloat16(), v.bfloat16()
+    scratch2 = torch.empty(ops().attn_decode_scratch_floats(2, nq, hd, 4), dtype=torch.float32, device=d)
+    out2 = torch.zeros((2, nq * hd), dtype=torch.bfloat16, device=d)
+    slots2 = torch.tensor([0, 1], dtype=torch.int32, device=d)
+    ops().attn_decode(q2, kb, vb, table2, slots2, lens, scratch2, out2, nq, nkv, hd, 1.0, 0.0, 0, 0, 64, 2)
+    assert torch.isnan(out2[0].float()).all() and torch.isfinite(out2[1].float()).all()
+    ops().attn_decode(q2, kb, vb, table2, slots2, lens, scratch2, out2, nq, nkv, hd, 1.0, 0.0, 0, 0, 64, 4)
+    want = torch.empty((2, nq * hd), dtype=torch.float64)
+    R.attn_decode(q2.cpu(), kb.cpu(), vb.cpu(), table2.cpu(), slots2.cpu(), lens.cpu(), None, want, nq, nkv, hd, 1.0, 0.0, 0, 0, 64, 4)
+    close(out2, want, BF16_TOL, "attn_decode after an undersized launch")
 
 
 @pytest.mark.parametrize("Rn,V", [(1, 7), (5, 384), (3, 256000), (64, 1000), (2, 50003), (8, 32001), (32, 16384), (33, 20000)])
