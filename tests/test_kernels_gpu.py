@@ -826,6 +826,37 @@ def test_attn_prefill_of_many_sequences(hd, window, cap, prefill_kernel):
     assert ops().attn_tc05_timeouts(hd) == 0
 
 
+@pytest.mark.parametrize("window", [0, 1024])
+def test_attn_prefill_forms_agree_on_a_large_step(window):
+    """A step of more than nine thousand tokens at Gemma2-2B's head shape (too large for the plain statement in a
+    test's time): the two forms of the tcgen05 kernel walk the same tiles in the same order and give the same
+    bits, and the mma.sync kernel agrees with them within the tolerance of bfloat16 outputs."""
+    nq, nkv, hd = 8, 4, 256
+    lens = [4096, 1500, 3000, 777]
+    T = sum(lens)
+    d = dev()
+    first = torch.tensor([0] + list(np.cumsum(lens)[:-1]), dtype=torch.int32, device=d)
+    tok_pos = torch.cat([torch.arange(n) for n in lens]).int().to(d)
+    tok_seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).int().to(d)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=d)
+    qkv = rnd((T, nq + 2 * nkv, hd), torch.bfloat16, 83)
+    outs = {}
+    try:
+        for which in (3, 2, 0):
+            ops().attn_set_prefill_kernel(hd, which)
+            out = torch.full((T, nq * hd), 9.0, dtype=torch.bfloat16, device=d)
+            ops().attn_prefill(qkv, tok_pos, tok_seq, first, out, nq, nkv, hd, 1.0 / math.sqrt(hd), 50.0, window,
+                               seq_len=seq_len, host_lens=lens)
+            outs[which] = out
+    finally:
+        ops().attn_set_prefill_kernel(hd, 1)
+    assert torch.isfinite(outs[3].float()).all()
+    assert torch.equal(outs[3], outs[2])
+    # (each kernel is held to 2 x BF16_TOL of the exact result elsewhere: to each other they may differ by twice that)
+    close(outs[3], outs[0].double().cpu(), 4 * BF16_TOL, "tcgen05 against mma.sync on a large step")
+    assert ops().attn_tc05_timeouts(hd) == 0
+
+
 @pytest.mark.parametrize("window", [0, 600])
 def test_attn_prefill_of_a_long_prompt(window, prefill_kernel):
     """A prompt of many tiles next to short ones (no tile is shared: the step has enough of them)."""
