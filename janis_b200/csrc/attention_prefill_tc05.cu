@@ -6,14 +6,18 @@
 // are those of attention_prefill_mma.cu).  Three roles:
 //   * one thread brings Q once and then K and V tiles by TMA tensor maps (128-byte swizzle, slabs of 64
 //     features) into rings of two stages each;
-//   * one thread issues tcgen05.mma: S = Q K^T (K-major operands) into one of two [128 x 64] float
-//     buffers in tensor memory, and O += P V (V is the MN-major operand: its rows are keys) into a
-//     [128 x head size] float accumulator in tensor memory;
+//   * two threads issue tcgen05.mma, each on its own: one S = Q K^T (K-major operands from shared memory) into
+//     one of two [128 x 64] float buffers in tensor memory, the other O += P V (P from tensor memory, V from
+//     shared memory as the MN-major operand: its rows are keys) into a [128 x head size] float accumulator
+//     in tensor memory.  Issuing a product costs a thread 85 to 110 cycles (a tile has twenty of them): one
+//     thread for both spent 1,900 of a tile's 3,400 cycles issuing;
 //   * sixteen warps do the softmax, four threads per query row (tensor-memory lane = row; a thread takes
 //     16 of a tile's 64 keys): tcgen05.ld of the scores, scale, cap * tanh, masks on absolute positions,
-//     the row's maximum through shared memory, exponentials, P rounded to bfloat16 into shared memory
-//     for the second product.  Four softmax warps per scheduler hide each other's latencies; with one
-//     the kernel ran at a sixth of an instruction per cycle.
+//     the row's maximum through shared memory, exponentials, P rounded to bfloat16 into one of two
+//     buffers in tensor memory (pairs of keys per 32-bit column) for the second product.  With one buffer of
+//     P (in shared memory) the softmax of a tile had to wait for the products of the tile before.  Four
+//     softmax warps per scheduler hide each other's latencies; with one the kernel ran at a sixth of an
+//     instruction per cycle.
 // The scores run two tiles ahead of P V, and every softmax thread has two tiles in flight: it takes tile
 // i + 1 out of tensor memory, caps and masks it and publishes its maximum before it turns tile i into P, so
 // that it waits neither for the products nor for the other threads of its row.  The accumulator is
@@ -48,9 +52,8 @@ constexpr int KV_SLAB = BN * 128;
 constexpr int Q_BYTES = SLABS * Q_SLAB;
 constexpr int KV_TILE = SLABS * KV_SLAB;              // one of K or V, one stage
 constexpr int STAGES = 2;
-constexpr int P_BYTES = BM * 128;                     // 64 keys of bfloat16 per query row
-constexpr int SMEM_BYTES = 1024 + Q_BYTES + STAGES * 2 * KV_TILE + P_BYTES;
-constexpr int TMEM_COLS = HD + 128 <= 256 ? 256 : 512;        // O, then two buffers of S
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + STAGES * 2 * KV_TILE;
+constexpr int TMEM_COLS = HD + 192 <= 256 ? 256 : 512;        // O, two buffers of S, two of P (bfloat16 pairs: 32 columns each)
 #ifndef JANIS_PT_SPLIT
 #define JANIS_PT_SPLIT 4
 #endif
@@ -58,8 +61,8 @@ constexpr int SPLIT = JANIS_PT_SPLIT;                 // threads that share a qu
 constexpr int CPT = 64 / SPLIT;                       // keys per softmax thread and tile: 16
 static_assert(SPLIT == 4, "the softmax works in pieces of 16 columns");
 constexpr int SOFTMAX_WARPS = 4 * SPLIT;              // warp w: rows 32 (w % 4) .., keys CPT (w / 4) .. of a tile
-constexpr int LOADER_WARP = SOFTMAX_WARPS, ISSUER_WARP = SOFTMAX_WARPS + 1;
-constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+constexpr int LOADER_WARP = SOFTMAX_WARPS, ISSUER_WARP = SOFTMAX_WARPS + 1, PV_WARP = SOFTMAX_WARPS + 2;
+constexpr int THREADS = (SOFTMAX_WARPS + 3) * 32;
 constexpr int OCOLS = HD / SPLIT;                     // accumulator columns a softmax thread looks after
 constexpr float RESCALE_STEP = 8.0f;                  // in units of log2: P stays below 2^8
 // The softmax's work per score is what bounds this kernel, most of it on the special-function unit (16 results a
@@ -94,7 +97,7 @@ __device__ __forceinline__ float ex2_poly(float x) {
     return x < -126.0f ? 0.f : r;
 }
 
-enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_DONE = 14, ROW_X = 15, N_BARS = 17 };
+enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_DONE = 15, ROW_X = 17, N_BARS = 19 };
 
 __device__ int g_timeouts = 0;
 
@@ -157,6 +160,13 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
         "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// the same with the first operand in tensor memory (row i in lane i, two bfloat16 of K per 32-bit column)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -179,6 +189,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -236,8 +251,6 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t sQ = (raw + 1023) & ~1023u;        // swizzle atoms want 1024-byte alignment
     const uint32_t sKV = sQ + Q_BYTES;                // stage s: K at sKV + s * 2 KV_TILE, V right after
-    const uint32_t sP = sKV + STAGES * 2 * KV_TILE;
-    unsigned char* p_ptr = smem_raw + (sP - raw);
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
     auto bar = [&](int i) { return bar0 + 8 * i; };
 
@@ -251,8 +264,10 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_init(bar(S_FULL + i), 1);
             mbar_init(bar(S_EMPTY + i), SOFTMAX_WARPS);
         }
-        mbar_init(bar(P_FULL), SOFTMAX_WARPS);
-        mbar_init(bar(O_DONE), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(P_FULL + i), SOFTMAX_WARPS);
+            mbar_init(bar(O_DONE + i), 1);
+        }
         mbar_init(bar(ROW_X), SOFTMAX_WARPS);
         mbar_init(bar(ROW_X + 1), SOFTMAX_WARPS);
         failed = 0;
@@ -279,7 +294,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tO = tmem, tS = tmem + HD;          // S buffer b at tS + 64 b
+    const uint32_t tO = tmem, tS = tmem + HD, tP = tS + 128;   // S buffer b at tS + 64 b, P buffer b at tP + 32 b
     const volatile int* fail_flag = &failed;
 
     if (warp == LOADER_WARP && lane == 0) {
@@ -315,48 +330,47 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         if (!ok) atomicExch(&failed, 1);
     } else if (warp == ISSUER_WARP && lane == 0) {
-        // ---- the thread that issues the products
-        const uint32_t idesc_s = instr_desc(BM, BN, false), idesc_o = instr_desc(BM, HD, true);
-        auto scores = [&](int it) {                   // S[it & 1] = Q K(it)^T
-            const uint32_t sK = sKV + (it & 1) * 2 * KV_TILE;
+        // ---- the thread that issues the scores: S[it & 1] = Q K(it)^T, two tiles ahead of P V.  (Issuing one
+        // tcgen05.mma costs the thread 85 to 110 cycles, more than a product of 64 keys runs: with one thread
+        // for both kinds of product, issuing them took 1,900 of a tile's 3,400 cycles.)
+        const uint32_t idesc_s = instr_desc(BM, BN, false);
+        const uint64_t dQ = smem_desc(sQ), dK[2] = {smem_desc(sKV), smem_desc(sKV + 2 * KV_TILE)};
+        bool ok = mbar_wait(bar(Q_FULL), 0, fail_flag);
+        for (int it = 0; ok && it < n_tiles; ++it) {
+            const int b = it & 1;
+            ok = mbar_wait(bar(K_FULL + b), (it >> 1) & 1, fail_flag) &&
+                 (it < 2 || mbar_wait(bar(S_EMPTY + b), ((it >> 1) - 1) & 1, fail_flag));
+            if (!ok) break;
+            fence_after();
+            const uint64_t dk = dK[b];
+            const uint32_t ts = tS + 64 * b;
+#pragma unroll
             for (int sl = 0; sl < SLABS; ++sl)
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
-                    umma(tS + 64 * (it & 1), smem_desc(sQ + sl * Q_SLAB + kk * 32), smem_desc(sK + sl * KV_SLAB + kk * 32),
+                    umma(ts, dQ + (uint64_t)((sl * Q_SLAB + kk * 32) >> 4), dk + (uint64_t)((sl * KV_SLAB + kk * 32) >> 4),
                          idesc_s, (sl > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(bar(S_FULL + (it & 1)));      // the scores are there ...
-            umma_commit(bar(K_EMPTY + (it & 1)));     // ... and these keys are no longer needed
-        };
-        bool ok = mbar_wait(bar(Q_FULL), 0, fail_flag) && mbar_wait(bar(K_FULL), 0, fail_flag);
-        if (ok) {
-            fence_after();
-            scores(0);
+            umma_commit(bar(S_FULL + b));             // the scores are there ...
+            umma_commit(bar(K_EMPTY + b));            // ... and these keys are no longer needed
         }
-        if (ok && n_tiles > 1) {
-            ok = mbar_wait(bar(K_FULL + 1), 0, fail_flag);
-            if (ok) {
-                fence_after();
-                scores(1);
-            }
-        }
+        if (!ok) atomicExch(&failed, 1);
+    } else if (warp == PV_WARP && lane == 0) {
+        // ---- the thread that issues O += P V
+        const uint32_t idesc_o = instr_desc(BM, HD, true);
+        const uint64_t dV[2] = {smem_desc(sKV + KV_TILE, KV_SLAB), smem_desc(sKV + 2 * KV_TILE + KV_TILE, KV_SLAB)};
+        bool ok = true;
         for (int it = 0; ok && it < n_tiles; ++it) {
-            if (it + 2 < n_tiles) {                   // the scores run two tiles ahead: the softmax reads tile it + 1
-                const int nx = it + 2, b = nx & 1;    // while it finishes tile it
-                ok = mbar_wait(bar(K_FULL + b), (nx >> 1) & 1, fail_flag) &&
-                     mbar_wait(bar(S_EMPTY + b), ((nx >> 1) - 1) & 1, fail_flag);
-                if (!ok) break;
-                fence_after();
-                scores(nx);
-            }
-            ok = mbar_wait(bar(P_FULL), it & 1, fail_flag) && mbar_wait(bar(V_FULL + (it & 1)), (it >> 1) & 1, fail_flag);
+            const int b = it & 1;
+            ok = mbar_wait(bar(P_FULL + b), (it >> 1) & 1, fail_flag) && mbar_wait(bar(V_FULL + b), (it >> 1) & 1, fail_flag);
             if (!ok) break;
             fence_after();
-            const uint32_t sV = sKV + (it & 1) * 2 * KV_TILE + KV_TILE;
+            const uint64_t dv = dV[b];
+            const uint32_t tp = tP + 32 * b;
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)              // O += P[:, 16 kk ..] V[16 kk .., :]: all features in one instruction
-                umma(tO, smem_desc(sP + kk * 32), smem_desc(sV + kk * 2048, KV_SLAB), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(bar(V_EMPTY + (it & 1)));      // the values are free once these have read them
-            umma_commit(bar(O_DONE));                  // and the accumulator holds tile `it`
+            for (int kk = 0; kk < 4; ++kk)              // P[:, 16 kk ..] from tensor memory, V[16 kk .., :]: all features in one instruction
+                umma_ts(tO, tp + kk * 8, dv + (uint64_t)((kk * 2048) >> 4), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(bar(V_EMPTY + b));             // the values are free once these have read them
+            umma_commit(bar(O_DONE + b));              // and the accumulator holds tile `it`; P's buffer is free
         }
         if (!ok) atomicExch(&failed, 1);
     } else if (warp < SOFTMAX_WARPS) {
@@ -444,11 +458,16 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 l_run += p0 + p1;
                 pk[j / 2] = pf::pack_bf16(p0, p1);
             }
-            // P's buffer and the accumulator are free once the products of the tile before have finished
-            if (it > 0) {
-                if (!mbar_wait(bar(O_DONE), (it - 1) & 1, fail_flag)) return false;
+            // P has two buffers in tensor memory: this tile's is free once the products of the tile before last have
+            // finished, so the softmax does not wait for the products of the tile before (it did, with one buffer of
+            // P in shared memory: the round trip softmax -> products -> softmax then set the time of a tile, 1.5 us
+            // whatever the head size, with the softmax's arithmetic taken out as well as with it).  Only a warp that
+            // has to rescale the accumulator waits for them.
+            if (it >= 2 && !mbar_wait(bar(O_DONE + (it & 1)), ((it - 2) >> 1) & 1, fail_flag)) return false;
+            if (it > 0 && __any_sync(0xffffffffu, grow)) {   // tensor-memory accesses are warp-wide: rows that keep their reference use 1
+                if (!mbar_wait(bar(O_DONE + ((it - 1) & 1)), ((it - 1) >> 1) & 1, fail_flag)) return false;
                 fence_after();
-                if (__any_sync(0xffffffffu, grow)) {  // tensor-memory accesses are warp-wide: rows that keep their reference use 1
+                {
 #pragma unroll 1
                     for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
                         uint32_t o[16];
@@ -477,18 +496,15 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         const int sl = idx / pieces, pc = idx % pieces;
                         *reinterpret_cast<uint4*>(v_ptr + sl * KV_SLAB + n_valid * 128 + pc * 16) = make_uint4(0u, 0u, 0u, 0u);
                     }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");     // before the products read them
                 }
             }
-            // this thread's CPT keys of row r of P: pieces of 16 bytes, swizzled like the TMA tiles
-#pragma unroll
-            for (int c = 0; c < CPT / 8; ++c) {
-                const int piece = (CPT / 8) * h + c;
-                *reinterpret_cast<uint4*>(p_ptr + r * 128 + ((piece ^ (r & 7)) << 4)) =
-                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            // this thread's CPT keys of row r of P: CPT / 2 columns of its lane in the tile's buffer
+            fence_after();
+            tmem_st8(tP + 32 * (it & 1) + (CPT / 2) * h + lane_base, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             fence_before();
-            warp_arrive(bar(P_FULL), lane);
+            warp_arrive(bar(P_FULL + (it & 1)), lane);
             return true;
         };
         uint32_t sv[CPT], sv_next[CPT];
@@ -501,7 +517,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int j = 0; j < CPT; ++j) sv[j] = sv_next[j];
             base = base_next;
         }
-        if (ok) ok = mbar_wait(bar(O_DONE), (n_tiles - 1) & 1, fail_flag);
+        if (ok) ok = mbar_wait(bar(O_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, fail_flag);
         if (!ok) atomicExch(&failed, 1);
         // the row's sum, in the order of the threads' keys
         if (ok) {
@@ -659,8 +675,6 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t sQ = (raw + 1023) & ~1023u;
     const uint32_t sKV = sQ + Q_BYTES;
-    const uint32_t sP = sKV + STAGES * 2 * KV_TILE;
-    unsigned char* p_ptr = smem_raw + (sP - raw);
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
     auto bar = [&](int i) { return bar0 + 8 * i; };
     const volatile int* fail_flag = &failed;
@@ -677,10 +691,10 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
             mbar_init(bar(S_EMPTY + i), SOFTMAX_WARPS);
             mbar_init(bar(ROW_X + i), SOFTMAX_WARPS);
             mbar_init(bar(ITEM_FULL + i), 1);
-            mbar_init(bar(ITEM_EMPTY + i), SOFTMAX_WARPS + 1);
+            mbar_init(bar(ITEM_EMPTY + i), SOFTMAX_WARPS + 2);
+            mbar_init(bar(P_FULL + i), SOFTMAX_WARPS);
+            mbar_init(bar(O_DONE + i), 1);
         }
-        mbar_init(bar(P_FULL), SOFTMAX_WARPS);
-        mbar_init(bar(O_DONE), 1);
         mbar_init(bar(EPI_DONE), SOFTMAX_WARPS);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -740,7 +754,7 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
     __syncthreads();
     fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tO = tmem, tS = tmem + HD;
+    const uint32_t tO = tmem, tS = tmem + HD, tP = tS + 128;
     const int group = nq / nkv;
 
     if (warp == LOADER_WARP) {
@@ -804,8 +818,9 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
         }
         if (!ok && lane == 0) atomicExch(&failed, 1);
     } else if (warp == ISSUER_WARP && lane == 0) {
-        // ---- the thread that issues the products
-        const uint32_t idesc_s = instr_desc(BM, BN, false), idesc_o = instr_desc(BM, HD, true);
+        // ---- the thread that issues the scores
+        const uint32_t idesc_s = instr_desc(BM, BN, false);
+        const uint64_t dQ = smem_desc(sQ), dK[2] = {smem_desc(sKV), smem_desc(sKV + 2 * KV_TILE)};
         bool ok = true;
         int g = 0;
         for (int k = 0; ok; ++k) {
@@ -814,40 +829,52 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
             const int n = items[k & 1].n_tiles;
             mbar_arrive(bar(ITEM_EMPTY + (k & 1)));
             if (n < 0) break;
-            auto scores = [&](int i) -> bool {        // S[(g + i) & 1] = Q K(i)^T
+            ok = mbar_wait(bar(Q_FULL), k & 1, fail_flag);
+            for (int i = 0; ok && i < n; ++i) {      // S[(g + i) & 1] = Q K(i)^T
                 const int gi = g + i, b = gi & 1;
-                if (i == 0 && !mbar_wait(bar(Q_FULL), k & 1, fail_flag)) return false;
-                if (!mbar_wait(bar(K_FULL + b), (gi >> 1) & 1, fail_flag)) return false;
-                if (gi >= 2 && !mbar_wait(bar(S_EMPTY + b), ((gi >> 1) - 1) & 1, fail_flag)) return false;
+                ok = mbar_wait(bar(K_FULL + b), (gi >> 1) & 1, fail_flag) &&
+                     (gi < 2 || mbar_wait(bar(S_EMPTY + b), ((gi >> 1) - 1) & 1, fail_flag));
+                if (!ok) break;
                 fence_after();
-                const uint32_t sK = sKV + b * 2 * KV_TILE;
+                const uint64_t dk = dK[b];
+                const uint32_t ts = tS + 64 * b;
+#pragma unroll
                 for (int sl = 0; sl < SLABS; ++sl)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma(tS + 64 * b, smem_desc(sQ + sl * Q_SLAB + kk * 32), smem_desc(sK + sl * KV_SLAB + kk * 32),
+                        umma(ts, dQ + (uint64_t)((sl * Q_SLAB + kk * 32) >> 4), dk + (uint64_t)((sl * KV_SLAB + kk * 32) >> 4),
                              idesc_s, (sl > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(bar(S_FULL + b));
                 umma_commit(bar(K_EMPTY + b));
                 if (i == n - 1) umma_commit(bar(Q_EMPTY));     // the item's last scores: Q may be overwritten
-                return true;
-            };
-            ok = scores(0);
-            if (ok && n > 1) ok = scores(1);
+            }
+            g += n;
+        }
+        if (!ok) atomicExch(&failed, 1);
+    } else if (warp == PV_WARP && lane == 0) {
+        // ---- the thread that issues O += P V
+        const uint32_t idesc_o = instr_desc(BM, HD, true);
+        const uint64_t dV[2] = {smem_desc(sKV + KV_TILE, KV_SLAB), smem_desc(sKV + 2 * KV_TILE + KV_TILE, KV_SLAB)};
+        bool ok = true;
+        int g = 0;
+        for (int k = 0; ok; ++k) {
+            ok = mbar_wait(bar(ITEM_FULL + (k & 1)), (k >> 1) & 1, fail_flag);
+            if (!ok) break;
+            const int n = items[k & 1].n_tiles;
+            mbar_arrive(bar(ITEM_EMPTY + (k & 1)));
+            if (n < 0) break;
             for (int it = 0; ok && it < n; ++it) {
-                if (it + 2 < n) {
-                    ok = scores(it + 2);
-                    if (!ok) break;
-                }
                 const int gi = g + it, b = gi & 1;
-                ok = mbar_wait(bar(P_FULL), gi & 1, fail_flag) && mbar_wait(bar(V_FULL + b), (gi >> 1) & 1, fail_flag);
+                ok = mbar_wait(bar(P_FULL + b), (gi >> 1) & 1, fail_flag) && mbar_wait(bar(V_FULL + b), (gi >> 1) & 1, fail_flag);
                 if (!ok) break;
                 fence_after();
-                const uint32_t sV = sKV + b * 2 * KV_TILE + KV_TILE;
+                const uint64_t dv = dV[b];
+                const uint32_t tp = tP + 32 * b;
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
-                    umma(tO, smem_desc(sP + kk * 32), smem_desc(sV + kk * 2048, KV_SLAB), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+                    umma_ts(tO, tp + kk * 8, dv + (uint64_t)((kk * 2048) >> 4), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(bar(V_EMPTY + b));
-                umma_commit(bar(O_DONE));
+                umma_commit(bar(O_DONE + b));
             }
             g += n;
         }
@@ -938,12 +965,13 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
                     l_run += p0 + p1;
                     pk[j / 2] = pf::pack_bf16(p0, p1);
                 }
-                // P's buffer and the accumulator are free once the products of the tile before have finished (an
-                // item's first tile follows the wait for the last products of the item before, below)
-                if (it > 0) {
-                    if (!mbar_wait(bar(O_DONE), (gi - 1) & 1, fail_flag)) return false;
+                // P's buffer is free once the products of the tile before last have finished (across items too); only
+                // a warp that has to rescale the accumulator waits for the products of the tile before
+                if (gi >= 2 && !mbar_wait(bar(O_DONE + b), ((gi - 2) >> 1) & 1, fail_flag)) return false;
+                if (it > 0 && __any_sync(0xffffffffu, grow)) {
+                    if (!mbar_wait(bar(O_DONE + ((gi - 1) & 1)), ((gi - 1) >> 1) & 1, fail_flag)) return false;
                     fence_after();
-                    if (__any_sync(0xffffffffu, grow)) {
+                    {
 #pragma unroll 1
                         for (int c = OCOLS * h; c < OCOLS * (h + 1); c += 16) {
                             uint32_t o[16];
@@ -967,17 +995,14 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
                             const int sl = idx / pieces, pc = idx % pieces;
                             *reinterpret_cast<uint4*>(v_ptr + sl * KV_SLAB + n_valid * 128 + pc * 16) = make_uint4(0u, 0u, 0u, 0u);
                         }
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");     // before the products read them
                     }
                 }
-#pragma unroll
-                for (int c = 0; c < CPT / 8; ++c) {
-                    const int pc = (CPT / 8) * h + c;
-                    *reinterpret_cast<uint4*>(p_ptr + r * 128 + ((pc ^ (r & 7)) << 4)) =
-                        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-                }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                fence_after();
+                tmem_st8(tP + 32 * b + (CPT / 2) * h + lane_base, pk);
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 fence_before();
-                warp_arrive(bar(P_FULL), lane);
+                warp_arrive(bar(P_FULL + b), lane);
                 return true;
             };
             uint32_t sv[CPT], sv_next[CPT];
@@ -990,7 +1015,7 @@ attn_prefill_tc05_items_kernel(const __grid_constant__ CUtensorMap map_q, const 
                 for (int j = 0; j < CPT; ++j) sv[j] = sv_next[j];
                 base = base_next;
             }
-            if (ok) ok = mbar_wait(bar(O_DONE), (g + n_tiles - 1) & 1, fail_flag);
+            if (ok) ok = mbar_wait(bar(O_DONE + ((g + n_tiles - 1) & 1)), ((g + n_tiles - 1) >> 1) & 1, fail_flag);
             if (ok) {
                 const int x = gx + n_tiles;
                 row_sum[h][r] = l_run;
@@ -1124,10 +1149,11 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int 
 }  // namespace pt
 
 // Which form of the kernel a step runs: 0 a CTA per tile of queries and head, 2 CTAs that stay and take item after
-// item, 1 (default) by the step's size: the CTAs that stay save the coming and going of a CTA (about 3 us an item) and
-// lose a little where a CTA gets one item or two (they ask for their next item late, so that none holds work that
-// another could do).  Measured per layer at 8 heads of 256: 4 prompts of 4,096 tokens 374 -> 351 us, one of 8,192
-// 346 -> 340, 40 of 100 tokens 31.8 -> 24.1; one of 2,048 43.0 -> 45.5, one of 1,024 21.5 -> 23.2.
+// item, 1 (default) by the step's size: the CTAs that stay where the step has a place an SM or more (they save the
+// coming and going of a CTA, about 3 us an item, and ask for their next item late, so that none holds work that
+// another could do), a CTA per tile below that (there the two are equal).  Measured per layer at 8 heads of 256, a
+// CTA per tile against CTAs that stay: 4 prompts of 4,096 tokens 357 -> 320 us, one of 8,192 321 -> 301, one of
+// 4,096 95.8 -> 91.3, 40 of 100 tokens 30.8 -> 24.4, one of 2,048 40.2 = 40.2, two of 1,024 29.3 -> 30.2.
 static int g_tc05_items = 1;
 
 static int tc05_sm_count() {
@@ -1160,7 +1186,7 @@ int launch_prefill_tc05(const void* q_src, const void* kv_src, int n_tok, const 
                                           cudaGetErrorString(e));
         configured = true;
     }
-    const bool many = (long long)n_tiles_bound * parts * nq >= 2LL * tc05_sm_count();
+    const bool many = (long long)n_tiles_bound * parts * nq >= (long long)tc05_sm_count();
     if (g_tc05_items == 2 || (g_tc05_items == 1 && many)) {
         static bool items_configured = false;
         if (!items_configured) {
