@@ -395,12 +395,13 @@ static int g_prefill_piece = 0;     // key tiles per piece of a shared tile of q
 JANIS_EXPORT void janis_attn_set_prefill_piece(int piece) { g_prefill_piece = piece > 0 ? piece : 0; }
 
 // How long a step takes whose shared tiles are cut into pieces of `piece` key tiles, in microseconds, by a model
-// of four numbers fitted to a B200 at head size 256 (150 timings of 1 to 7 prompts of 300 to 4,096 tokens and
-// pieces of 4 to 140 tiles, 4 % off on average): a CTA costs `cta` before and after its tiles (9.9 us for the tcgen05
-// kernel: its launch, Q and the first keys, the two tiles the softmax runs behind, the way out), `tile` per key
-// tile, 1.9 us more when it leaves a partial result, and the merge 0.8 us and 0.39 us per round of partial rows.
-// CTAs go to the SM that is free first, in the order of their launch.  The step's lengths are on the device: the
-// model takes n_seq sequences of equal length.
+// of five numbers fitted to a B200 at head size 256 (60 timings of 1 to 7 prompts of 300 to 4,096 tokens and
+// pieces of 4 to "nothing shared", 5 % off on average): a CTA's item costs `cta` besides its tiles (7.1 us for the
+// tcgen05 kernel: Q and the first keys, the tiles the softmax runs behind, the masked tiles at the diagonal, the way
+// out; 9.9 us before P moved to tensor memory), `tile` per key tile (1.22 us), 1.8 us more when it leaves a partial
+// result, and a step with shared tiles 6 us for the places of parts that come to nothing and for the merge's
+// launch, plus 0.45 us per round of partial rows.  CTAs go to the SM that is free first, in the order of their
+// launch.  The step's lengths are on the device: the model takes n_seq sequences of equal length.
 static double prefill_model_us(int n_seq, int len, int nq, int window, int parts, int piece, int sms, double cta,
                                double tile, int* longest) {
     std::vector<std::pair<int, bool>> items;          // key tiles, leaves a partial result; in tile order
@@ -420,12 +421,12 @@ static double prefill_model_us(int n_seq, int len, int nq, int window, int parts
     for (int s = n_seq - 1; s >= 0; --s)              // the last tile of the last sequence is launched first
         for (int i = (int)items.size() - 1; i >= 0; --i)
             for (int h = 0; h < nq; ++h) {
-                const double t = free_at.top() + cta + tile * items[i].first + (items[i].second ? 1.9 : 0.0);
+                const double t = free_at.top() + cta + tile * items[i].first + (items[i].second ? 1.8 : 0.0);
                 free_at.pop();
                 free_at.push(t);
                 end = std::max(end, t);
             }
-    if (split_parts) end += 0.8 + 0.39 * (double)(split_parts * n_seq * nq) / sms;
+    if (split_parts) end += 6.0 + 0.45 * (double)(split_parts * n_seq * nq) / sms;
     return end;
 }
 
@@ -444,7 +445,7 @@ static int prefill_piece_for(int n_tok, int n_seq, int nq, int window, int parts
         const int sms = sm_count();
         // per key tile: the softmax's share does not depend on the head size, the products' does; the mma.sync
         // kernel took 2.7 times as long per tile at head size 256 and has less to do around its tiles
-        const double tile = tc05 ? 1.0 + 0.43 * pf::HD / 256.0 : 3.9 * pf::HD / 256.0, cta = tc05 ? 9.9 : 6.0;
+        const double tile = tc05 ? 1.0 + 0.22 * pf::HD / 256.0 : 3.9 * pf::HD / 256.0, cta = tc05 ? 7.1 : 6.0;
         int most = 0, best = 4;
         double best_us = prefill_model_us(n_seq, len, nq, window, parts, 4, sms, cta, tile, &most);
         long long key_tiles = 0;
@@ -503,7 +504,8 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
                                         int nkv, int q_row_heads, int kv_row_heads, int kv_k_head0, float scale,
                                         float cap, int window, float* partial, long long partial_floats,
                                         const int* seq_start, const int* seq_slot, const void* kpool, const void* vpool,
-                                        const int* page_table, int table_stride, int ring_len, cudaStream_t stream) {
+                                        const int* page_table, int table_stride, int ring_len, int max_len,
+                                        cudaStream_t stream) {
     if (n_seq <= 0 || n_tiles_bound <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attn_prefill_mma: %d query heads do not divide over %d key heads", nq, nkv);
     if (((uintptr_t)q_src | (uintptr_t)kv_src | (uintptr_t)out | (uintptr_t)partial | (uintptr_t)kpool | (uintptr_t)vpool) & 15)
@@ -533,14 +535,15 @@ JANIS_EXPORT int janis_attn_prefill_mma(const void* q_src, const void* kv_src, i
     if (piece <= 0 && parts > 1) {
         int longest = 0;
         piece = prefill_piece_for(n_tok, n_seq, nq, window, parts, tc05, &longest);
-        // (the sequences' real lengths may differ from the model's: a tile of queries of a step that starts its
-        // sequences never has more key tiles than the step has tokens)
-        if (!ext && piece >= longest && piece >= n_tok / pf::BN + 1) parts = 1;
     }
     if (piece <= 0) piece = 4;
-    // No tile of queries has more key tiles than the step has tokens (when its sequences start with it): places for
-    // parts that no tile can have would be CTAs that only come and go, and a CTA of this size takes 2 to 3 us to do so.
-    if (!ext && parts > 1) parts = std::max(1, std::min(parts, (n_tok / pf::BN + 1 + piece - 1) / piece));
+    // No tile of queries has more key tiles than the step's longest sequence has (when the sequences start with the
+    // step): places for parts that no tile can have would be CTAs that only come and go (2 to 3 us each for a CTA of
+    // this size), and a piece that no tile exceeds means that nothing is shared: no places for parts, no merge.
+    // (max_len: the longest sequence's tokens in this step, when the host knows them; else the step's tokens bound it)
+    int most_tiles = ((max_len > 0 ? std::min(max_len, n_tok) : n_tok) + pf::BN - 1) / pf::BN;
+    if (window > 0) most_tiles = std::min(most_tiles, (window + pf::BM) / pf::BN + 1);        // a window bounds a tile's keys
+    if (!ext && parts > 1) parts = std::max(1, std::min(parts, (most_tiles + piece - 1) / piece));
     if ((long long)n_tiles_bound * parts > 65535) return fail("attn_prefill_mma: %d tiles of queries exceed the grid", n_tiles_bound);
     int done = -1;
     if (g_prefill_kernel == 1 && !ext)                // the tcgen05 kernel takes sequences that start at position 0

@@ -90,7 +90,7 @@ def attention_lib(head_dim: int):
         lib.janis_attn_prefill.argtypes = [P, P, I, P, P, P, P, I, I, I, I, I, I, F, F, I, P, P, P, P, P, I, I, P]
         lib.janis_attn_decode.argtypes = [P, P, P, I, P, I, P, P, P, c_longlong, P, I, I, I, I, F, F, I, I, I, I, P]
         lib.janis_attn_prefill_mma.argtypes = [P, P, I, P, P, I, I, P, I, I, I, I, I, F, F, I, P, c_longlong,
-                                               P, P, P, P, P, I, I, P]
+                                               P, P, P, P, P, I, I, I, P]
         lib.janis_attn_set_prefill_kernel.argtypes = [I]
         lib.janis_attn_set_prefill_kernel.restype = None
         lib.janis_attn_set_prefill_piece.argtypes = [I]
@@ -585,7 +585,8 @@ def _attn_prefill_mma(qkv, seq_first_row, seq_len, out, nq, nkv, hd, scale, cap,
                                            seq_len.data_ptr(), n_seq, tiles, out.data_ptr(), nq, nkv,
                                            qkv.shape[1], kv_row_heads, kv_k_head0, float(scale), float(cap),
                                            int(window), _t(scratch, "scratch", torch.float32) if scratch is not None else None,
-                                           scratch.numel() if scratch is not None else 0, *cached, _stream()))
+                                           scratch.numel() if scratch is not None else 0, *cached,
+                                           max(int(n) for n in host_lens) if host_lens else 0, _stream()))
     global _launches
     _launches += int(lib.janis_attn_prefill_kernels()) - 1     # the merge, when tiles were shared
     return out
