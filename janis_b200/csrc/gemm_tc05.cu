@@ -360,11 +360,15 @@ JANIS_EXPORT void janis_tc05_set_stages(int stages) {
     g_tc05_stages = stages <= 0 ? 0 : (stages < tc::MIN_STAGES ? tc::MIN_STAGES : (stages > tc::MAX_STAGES ? tc::MAX_STAGES : stages));
 }
 
-// The same count copied into `host` (pinned memory, one int) in the order of `stream`, without waiting for it: a
-// caller that waits for the stream anyway (for its tokens) finds the count there afterwards.
+namespace janis { int gemv_push_timeouts_async(int* host, cudaStream_t stream); }      // gemv_bf16.cu
+
+// The same count copied into `host` (pinned memory, two ints: this kernel's count, then that of the skinny products'
+// clusters) in the order of `stream`, without waiting for it: a caller that waits for the stream anyway (for its
+// tokens) finds the counts there afterwards.
 JANIS_EXPORT int janis_tc05_timeouts_async(int* host, cudaStream_t stream) {
     cudaError_t e = cudaMemcpyFromSymbolAsync(host, tc::g_timeouts, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
-    return e == cudaSuccess ? 0 : fail("tc05_timeouts_async: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail("tc05_timeouts_async: %s", cudaGetErrorString(e));
+    return janis::gemv_push_timeouts_async(host + 1, stream);
 }
 
 JANIS_EXPORT int janis_tc05_timeouts() {

@@ -426,7 +426,7 @@ class WaitWatch:
         self._where: dict[str, int] = {}           # library -> index of its first counter
         self._seen = [0] * 64
 
-    def _slot(self, name: str) -> int:              # two counters a library (the core library uses one)
+    def _slot(self, name: str) -> int:              # two counters a library (core: the tcgen05 product's waits, the clusters' of the skinny products)
         if name not in self._where:
             if 2 * len(self._where) + 2 > 64:
                 raise KernelError("too many attention libraries for one watch")
