@@ -515,11 +515,14 @@ __device__ __forceinline__ void fill_heads(bf16* out, int s, int nq, int nkv, in
 // than two an SM can hold, more CTAs in flight pay more than depth (64 sequences of unequal lengths: 63.6 -> 56.5 us a
 // layer with two stages; 8 sequences of 8,100 keys: 49.5 -> 47.8 us); with fewer CTAs than that, depth does (one
 // sequence: 523 against 545 tok/s); four stages and one CTA an SM are far slower (98 us).  The launch chooses.
-template <int NS>
+// WIDE: stages of 64 keys at head sizes above 128 too (a warp then has two column tiles of scores in flight): for
+// launches with no more CTAs than SMs, where a CTA has an SM's shared memory to itself and the time of a tile, not
+// the CTAs an SM holds, sets the pace (one sequence: 2.7 us for a tile of 32 keys, a CTA's chunk of 64 keys 5.4 us).
+template <int NS, bool WIDE = false>
 struct MmaDecode {
     static constexpr int WARPS = 4;
     static constexpr int STAGES = NS;
-    static constexpr int TILE = HD <= 128 ? 64 : 32;                 // keys per stage
+    static constexpr int TILE = (HD <= 128 || WIDE) ? 64 : 32;       // keys per stage
     static constexpr int NT = TILE / 32;                              // 8-key column tiles per warp and stage
     static constexpr int TILE_BYTES = TILE * HD * 2;
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -534,13 +537,13 @@ struct MmaDecode {
 
 // DIRECT: the launch has one chunk per sequence and the kernel writes the result itself (`out`); otherwise it
 // leaves a partial per chunk for the merge kernel.
-template <int RB, bool DIRECT, int NS>
-__global__ void __launch_bounds__(MmaDecode<NS>::WARPS * 32)
+template <int RB, bool DIRECT, int NS, bool WIDE = false>
+__global__ void __launch_bounds__(MmaDecode<NS, WIDE>::WARPS * 32)
 attn_decode_mma_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
                        const int* __restrict__ page_table, int table_stride, const int* __restrict__ seq_slot,
                        const int* __restrict__ seq_len, float* __restrict__ partial, int nq, int nkv, int q_row_heads,
                        float scale, float cap, int window, int ring_len, int chunk, bf16* __restrict__ out) {
-    typedef MmaDecode<NS> S;
+    typedef MmaDecode<NS, WIDE> S;
     extern __shared__ __align__(128) unsigned char stage_mem[];
     __shared__ __align__(8) unsigned long long full[S::STAGES];
     const int s = blockIdx.z;
@@ -1019,18 +1022,18 @@ JANIS_EXPORT int janis_attn_wait_probe(int tries, int* status, cudaStream_t stre
     return launched("wait_probe");
 }
 
-template <int RB, int NS>
+template <int RB, int NS, bool WIDE = false>
 static int launch_decode_mma_ns(const bf16* qkv, const bf16* kpool, const bf16* vpool, const int* page_table,
                                 int table_stride, const int* seq_slot, const int* seq_len, float* partial, int n_seq, int nq,
                                 int nkv, int q_row_heads, float scale, float cap, int window, int ring_len, int chunk,
                                 int max_chunks, bf16* out, cudaStream_t stream) {
-    typedef MmaDecode<NS> S;
+    typedef MmaDecode<NS, WIDE> S;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, false, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, false, NS, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              S::SMEM_BYTES);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, true, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            e = cudaFuncSetAttribute(attn_decode_mma_kernel<RB, true, NS, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      S::SMEM_BYTES);
         if (e != cudaSuccess) return fail("attn_decode: shared memory of %d bytes refused: %s", S::SMEM_BYTES,
                                           cudaGetErrorString(e));
@@ -1039,10 +1042,10 @@ static int launch_decode_mma_ns(const bf16* qkv, const bf16* kpool, const bf16* 
     const int rep = nq / nkv;
     dim3 grid(max_chunks, nkv * ((rep + RB - 1) / RB), n_seq);
     if (out != nullptr)
-        return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, true, NS>, grid, dim3(S::WARPS * 32),
+        return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, true, NS, WIDE>, grid, dim3(S::WARPS * 32),
                              S::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
                              partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, out);
-    return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, false, NS>, grid, dim3(S::WARPS * 32),
+    return launch_kernel("attn_decode", attn_decode_mma_kernel<RB, false, NS, WIDE>, grid, dim3(S::WARPS * 32),
                          S::SMEM_BYTES, stream, 1, qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len,
                          partial, nq, nkv, q_row_heads, scale, cap, window, ring_len, chunk, out);
 }
@@ -1056,6 +1059,9 @@ static int decode_sm_count() {
     }
     return n;
 }
+
+static int g_mma_wide = 1;          // 0: never the stages of 64 keys at head sizes above 128 (tests and tuning)
+JANIS_EXPORT void janis_attn_set_decode_wide(int on) { g_mma_wide = on ? 1 : 0; }
 
 static int g_mma_stages = 0;        // 0: chosen per launch from the number of CTAs; 2 or 3: fixed (tests and tuning)
 
@@ -1076,6 +1082,9 @@ static int launch_decode_mma_rb(const bf16* qkv, const bf16* kpool, const bf16* 
                                 int max_chunks, bf16* out, cudaStream_t stream) {
     const int rep = nq / nkv;
     const long long n_ctas = (long long)max_chunks * nkv * ((rep + RB - 1) / RB) * n_seq;
+    if (HD > 128 && g_mma_wide && n_ctas <= decode_sm_count())       // a CTA an SM at most: stages of 64 keys
+        return launch_decode_mma_ns<RB, 2, true>(qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, n_seq, nq,
+                                                 nkv, q_row_heads, scale, cap, window, ring_len, chunk, max_chunks, out, stream);
     if (janis_attn_decode_stages(n_ctas) == 2)
         return launch_decode_mma_ns<RB, 2>(qkv, kpool, vpool, page_table, table_stride, seq_slot, seq_len, partial, n_seq, nq, nkv,
                                            q_row_heads, scale, cap, window, ring_len, chunk, max_chunks, out, stream);

@@ -95,6 +95,8 @@ def attention_lib(head_dim: int):
         lib.janis_attn_set_prefill_kernel.restype = None
         lib.janis_attn_set_prefill_piece.argtypes = [I]
         lib.janis_attn_set_prefill_piece.restype = None
+        lib.janis_attn_set_decode_wide.argtypes = [I]
+        lib.janis_attn_set_decode_wide.restype = None
         lib.janis_attn_set_prefill_items.argtypes = [I]
         lib.janis_attn_set_prefill_items.restype = None
         lib.janis_attn_prefill_kernels.argtypes = []
@@ -618,6 +620,12 @@ def attn_prefill_piece(hd: int, n_tok: int, n_seq: int, nq: int, window: int = 0
 def attn_tc05_timeouts(hd: int) -> int:
     """How often a CTA of the tcgen05 prompt kernel has given up a wait (0 unless something is badly wrong)."""
     return int(attention_lib(hd).janis_attn_tc05_timeouts())
+
+
+def attn_set_decode_wide(hd: int, on: bool = True) -> None:
+    """Whether the tensor-core decode kernel of a head size above 128 takes stages of 64 keys in launches of no more
+    CTAs than SMs (the default) or stages of 32 keys always.  For tests and tuning."""
+    attention_lib(hd).janis_attn_set_decode_wide(1 if on else 0)
 
 
 def attn_set_decode_kernel(hd: int, which: int = 2) -> None:

@@ -682,15 +682,19 @@ def test_attn_decode(dtype, nq, nkv, hd, window, ring, chunk, kernel):
                   ring, chunk, max_chunks)
     ops().attn_set_decode_kernel(hd, kernel)
     try:
-        for stages in ((2, 3) if kernel == 2 else (0,)):        # the tensor-core kernel with both depths of its pipeline
+        # the tensor-core kernel with both depths of its pipeline, and (this launch has fewer CTAs than a GPU has SMs)
+        # with stages of 64 keys and of 32 at head sizes above 128
+        for stages, wide in (((2, True), (3, True), (2, False)) if kernel == 2 else ((0, True),)):
             ops().attn_set_decode_stages(hd, stages)
+            ops().attn_set_decode_wide(hd, wide)
             out.fill_(7.0)
             ops().attn_decode(qkv, k, v, perm.to(d), seq_slot.to(d), seq_len.to(d), scratch, out, nq, nkv, hd, scale, cap,
                               window, ring, chunk, max_chunks)
-            close(out, want, tol_of(dtype), f"attn_decode (stages {stages})")
+            close(out, want, tol_of(dtype), f"attn_decode (stages {stages}, wide {wide})")
     finally:
         ops().attn_set_decode_kernel(hd, 2)
         ops().attn_set_decode_stages(hd, 0)
+        ops().attn_set_decode_wide(hd, True)
     assert ops().attn_wait_timeouts(hd) == 0
 
 
