@@ -611,7 +611,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 // one) from a counter, so that what a CTA costs besides its tiles is paid once, not per tile of queries: the launch
 // of a CTA of this size and its way out (2 to 3 us), Q and the first keys (asked for while the item before is still
 // at its last tiles), the products' start.  What stays per item is the way out of its result.  An item's place is
-// told to the three roles through two slots in shared memory; the rings of keys and values, the two score buffers,
+// told to the other roles through two slots in shared memory; the rings of keys and values, the two score buffers,
 // P and the accumulator carry on from item to item (their barriers count tiles across items).  The result leaves
 // through the ring stage of the item's last tile (bfloat16: one stage holds a tile of queries), which is the stage
 // of the next item's second tile: the loader brings the next item's first tile meanwhile and waits for the way out
