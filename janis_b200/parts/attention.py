@@ -106,10 +106,13 @@ class SoftmaxAttention(Mixer):
                 launched = min(launched, (self.window + chunk - 1) // chunk + 1)
             resident = held(self.head_dim, ctx.rt.dtype, pairs * launched, sm_count) if held else 2 * sm_count
             if ctx.len_even:
-                # CTAs of equal length run in waves
+                # CTAs of equal length run in waves.  A launch of no more CTAs than SMs takes stages of 64 keys at
+                # head sizes above 128, which cost about two thirds of two stages of 32 (one sequence of 8,100 keys:
+                # 14.9 us a layer at chunks of 256 and 128 CTAs against 17.1 at chunks of 192 and 172 CTAs)
                 n_chunks = (seen + chunk - 1) // chunk + extra
                 waves = (pairs * n_chunks + resident - 1) // resident
-                cost = waves * (min(chunk, seen) // 32 + 6) + n_chunks / 8      # (the merge reads every chunk)
+                wide = self.head_dim > 128 and pairs * launched <= sm_count
+                cost = waves * (min(chunk, seen) // 32 * (0.65 if wide else 1.0) + 6) + n_chunks / 8      # (the merge reads every chunk)
             else:
                 # unequal lengths: the SMs' even share of all tiles and fixed shares, then the longest CTA, which
                 # may start last (halved while every CTA has an SM's slot to itself from the start)
